@@ -1,0 +1,1 @@
+"""CUDA sources of the kernels and the script that builds them."""

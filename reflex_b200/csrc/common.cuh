@@ -1,0 +1,65 @@
+// Shared helpers of the sm_100a kernels: status codes, element loads/stores
+// that widen to 32-bit, warp and block reductions with a fixed order.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define RFX_DT_F32 0
+#define RFX_DT_BF16 1
+
+// Return codes of the host entry points: 0 ok, a positive cudaError_t, or one
+// of these negative values for an argument the kernel refuses.
+#define RFX_ERR_BAD_ARG (-1)
+#define RFX_ERR_UNSUPPORTED (-2)
+#define RFX_ERR_TIMEOUT (-3)
+
+#define RFX_CHECK_LAUNCH()                         \
+    do {                                           \
+        cudaError_t e__ = cudaGetLastError();      \
+        if (e__ != cudaSuccess) return (int)e__;   \
+    } while (0)
+
+namespace rfx {
+
+template <typename T> __device__ __forceinline__ float ld(const T* p, size_t i);
+template <> __device__ __forceinline__ float ld<float>(const float* p, size_t i) { return p[i]; }
+template <> __device__ __forceinline__ float ld<__nv_bfloat16>(const __nv_bfloat16* p, size_t i) {
+    return __bfloat162float(p[i]);
+}
+
+template <typename T> __device__ __forceinline__ void st(T* p, size_t i, float v);
+template <> __device__ __forceinline__ void st<float>(float* p, size_t i, float v) { p[i] = v; }
+template <> __device__ __forceinline__ void st<__nv_bfloat16>(__nv_bfloat16* p, size_t i, float v) {
+    p[i] = __float2bfloat16_rn(v);
+}
+
+// Sum over the 32 lanes in a fixed butterfly order; every lane gets the total.
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads.  `scratch` holds 32 floats.  The
+// order (lane butterfly, then warps in index order) depends only on blockDim.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();  // scratch may still be read from an earlier call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = 0.0f;
+    for (int w = 0; w < nwarps; ++w) total += scratch[w];
+    return total;
+}
+
+}  // namespace rfx

@@ -1,0 +1,183 @@
+// Embedding gather, RMSNorm with the residual add, SwiGLU.
+//
+// Statistics and the residual stream are 32-bit in both precisions; only what
+// feeds a matrix product is rounded to bfloat16 on the bfloat16 path.
+#include "common.cuh"
+
+namespace {
+
+using namespace rfx;
+
+// hidden[r, :] = table[ids[r], :] * scale       (src/model/dense.rs:1959-1967)
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                             float* __restrict__ out, int H, int V, float scale,
+                             int* __restrict__ err) {
+    const int r = blockIdx.x;
+    const int id = ids[r];
+    if (id < 0 || id >= V) {
+        if (threadIdx.x == 0) atomicExch(err, 1 + r);
+        for (int c = threadIdx.x; c < H; c += blockDim.x) out[(size_t)r * H + c] = 0.0f;
+        return;
+    }
+    const T* row = table + (size_t)id * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x)
+        out[(size_t)r * H + c] = ld<T>(row, c) * scale;
+}
+
+// One block per output row.
+//   src = rows ? rows[blockIdx.x] : blockIdx.x
+//   t   = x[src] (+ delta[src])                     residual sum in 32-bit
+//   if x_out: x_out[src] = t                        (only without `rows`; may be x)
+//   if out:   out[blockIdx.x] = t * rsqrt(mean(t^2) + eps) * (w_offset + w)
+// The sum of squares runs in an order fixed by the block size, which the host
+// derives from H alone, so a row's result does not depend on the batch.
+// Formula: src/kernels_cuda/rmsnorm.cuh:14-40, rmsnorm.cu:44-52; the fused add
+// is src/kernels_cuda/decode_ops.cu:10-35.
+template <typename TD, typename TO>
+__global__ void rmsnorm_kernel(const float* x, const TD* __restrict__ delta,
+                               float* x_out, const float* __restrict__ w,
+                               TO* __restrict__ out, const int* __restrict__ rows, int H,
+                               float eps, float w_offset) {
+    __shared__ float scratch[32];
+    extern __shared__ float row_buf[];  // H floats
+    const int src = rows ? rows[blockIdx.x] : blockIdx.x;
+    const float* xr = x + (size_t)src * H;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float t = xr[c];
+        if (delta) t += ld<TD>(delta, (size_t)src * H + c);
+        row_buf[c] = t;
+        ss = fmaf(t, t, ss);
+    }
+    if (x_out) {
+        for (int c = threadIdx.x; c < H; c += blockDim.x) x_out[(size_t)src * H + c] = row_buf[c];
+    }
+    if (!out) return;
+    const float total = block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(total / (float)H + eps);
+    TO* orow = out + (size_t)blockIdx.x * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x)
+        st<TO>(orow, c, (row_buf[c] * r) * (w_offset + w[c]));
+}
+
+// out[r, i] = silu(gu[r, i]) * gu[r, I + i],  silu(g) = g / (1 + exp(-g))
+// (src/kernels_cuda/silu_and_mul.cu:7-23)
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int R, int I) {
+    const size_t n = (size_t)R * I;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / I, c = i % I;
+        const float g = ld<T>(gu, r * 2 * I + c);
+        const float u = ld<T>(gu, r * 2 * I + I + c);
+        st<T>(out, i, (g / (1.0f + expf(-g))) * u);
+    }
+}
+
+// y[i] = a[i] + b[i] in 32-bit (src/kernels_cuda/elementwise.cu:8-24)
+template <typename T>
+__global__ void add_kernel(float* __restrict__ a, const T* __restrict__ b, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x)
+        a[i] += ld<T>(b, i);
+}
+
+int norm_threads(int H) {
+    int t = ((H + 3) / 4 + 31) / 32 * 32;
+    if (t < 32) t = 32;
+    if (t > 512) t = 512;
+    return t;
+}
+
+}  // namespace
+
+extern "C" int rfx_embed(const void* table, int table_dt, const int* ids, int R, int H, int V,
+                         float scale, float* out, int* err, void* stream) {
+    if (R <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dt == RFX_DT_F32)
+        embed_kernel<float><<<R, threads, 0, s>>>((const float*)table, ids, out, H, V, scale, err);
+    else if (table_dt == RFX_DT_BF16)
+        embed_kernel<__nv_bfloat16>
+            <<<R, threads, 0, s>>>((const __nv_bfloat16*)table, ids, out, H, V, scale, err);
+    else
+        return RFX_ERR_BAD_ARG;
+    RFX_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int rfx_rmsnorm(const float* x, const void* delta, int delta_dt, float* x_out,
+                           const float* w, float eps, float w_offset, void* out, int out_dt,
+                           const int* rows, int R_out, int H, void* stream) {
+    if (R_out <= 0) return 0;
+    if (rows && x_out) return RFX_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = norm_threads(H);
+    const size_t smem = (size_t)H * sizeof(float);
+    if (smem > 200 * 1024) return RFX_ERR_UNSUPPORTED;
+#define RFX_NORM(TD, TO)                                                                       \
+    do {                                                                                       \
+        if (smem > 48 * 1024) {                                                                \
+            cudaError_t e = cudaFuncSetAttribute(rmsnorm_kernel<TD, TO>,                       \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                                                 (int)smem);                                   \
+            if (e != cudaSuccess) return (int)e;                                               \
+        }                                                                                      \
+        rmsnorm_kernel<TD, TO><<<R_out, threads, smem, s>>>(x, (const TD*)delta, x_out, w,     \
+                                                            (TO*)out, rows, H, eps, w_offset); \
+    } while (0)
+    const bool dbf = delta && delta_dt == RFX_DT_BF16;
+    if (out_dt == RFX_DT_BF16) {
+        if (dbf) RFX_NORM(__nv_bfloat16, __nv_bfloat16);
+        else RFX_NORM(float, __nv_bfloat16);
+    } else if (out_dt == RFX_DT_F32) {
+        if (dbf) RFX_NORM(__nv_bfloat16, float);
+        else RFX_NORM(float, float);
+    } else {
+        return RFX_ERR_BAD_ARG;
+    }
+#undef RFX_NORM
+    RFX_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int rfx_swiglu(const void* gate_up, void* out, int dt, int R, int I, void* stream) {
+    if (R <= 0 || I <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t n = (size_t)R * I;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dt == RFX_DT_F32)
+        swiglu_kernel<float><<<blocks, 256, 0, s>>>((const float*)gate_up, (float*)out, R, I);
+    else if (dt == RFX_DT_BF16)
+        swiglu_kernel<__nv_bfloat16>
+            <<<blocks, 256, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, R, I);
+    else
+        return RFX_ERR_BAD_ARG;
+    RFX_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int rfx_add(float* a, const void* b, int b_dt, long long n, void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (b_dt == RFX_DT_F32)
+        add_kernel<float><<<blocks, 256, 0, s>>>(a, (const float*)b, (size_t)n);
+    else if (b_dt == RFX_DT_BF16)
+        add_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(a, (const __nv_bfloat16*)b, (size_t)n);
+    else
+        return RFX_ERR_BAD_ARG;
+    RFX_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" const char* rfx_error_string(int code) {
+    if (code == RFX_ERR_BAD_ARG) return "bad argument";
+    if (code == RFX_ERR_UNSUPPORTED) return "size not supported by this kernel";
+    if (code == RFX_ERR_TIMEOUT) return "bounded device wait ran out";
+    return cudaGetErrorString((cudaError_t)code);
+}

@@ -1,0 +1,134 @@
+// After the q/k/v projections, per row and head: per-head RMSNorm of q and k,
+// rotary position encoding, then q to the workspace and k, v into the paged
+// cache at the row's position.  One launch instead of the reference's five
+// (norm x2, rope x2, cache store: src/model/dense.rs:1355-1409; decode:
+// src/model/decode_step.rs:232-279).
+//
+// Formulas.  Norm: y = (x * r) * w, r = 1/sqrt(mean(x^2) + eps), one weight
+// vector of head_dim shared by all heads (src/kernels_cuda/decode_ops.cu:40-71).
+// Rotary, half-split pairs (i, i + rd/2) for i < rd/2
+// (src/kernels_cuda/rope.cu:9-37):  theta = (float)pos / denom[i] with
+// denom[i] = base^(2i/rd);  (a, b) <- (a cos - b sin, a sin + b cos).
+// Elements >= rd stay.  v is stored as projected.  All arithmetic is 32-bit;
+// the angle is a 32-bit division followed by sincosf with full range reduction.
+#include "common.cuh"
+#include "paged.cuh"
+
+namespace {
+
+using namespace rfx;
+
+constexpr int MAX_PER_LANE = 16;  // head_dim <= 512
+
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(128)
+qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restrict__ q_w,
+                const float* __restrict__ k_w, float eps, float w_offset,
+                const float* __restrict__ rope_denom, int rotary_dim,
+                const int* __restrict__ row_pos, const int* __restrict__ row_slot,
+                TO* __restrict__ q_out, TO* __restrict__ k_pages, TO* __restrict__ v_pages,
+                PagedKV cache, int nq, int nkv_in) {
+    extern __shared__ float smem[];  // [warps][head_dim]
+    const int d = cache.head_dim;
+    const int r = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int pos = row_pos[r];
+    const int slot = row_slot[r];
+    float* buf = smem + warp * d;
+    const int half = rotary_dim / 2;
+    const int total = nq + 2 * nkv_in;
+
+    for (int hh = warp; hh < total; hh += nwarps) {
+        const TI* src = qkv + (size_t)r * row_stride + (size_t)hh * d;
+        const bool is_q = hh < nq;
+        const bool is_k = !is_q && hh < nq + nkv_in;
+        TO* dst;
+        if (is_q) {
+            dst = q_out + ((size_t)r * nq + hh) * d;
+        } else if (is_k) {
+            dst = k_pages + kv_offset(cache, slot, pos, hh - nq);
+        } else {
+            dst = v_pages + kv_offset(cache, slot, pos, hh - nq - nkv_in);
+        }
+        if (!is_q && !is_k) {  // v: stored as projected
+            for (int e = lane; e < d; e += 32) st<TO>(dst, e, ld<TI>(src, e));
+            continue;
+        }
+        float v[MAX_PER_LANE];
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < MAX_PER_LANE; ++i) {
+            const int e = i * 32 + lane;
+            v[i] = e < d ? ld<TI>(src, e) : 0.0f;
+            ss = fmaf(v[i], v[i], ss);
+        }
+        const float* w = is_q ? q_w : k_w;
+        if (w) {
+            const float rinv = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);
+#pragma unroll
+            for (int i = 0; i < MAX_PER_LANE; ++i) {
+                const int e = i * 32 + lane;
+                if (e < d) v[i] = (v[i] * rinv) * (w_offset + w[e]);
+            }
+        }
+        if (rope_denom == nullptr || half == 0) {
+#pragma unroll
+            for (int i = 0; i < MAX_PER_LANE; ++i) {
+                const int e = i * 32 + lane;
+                if (e < d) st<TO>(dst, e, v[i]);
+            }
+            continue;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < MAX_PER_LANE; ++i) {
+            const int e = i * 32 + lane;
+            if (e < d) buf[e] = v[i];
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < MAX_PER_LANE; ++i) {
+            const int e = i * 32 + lane;
+            if (e >= d) break;
+            float o = v[i];
+            if (e < rotary_dim) {
+                const int fi = e < half ? e : e - half;
+                const float theta = (float)pos / rope_denom[fi];
+                float sn, cs;
+                sincosf(theta, &sn, &cs);
+                if (e < half) o = v[i] * cs - buf[e + half] * sn;
+                else o = buf[e - half] * sn + v[i] * cs;
+            }
+            st<TO>(dst, e, o);
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" int rfx_qkv_post(const void* qkv, int in_dt, int row_stride, const float* q_w,
+                            const float* k_w, float eps, float w_offset, const float* rope_denom,
+                            int rotary_dim, const int* row_pos, const int* row_slot, void* q_out,
+                            void* k_pages, void* v_pages, int out_dt, const int* page_table,
+                            int max_pages, int page_size, int R, int nq, int nkv_in, int nkv,
+                            int head_dim, void* stream) {
+    if (R <= 0) return 0;
+    if (head_dim <= 0 || head_dim > 32 * MAX_PER_LANE) return RFX_ERR_UNSUPPORTED;
+    if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return RFX_ERR_BAD_ARG;
+    if (nkv_in != 0 && nkv_in != nkv) return RFX_ERR_BAD_ARG;
+    PagedKV cache{page_table, max_pages, page_size, nkv, head_dim};
+    const int threads = 128;
+    const size_t smem = (size_t)(threads / 32) * head_dim * sizeof(float);
+    cudaStream_t s = (cudaStream_t)stream;
+#define RFX_POST(TI, TO)                                                                        \
+    qkv_post_kernel<TI, TO><<<R, threads, smem, s>>>(                                           \
+        (const TI*)qkv, row_stride, q_w, k_w, eps, w_offset, rope_denom, rotary_dim, row_pos,   \
+        row_slot, (TO*)q_out, (TO*)k_pages, (TO*)v_pages, cache, nq, nkv_in)
+    if (in_dt == RFX_DT_F32 && out_dt == RFX_DT_F32) RFX_POST(float, float);
+    else if (in_dt == RFX_DT_F32 && out_dt == RFX_DT_BF16) RFX_POST(float, __nv_bfloat16);
+    else if (in_dt == RFX_DT_BF16 && out_dt == RFX_DT_BF16) RFX_POST(__nv_bfloat16, __nv_bfloat16);
+    else return RFX_ERR_BAD_ARG;
+#undef RFX_POST
+    RFX_CHECK_LAUNCH();
+    return 0;
+}

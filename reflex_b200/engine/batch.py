@@ -1,0 +1,116 @@
+"""The description of one step's work, on the host and on the device.
+
+Rows of all sequences are packed without padding: sequence s brings
+`n_new[s]` tokens, which become rows `row0[s] .. row0[s] + n_new[s]` at
+positions `start[s] ..`.  Every kernel reads a row's position and slot from
+device arrays, so the same launch set serves any mix of lengths and a captured
+graph can be replayed with new contents.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import torch
+
+
+@dataclass
+class StepBatch:
+    # host side
+    slots: List[int]
+    starts: List[int]          # positions already in the cache per sequence
+    new_counts: List[int]
+    row0: List[int]            # first row of each sequence; len S + 1
+    want_rows_host: List[int]  # packed row indices whose logits are wanted
+    # device side (int32)
+    tokens: torch.Tensor       # [R]
+    row_pos: torch.Tensor      # [R]
+    row_slot: torch.Tensor     # [R]
+    seq_slot: torch.Tensor     # [S]
+    seq_start: torch.Tensor    # [S]
+    seq_new: torch.Tensor      # [S]
+    seq_row0: torch.Tensor     # [S + 1]
+    want_rows: torch.Tensor    # [n_want]
+
+    @property
+    def n_rows(self) -> int:
+        return self.row0[-1]
+
+    @property
+    def n_seqs(self) -> int:
+        return len(self.slots)
+
+    @property
+    def is_decode(self) -> bool:
+        return all(n == 1 for n in self.new_counts)
+
+    @property
+    def max_new(self) -> int:
+        return max(self.new_counts)
+
+    @property
+    def max_context(self) -> int:
+        return max(s + n for s, n in zip(self.starts, self.new_counts))
+
+
+def layout(n_rows: int, n_seqs: int, n_want: int):
+    """Offsets of the fields inside one int32 buffer."""
+    o = {}
+    p = 0
+    for name, n in (("tokens", n_rows), ("row_pos", n_rows), ("row_slot", n_rows),
+                    ("seq_slot", n_seqs), ("seq_start", n_seqs), ("seq_new", n_seqs),
+                    ("seq_row0", n_seqs + 1), ("want_rows", n_want)):
+        o[name] = (p, n)
+        p += (n + 3) // 4 * 4  # 16-byte aligned fields
+    return o, p
+
+
+def pack_host(tokens: Sequence[Sequence[int]], slots: Sequence[int], starts: Sequence[int],
+              want: Sequence[Sequence[int]]):
+    """Flatten a step into the int32 words of `layout`, plus the host lists."""
+    new_counts = [len(t) for t in tokens]
+    row0 = [0]
+    for n in new_counts:
+        row0.append(row0[-1] + n)
+    R, S = row0[-1], len(tokens)
+    want_rows = [row0[i] + w for i, ws in enumerate(want) for w in ws]
+    offs, total = layout(R, S, len(want_rows))
+    words = [0] * total
+
+    def put(name, values):
+        p, n = offs[name]
+        words[p:p + n] = values
+
+    put("tokens", [t for seq in tokens for t in seq])
+    put("row_pos", [starts[i] + j for i in range(S) for j in range(new_counts[i])])
+    put("row_slot", [slots[i] for i in range(S) for _ in range(new_counts[i])])
+    put("seq_slot", list(slots))
+    put("seq_start", list(starts))
+    put("seq_new", new_counts)
+    put("seq_row0", row0)
+    put("want_rows", want_rows)
+    return words, offs, new_counts, row0, want_rows
+
+
+def make_batch(tokens, slots, starts, want, device, buffer: Optional[torch.Tensor] = None) -> StepBatch:
+    """Build the step's descriptors with one host-to-device copy.  With
+    `buffer` (a device int32 tensor large enough) the words are copied into it,
+    so a captured graph that reads the buffer sees the new step."""
+    words, offs, new_counts, row0, want_rows = pack_host(tokens, slots, starts, want)
+    host = torch.tensor(words, dtype=torch.int32)
+    if buffer is None:
+        dev = host.to(device)
+    else:
+        dev = buffer[: len(words)]
+        dev.copy_(host)
+
+    def f(name):
+        p, n = offs[name]
+        return dev[p:p + n]
+
+    return StepBatch(
+        slots=list(slots), starts=list(starts), new_counts=new_counts, row0=row0,
+        want_rows_host=want_rows, tokens=f("tokens"), row_pos=f("row_pos"), row_slot=f("row_slot"),
+        seq_slot=f("seq_slot"), seq_start=f("seq_start"), seq_new=f("seq_new"),
+        seq_row0=f("seq_row0"), want_rows=f("want_rows"))

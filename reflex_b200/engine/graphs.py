@@ -1,0 +1,44 @@
+"""Decode steps replayed as CUDA graphs.
+
+A decode step is a fixed set of launches whose sizes depend only on the number
+of sequences; positions, slots and tokens are read from device memory.  So one
+graph per batch size is captured at its first use and replayed afterwards with
+new contents copied into the same descriptor buffer.  (The reference's attempt
+failed because positions were kernel arguments that changed each step:
+docs/design/decode-speed.md:189-207.)
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .batch import layout, make_batch
+
+
+class DecodeGraph:
+    WARMUP = 2
+
+    def __init__(self, engine, n_seqs: int):
+        self.engine = engine
+        self.n = n_seqs
+        _, total = layout(n_seqs, n_seqs, n_seqs)
+        self.buffer = torch.zeros((total,), dtype=torch.int32, device=engine.device)
+        self.graph = None
+        self.logits = None
+        self.calls = 0
+
+    def run(self, tokens, slots, starts, want) -> torch.Tensor:
+        eng = self.engine
+        batch = make_batch(tokens, slots, starts, want, eng.device, buffer=self.buffer)
+        if self.graph is None:
+            self.calls += 1
+            if self.calls <= self.WARMUP:
+                return eng.model.forward(batch, eng.cache)
+            # capture: the eager call above has already sized every lazy buffer
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.logits = eng.model.forward(batch, eng.cache)
+            self.graph = g
+        self.graph.replay()
+        return self.logits

@@ -1,0 +1,111 @@
+"""The step function: the one way tokens go through the model.
+
+`Engine.step(entries)` takes, for each sequence of the batch, its next tokens
+(a whole prompt, a chunk of one, or a single decoded token) and the places
+among them whose logits are wanted.  It runs exactly those tokens as one packed
+batch against the cache that earlier steps left, writes their keys and values,
+and returns float32 logits [wanted, vocab].  There is no padding: a row's
+result depends only on its own sequence.  The reference has the two special
+cases, a whole-prompt prefill of one sequence and a one-token step
+(src/model/dense.rs:1930-1985, src/model/decode_step.rs:139-329); batches and
+mixed steps are this library's own.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache.store import PAGE_TOKENS, Cache
+from ..errors import CacheError, InvalidInput
+from .batch import StepBatch, make_batch
+from .model import CausalLM
+
+StepEntry = Tuple[int, Sequence[int], Sequence[int]]  # (sequence, tokens, wanted places)
+
+
+class Engine:
+    def __init__(self, model: CausalLM, max_tokens: int, max_slots: Optional[int] = None,
+                 use_graphs: bool = True):
+        self.model = model
+        self.device = model.device
+        self.cache = Cache(model.cache_entry_specs(), max_tokens, model.spec.max_positions,
+                           model.dtype, model.device, max_slots=max_slots)
+        self.vocab_size = model.spec.vocab_size
+        self.use_graphs = use_graphs and model.dtype == torch.bfloat16
+        self._graphs: Dict[int, "object"] = {}
+        self.steps_run = 0
+
+    # --- sequences ----------------------------------------------------------
+    def open(self) -> int:
+        """Start a sequence: takes a cache slot, returns its handle."""
+        return self.cache.take_slot()
+
+    def close(self, seq: int) -> None:
+        """End a sequence: its slot and pages go back to the cache."""
+        self.cache.give_slot(seq)
+
+    def length(self, seq: int) -> int:
+        return self.cache.length(seq)
+
+    # --- the step -------------------------------------------------------------
+    def _check(self, entries: Sequence[StepEntry]) -> None:
+        if not entries:
+            raise InvalidInput("a step needs at least one sequence")
+        seen = set()
+        V = self.vocab_size
+        for seq, tokens, want in entries:
+            if seq in seen:
+                raise InvalidInput(f"sequence {seq} appears twice in one step")
+            seen.add(seq)
+            if len(tokens) == 0:
+                raise InvalidInput(f"sequence {seq}: a step must bring at least one token")
+            for t in tokens:
+                if not (0 <= int(t) < V):
+                    raise InvalidInput(f"sequence {seq}: token id {t} is outside the vocabulary [0, {V})")
+            for w in want:
+                if not (0 <= int(w) < len(tokens)):
+                    raise InvalidInput(
+                        f"sequence {seq}: wanted place {w} is outside this step's {len(tokens)} tokens")
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        self._check(entries)
+        cache = self.cache
+        slots = [int(e[0]) for e in entries]
+        starts = [cache.length(s) for s in slots]
+        tokens = [[int(t) for t in e[1]] for e in entries]
+        want = [[int(w) for w in e[2]] for e in entries]
+        growth = [(s, len(t)) for s, t in zip(slots, tokens)]
+        before = [[g.end[s] for s in slots] for g in cache.kv_groups]
+        cache.reserve(growth)
+        try:
+            n_want = sum(len(w) for w in want)
+            if self.use_graphs and all(len(t) == 1 for t in tokens) and n_want == len(tokens):
+                logits = self._decode_graphed(tokens, slots, starts, want)
+            else:
+                batch = make_batch(tokens, slots, starts, want, self.device)
+                if n_want:
+                    logits = self.model.forward(batch, cache)
+                else:
+                    self.model.hidden_states(batch, cache)
+                    logits = torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        except Exception:
+            for g, ends in zip(cache.kv_groups, before):
+                for s, e in zip(slots, ends):
+                    g.shrink_to(s, e)
+            raise
+        cache.commit(growth)
+        self.steps_run += 1
+        return logits
+
+    # --- decode steps as CUDA graphs -----------------------------------------
+    def _decode_graphed(self, tokens, slots, starts, want) -> torch.Tensor:
+        from .graphs import DecodeGraph
+
+        n = len(tokens)
+        g = self._graphs.get(n)
+        if g is None:
+            g = DecodeGraph(self, n)
+            self._graphs[n] = g
+        return g.run(tokens, slots, starts, want)

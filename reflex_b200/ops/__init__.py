@@ -1,0 +1,206 @@
+"""Python faces of the CUDA kernels.
+
+Each function checks its tensors (device, dtype, layout), allocates the
+output, and launches on torch's current stream, so the calls order with the
+library matrix products and can be captured into a CUDA graph.  Sizes a kernel
+does not take are refused with an error that names them.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..errors import CudaError, InvalidInput
+from . import native
+
+F32, BF16 = 0, 1
+
+
+def dt_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise InvalidInput(f"kernels take float32 or bfloat16, got {dtype}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _chk(t: Optional[torch.Tensor], name: str, dtype=None) -> int:
+    if t is None:
+        return 0
+    if not t.is_cuda:
+        raise CudaError(f"{name} must live on the GPU (there is no CPU path)")
+    if not t.is_contiguous():
+        raise InvalidInput(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise InvalidInput(f"{name} must be {dtype}, got {t.dtype}")
+    return t.data_ptr()
+
+
+# ---------------------------------------------------------------- elementwise
+def embed(table: torch.Tensor, ids: torch.Tensor, scale: float, err_flag: torch.Tensor) -> torch.Tensor:
+    """hidden[r] = table[ids[r]] * scale, as float32 [R, H]."""
+    V, H = table.shape
+    R = ids.numel()
+    out = torch.empty((R, H), dtype=torch.float32, device=table.device)
+    st = native.lib().rfx_embed(
+        _chk(table, "table"), dt_code(table.dtype), _chk(ids, "ids", torch.int32), R, H, V,
+        float(scale), out.data_ptr(), _chk(err_flag, "err_flag", torch.int32), _stream())
+    native.check(st, "embed")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+            delta: Optional[torch.Tensor] = None, update_residual: bool = True,
+            rows: Optional[torch.Tensor] = None, weight_offset: float = 0.0,
+            want_out: bool = True) -> Optional[torch.Tensor]:
+    """RMSNorm of the float32 residual stream `x` [R, H], with the residual add
+    fused in: t = x (+ delta); x <- t (if `update_residual`, in place);
+    returns t * rsqrt(mean(t^2) + eps) * (weight_offset + weight) in
+    `out_dtype`.  With `rows` only those rows are read and the output has
+    `len(rows)` rows (the residual is then left alone)."""
+    R, H = x.shape
+    _chk(x, "x", torch.float32)
+    r_out = R if rows is None else rows.numel()
+    out = torch.empty((r_out, H), dtype=out_dtype, device=x.device) if want_out else None
+    x_out = x if (delta is not None and update_residual and rows is None) else None
+    st = native.lib().rfx_rmsnorm(
+        x.data_ptr(), _chk(delta, "delta"), dt_code(delta.dtype) if delta is not None else 0,
+        x_out.data_ptr() if x_out is not None else 0, _chk(weight, "weight", torch.float32),
+        float(eps), float(weight_offset), out.data_ptr() if out is not None else 0,
+        dt_code(out_dtype), _chk(rows, "rows", torch.int32), r_out, H, _stream())
+    native.check(st, f"rmsnorm (H={H})")
+    return out
+
+
+def add_(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a += b with a float32."""
+    _chk(a, "a", torch.float32)
+    st = native.lib().rfx_add(a.data_ptr(), _chk(b, "b"), dt_code(b.dtype), a.numel(), _stream())
+    native.check(st, "add")
+    return a
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """[R, 2I] -> silu(gate) * up, [R, I]; gate is the first half of a row."""
+    R, two_i = gate_up.shape
+    I = two_i // 2
+    out = torch.empty((R, I), dtype=gate_up.dtype, device=gate_up.device)
+    st = native.lib().rfx_swiglu(_chk(gate_up, "gate_up"), out.data_ptr(), dt_code(gate_up.dtype),
+                                 R, I, _stream())
+    native.check(st, "swiglu")
+    return out
+
+
+# -------------------------------------------------------------------- linear
+GEMV_MAX_ROWS = 16
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """y = x @ weight.T for weight [N, K] row-major.
+
+    float32: this library's own CUDA-core product (no reduced-precision matrix
+    mode; each output element reduced over k in index order).
+    bfloat16: the weight-streaming kernel for a few rows, the library matrix
+    product (cuBLAS, 32-bit accumulation) above that, where the reference uses
+    a library product too (src/model/kernels.rs:2518-2561)."""
+    R, K = x.shape
+    N, K2 = weight.shape
+    if K != K2:
+        raise InvalidInput(f"linear: x has {K} columns, weight has {K2}")
+    if x.dtype != weight.dtype:
+        raise InvalidInput(f"linear: x is {x.dtype}, weight is {weight.dtype}")
+    _chk(x, "x")
+    _chk(weight, "weight")
+    if x.dtype == torch.float32:
+        y = torch.empty((R, N), dtype=torch.float32, device=x.device)
+        st = native.lib().rfx_gemm_f32(x.data_ptr(), weight.data_ptr(), y.data_ptr(), R, N, K, _stream())
+        native.check(st, f"gemm_f32 (R={R}, N={N}, K={K})")
+        return y
+    out_dtype = out_dtype or torch.bfloat16
+    if R <= GEMV_MAX_ROWS and K % 8 == 0:
+        y = torch.empty((R, N), dtype=out_dtype, device=x.device)
+        st = native.lib().rfx_gemv_bf16(x.data_ptr(), weight.data_ptr(), y.data_ptr(),
+                                        dt_code(out_dtype), R, N, K, _stream())
+        native.check(st, f"gemv_bf16 (R={R}, N={N}, K={K})")
+        return y
+    if out_dtype == torch.float32:
+        return torch.mm(x, weight.t(), out_dtype=torch.float32)
+    return torch.mm(x, weight.t())
+
+
+# ----------------------------------------------------------------- attention
+def qkv_post(qkv: torch.Tensor, q_weight, k_weight, eps: float, weight_offset: float,
+             rope_denom, rotary_dim: int, row_pos: torch.Tensor, row_slot: torch.Tensor,
+             k_pages, v_pages, page_table: torch.Tensor, page_size: int, nq: int, nkv: int,
+             head_dim: int, writes_cache: bool, out_dtype: torch.dtype) -> torch.Tensor:
+    """Per-head q/k norm, rotary encoding, q out, k and v into the cache."""
+    R = qkv.shape[0]
+    nkv_in = nkv if writes_cache else 0
+    if qkv.shape[1] != (nq + 2 * nkv_in) * head_dim:
+        raise InvalidInput("qkv_post: qkv width does not match the head counts")
+    q = torch.empty((R, nq * head_dim), dtype=out_dtype, device=qkv.device)
+    st = native.lib().rfx_qkv_post(
+        _chk(qkv, "qkv"), dt_code(qkv.dtype), qkv.shape[1], _chk(q_weight, "q_norm", torch.float32),
+        _chk(k_weight, "k_norm", torch.float32), float(eps), float(weight_offset),
+        _chk(rope_denom, "rope_denom", torch.float32), int(rotary_dim),
+        _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32),
+        q.data_ptr(), _chk(k_pages, "k_pages"), _chk(v_pages, "v_pages"), dt_code(out_dtype),
+        _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size, R, nq, nkv_in,
+        nkv, head_dim, _stream())
+    native.check(st, f"qkv_post (head_dim={head_dim})")
+    return q
+
+
+def attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                    page_table: torch.Tensor, page_size: int, row_pos: torch.Tensor,
+                    row_slot: torch.Tensor, nq: int, nkv: int, head_dim: int,
+                    window: Optional[int], scale: float) -> torch.Tensor:
+    R = q.shape[0]
+    out = torch.empty_like(q)
+    st = native.lib().rfx_attention_plain(
+        _chk(q, "q"), _chk(k_pages, "k_pages", q.dtype), _chk(v_pages, "v_pages", q.dtype),
+        dt_code(q.dtype), _chk(page_table, "page_table", torch.int32), page_table.shape[1],
+        page_size, _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32),
+        out.data_ptr(), R, nq, nkv, head_dim, int(window or 0), float(scale), _stream())
+    native.check(st, f"attention_plain (head_dim={head_dim})")
+    return out
+
+
+def attention(q, k_pages, v_pages, page_table, page_size, batch, nq, nkv, head_dim, window, scale):
+    """Attention of the step's rows over their sequences' cached keys and
+    values; picks the kernel for the dtype and the kind of step."""
+    return attention_plain(q, k_pages, v_pages, page_table, page_size, batch.row_pos,
+                           batch.row_slot, nq, nkv, head_dim, window, scale)
+
+
+# ------------------------------------------------------------------ sampling
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    B, V = logits.shape
+    _chk(logits, "logits", torch.float32)
+    out = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    st = native.lib().rfx_argmax(logits.data_ptr(), V, B, V, out.data_ptr(), _stream())
+    native.check(st, "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
+           top_k: Optional[torch.Tensor] = None, top_p: Optional[torch.Tensor] = None,
+           scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    B, V = logits.shape
+    _chk(logits, "logits", torch.float32)
+    if scratch is None:
+        scratch = torch.empty((B, V), dtype=torch.float32, device=logits.device)
+    out = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    st = native.lib().rfx_sample(
+        logits.data_ptr(), V, B, V, _chk(temperature, "temperature", torch.float32),
+        _chk(top_k, "top_k", torch.int32), _chk(top_p, "top_p", torch.float32),
+        _chk(uniform, "uniform", torch.float32), _chk(scratch, "scratch", torch.float32),
+        out.data_ptr(), _stream())
+    native.check(st, "sample")
+    return out

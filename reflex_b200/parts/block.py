@@ -1,0 +1,62 @@
+"""Block arrangements: how a layer's parts are wired around the residual.
+
+"prenorm": h += mixer(norm1(h)); h += ffn(norm2(h))
+(src/model/dense.rs:1441-1484).  The residual stream is 32-bit; each add is
+fused into the norm that follows it, so a block hands its last delta on as
+`pending` and the next block's (or the model's final) norm adds it
+(src/model/decode_step.rs:199-210, 293-300).
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from ..config.spec import LayerSpec, names_dict
+from .registry import FEED_FORWARDS, MIXERS, NORMS, TensorInfo, register_block
+
+
+@register_block("prenorm")
+class PreNormBlock:
+    def __init__(self, spec: LayerSpec, dtype: torch.dtype, device):
+        self.spec = spec
+        self.mixer_norm = NORMS.get(spec.mixer_norm.kind)(spec.mixer_norm, dtype, device)
+        self.feed_forward_norm = NORMS.get(spec.feed_forward_norm.kind)(
+            spec.feed_forward_norm, dtype, device)
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, dtype, device)
+        self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, dtype, device)
+
+    @classmethod
+    def tensor_names(cls, spec: LayerSpec) -> Dict[str, Tuple[str, str, TensorInfo]]:
+        """full tensor name -> (part, role, info) for every tensor of the layer."""
+        out: Dict[str, Tuple[str, str, TensorInfo]] = {}
+        block_names = names_dict(spec.names)
+
+        def add(part: str, infos: Dict[str, TensorInfo], names: Dict[str, str]) -> None:
+            for role, info in infos.items():
+                suffix = names.get(role, role)
+                out[spec.prefix + suffix] = (part, role, info)
+
+        add("mixer_norm", {"weight": NORMS.get(spec.mixer_norm.kind).tensor_specs(spec.mixer_norm)["weight"]},
+            {"weight": block_names.get("mixer_norm", "mixer_norm.weight")})
+        add("feed_forward_norm",
+            {"weight": NORMS.get(spec.feed_forward_norm.kind).tensor_specs(spec.feed_forward_norm)["weight"]},
+            {"weight": block_names.get("feed_forward_norm", "feed_forward_norm.weight")})
+        add("mixer", MIXERS.get(spec.mixer.kind).tensor_specs(spec.mixer), names_dict(spec.mixer.names))
+        add("feed_forward", FEED_FORWARDS.get(spec.feed_forward.kind).tensor_specs(spec.feed_forward),
+            names_dict(spec.feed_forward.names))
+        return out
+
+    def bind(self, by_part: Dict[str, Dict[str, torch.Tensor]]) -> None:
+        self.mixer_norm.bind(by_part.get("mixer_norm", {}))
+        self.feed_forward_norm.bind(by_part.get("feed_forward_norm", {}))
+        self.mixer.bind(by_part.get("mixer", {}))
+        self.feed_forward.bind(by_part.get("feed_forward", {}))
+
+    def forward(self, hidden: torch.Tensor, pending: Optional[torch.Tensor], ctx):
+        x = self.mixer_norm(hidden, delta=pending)
+        a = self.mixer.forward(x, ctx)
+        x = self.feed_forward_norm(hidden, delta=a)
+        f = self.feed_forward.forward(x)
+        return hidden, f

@@ -1,0 +1,49 @@
+"""Gated feed-forward (SwiGLU), dense.
+
+gate = x Wg^T, up = x Wu^T, act = gate / (1 + exp(-gate)) * up, out = act Wd^T
+(src/model/dense.rs:1476-1481, src/kernels_cuda/silu_and_mul.cu:7-23).  The
+gate and up weights are stacked into one [2I, H] matrix at load so that one
+product serves both, as the reference's decode path fuses them by kernel
+(src/kernels_cuda/gemv_fused.cu:143-203); stacking rows changes no output.
+"""
+
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from .. import ops
+from ..config.spec import FeedForwardSpec
+from .registry import TensorInfo, register_feed_forward
+
+
+@register_feed_forward("swiglu")
+class SwiGLU:
+    def __init__(self, spec: FeedForwardSpec, dtype: torch.dtype, device):
+        self.spec = spec
+        self.dtype = dtype
+        self.device = device
+        self.gate_up = None
+        self.down = None
+
+    @classmethod
+    def tensor_specs(cls, spec: FeedForwardSpec) -> Dict[str, TensorInfo]:
+        H, I = spec.hidden_size, spec.intermediate_size
+        return {
+            "gate_proj": TensorInfo((I, H), "matrix"),
+            "up_proj": TensorInfo((I, H), "matrix"),
+            "down_proj": TensorInfo((H, I), "matrix"),
+        }
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        def dev(t):
+            return t.to(device=self.device, dtype=self.dtype)
+
+        self.gate_up = torch.cat([dev(tensors["gate_proj"]), dev(tensors["up_proj"])], dim=0).contiguous()
+        self.down = dev(tensors["down_proj"]).contiguous()
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        gu = ops.linear(x, self.gate_up)
+        act = ops.swiglu(gu)
+        return ops.linear(act, self.down, out_dtype=torch.float32)

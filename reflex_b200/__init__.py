@@ -30,3 +30,14 @@ def load_model(model_dir, dtype="bfloat16", device="cuda:0"):
 
     dt = {"bfloat16": torch.bfloat16, "float32": torch.float32}.get(dtype, dtype)
     return _load(model_dir, dt, device)
+
+
+from .sampling.params import SamplingParams  # noqa: E402,F401
+
+
+def __getattr__(name):
+    if name in ("Model", "System1Response", "System1CandidateResult"):
+        from . import api
+
+        return getattr(api, name)
+    raise AttributeError(name)

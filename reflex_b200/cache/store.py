@@ -230,7 +230,10 @@ class Cache:
                 raise ContextOverflow(new_len, self.max_positions)
             for gi, g in enumerate(self.kv_groups):
                 if (new_len + PAGE_TOKENS - 1) // PAGE_TOKENS > g.pages_per_seq:
-                    raise ContextOverflow(new_len, g.pages_per_seq * PAGE_TOKENS)
+                    # within the model's positions, so it is the cache that is too small
+                    raise OutOfMemory(
+                        f"cache is out of pages: one sequence of {new_len} tokens needs more than "
+                        f"the cache's {g.pages_per_seq * PAGE_TOKENS} tokens")
                 need[gi] += g.pages_needed(slot, new_len)
         for gi, g in enumerate(self.kv_groups):
             if need[gi] > g.pool.free_count:

@@ -182,4 +182,4 @@ def write_safetensors(path: str, tensors: Iterable[Tuple[str, torch.Tensor]]) ->
         for _, t in tensors:
             c = t.detach().contiguous().cpu()
             if c.numel():
-                f.write(c.view(torch.uint8).numpy().tobytes())
+                f.write(c.reshape(-1).view(torch.uint8).numpy().tobytes())

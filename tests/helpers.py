@@ -11,18 +11,44 @@ import numpy as np
 import plain_model
 from tiny_configs import ALL
 
-_FOLDERS: Dict[Tuple[str, int, str], str] = {}
+_FOLDERS: Dict[Tuple[str, int, str, float, str], str] = {}
 _PLAIN_CACHE: Dict[Tuple[str, Tuple[int, ...]], np.ndarray] = {}
 
 
-def model_folder(name: str, seed: int = 7, dtype: str = "float32") -> str:
-    """A model folder with random weights in a temporary place (made once)."""
-    from reflex_b200.weights import write_random_model
+def model_folder(name: str, seed: int = 7, dtype: str = "float32", sharp: float = 1.0,
+                 sharp_layers: str = "all") -> str:
+    """A model folder with random weights in a temporary place (made once).
 
-    key = (name, seed, dtype)
+    Random N(0, 0.02) weights give nearly flat attention, which would hide a
+    missing or misplaced key (each key moves the output by about 1/n).  With
+    `sharp` > 1 the per-head q and k norm weights are scaled so that scores
+    spread by about sharp^2 and a few keys dominate each softmax; in all
+    layers, or (`sharp_layers="last"`) in the last layer only.  A peaked
+    softmax multiplies an upstream relative error by about the scores' spread,
+    layer after layer, so rounding noise grows quickly when all layers are
+    sharp: fine in float32, too much in bfloat16, where only the last layer is
+    sharpened."""
+    import torch
+
+    from reflex_b200.weights import SafetensorsFile, write_random_model, write_safetensors
+
+    key = (name, seed, dtype, sharp, sharp_layers)
     if key not in _FOLDERS:
         d = tempfile.mkdtemp(prefix=f"rfx_tiny_{name}_")
         write_random_model(ALL[name], seed, d, dtype)
+        if sharp != 1.0:
+            path = os.path.join(d, "model.safetensors")
+            f = SafetensorsFile(path)
+            tensors = [(k, f.tensor(k).clone()) for k in f.keys()]
+            f.close()
+            last = f"model.layers.{ALL[name]['num_hidden_layers'] - 1}."
+
+            def hit(k):
+                return k.endswith(("q_norm.weight", "k_norm.weight")) and (
+                    sharp_layers == "all" or k.startswith(last))
+
+            tensors = [(k, (t.float() * sharp).to(t.dtype)) if hit(k) else (k, t) for k, t in tensors]
+            write_safetensors(path, tensors)
         _FOLDERS[key] = d
     return _FOLDERS[key]
 

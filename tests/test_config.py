@@ -1,0 +1,123 @@
+"""Configuration and registry (no GPU)."""
+
+import copy
+
+import pytest
+
+from reflex_b200 import CheckpointError, UnsupportedArchitecture
+from reflex_b200 import models  # noqa: F401
+from reflex_b200.config import Qwen3Config, resolve_architecture, spec_from_config_dict
+from tiny_configs import ALL, TINY_A, TINY_B, TINY_C
+
+
+def test_every_size_comes_from_config_json():
+    for name, cfg in ALL.items():
+        typed, spec = spec_from_config_dict(cfg)
+        assert isinstance(typed, Qwen3Config)
+        assert spec.vocab_size == cfg["vocab_size"]
+        assert spec.hidden_size == cfg["hidden_size"]
+        assert len(spec.layers) == cfg["num_hidden_layers"]
+        assert spec.max_positions == cfg["max_position_embeddings"]
+        assert spec.tie_word_embeddings == cfg["tie_word_embeddings"]
+        for layer in spec.layers:
+            m = layer.mixer
+            assert (m.num_heads, m.num_kv_heads, m.head_dim) == (
+                cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"])
+            assert m.scale == pytest.approx(cfg["head_dim"] ** -0.5)
+            assert m.position.theta == cfg["rope_theta"]
+            assert m.position.rotary_dim == cfg["head_dim"]
+            assert m.qk_norm.eps == cfg["rms_norm_eps"] == layer.mixer_norm.eps
+            assert layer.feed_forward.intermediate_size == cfg["intermediate_size"]
+
+
+def test_tiny_configs_differ_in_every_size():
+    keys = ["num_hidden_layers", "hidden_size", "num_attention_heads", "num_key_value_heads",
+            "head_dim", "intermediate_size", "vocab_size", "rope_theta", "rms_norm_eps",
+            "max_position_embeddings"]
+    for k in keys:
+        assert len({TINY_A[k], TINY_B[k], TINY_C[k]}) == 3 or k == "num_key_value_heads", k
+    assert TINY_A["tie_word_embeddings"] != TINY_B["tie_word_embeddings"]
+
+
+def test_registry_both_names_and_unknown():
+    a = resolve_architecture({"architectures": ["Qwen3ForCausalLM"]})
+    b = resolve_architecture({"model_type": "qwen3"})
+    assert a is b
+    with pytest.raises(UnsupportedArchitecture) as e:
+        resolve_architecture({"architectures": ["LlamaForCausalLM"], "model_type": "llama"})
+    assert "LlamaForCausalLM" in str(e.value) and "qwen3" in str(e.value)
+
+
+def test_missing_keys_are_listed_together():
+    cfg = copy.deepcopy(TINY_A)
+    del cfg["rms_norm_eps"], cfg["rope_theta"], cfg["vocab_size"]
+    with pytest.raises(CheckpointError) as e:
+        Qwen3Config.from_dict(cfg)
+    for k in ("rms_norm_eps", "rope_theta", "vocab_size"):
+        assert k in str(e.value)
+
+
+def test_defaults_follow_the_reference():
+    cfg = copy.deepcopy(TINY_A)
+    del cfg["head_dim"], cfg["num_key_value_heads"]
+    c = Qwen3Config.from_dict(cfg)
+    assert c.head_dim == cfg["hidden_size"] // cfg["num_attention_heads"]
+    assert c.num_key_value_heads == cfg["num_attention_heads"]
+
+
+def test_rope_theta_in_rope_parameters():
+    cfg = copy.deepcopy(TINY_A)
+    theta = cfg.pop("rope_theta")
+    cfg["rope_parameters"] = {"rope_theta": theta, "rope_type": "default"}
+    assert Qwen3Config.from_dict(cfg).rope_theta == theta
+
+
+@pytest.mark.parametrize("patch,needle", [
+    ({"rope_scaling": {"rope_type": "yarn", "factor": 4.0}}, "rope_scaling"),
+    ({"rope_parameters": {"rope_theta": 1e4, "rope_type": "linear", "factor": 2.0}}, "rope_scaling"),
+    ({"attention_bias": True}, "attention_bias"),
+    ({"hidden_act": "gelu"}, "hidden_act"),
+    ({"mlp_bias": True}, "mlp_bias"),
+])
+def test_unsupported_options_are_rejected_by_name(patch, needle):
+    cfg = copy.deepcopy(TINY_A)
+    cfg.update(patch)
+    with pytest.raises(UnsupportedArchitecture) as e:
+        Qwen3Config.from_dict(cfg)
+    assert needle in str(e.value)
+
+
+@pytest.mark.parametrize("patch", [
+    {"num_key_value_heads": 3}, {"head_dim": 15}, {"vocab_size": 0}, {"rms_norm_eps": 0.0},
+    {"num_hidden_layers": -1}, {"layer_types": ["full_attention"]},
+])
+def test_bad_values(patch):
+    cfg = copy.deepcopy(TINY_A)
+    cfg.update(patch)
+    with pytest.raises(CheckpointError):
+        Qwen3Config.from_dict(cfg)
+
+
+def test_sliding_layers_from_layer_types_and_from_max_window_layers():
+    _, spec = spec_from_config_dict(TINY_C)
+    assert [l.mixer.window for l in spec.layers] == [None, 37, None, 37]
+    cfg = copy.deepcopy(TINY_C)
+    del cfg["layer_types"]
+    cfg["max_window_layers"] = 3
+    _, spec = spec_from_config_dict(cfg)
+    assert [l.mixer.window for l in spec.layers] == [None, None, None, 37]
+    cfg["use_sliding_window"] = False
+    _, spec = spec_from_config_dict(cfg)
+    assert [l.mixer.window for l in spec.layers] == [None] * 4
+
+
+def test_config_roundtrip():
+    for cfg in ALL.values():
+        c = Qwen3Config.from_dict(cfg)
+        assert Qwen3Config.from_dict(c.to_dict()) == c
+
+
+def test_run_order_defaults_and_cache_entries():
+    _, spec = spec_from_config_dict(TINY_B)
+    assert [(r.layer, r.cache, r.writes_cache) for r in spec.run_order] == [(i, i, True) for i in range(3)]
+    assert spec.cache_entries() == {0: 0, 1: 1, 2: 2}

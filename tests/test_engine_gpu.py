@@ -1,0 +1,186 @@
+"""The engine against the plain implementation, in float32 and in bfloat16:
+each request alone and whole; with the last 32 tokens one by one; in batches of
+unequal lengths whose shorter requests end earlier, one batch after another so
+that slots are used again; long decoding; the first tokens of a sequence.
+
+Errors are measured as max |difference| / max |plain logits|.
+
+Random N(0, 0.02) weights give flat attention, which hides a misplaced key, so
+the tests that are about the cache sharpen the attention (helpers.model_folder).
+A peaked softmax multiplies an upstream relative error by about the spread of
+its scores, in every layer, so rounding noise grows with sharpness and depth:
+float32 runs sharpen every layer by 3 (scores spread by about 9), bfloat16
+runs sharpen only the last layer, since bfloat16's 8 significant bits start
+from 3e-3 per matrix product.
+
+Bounds, with what was measured on a B200 beside them:
+  float32, flat attention         3e-6    (3e-7 .. 7e-7)
+  float32, every layer sharp      1e-3    (1e-5 .. 1.4e-4, growing with the
+      position: the 32-bit rotation angle is off by up to position * 2^-24)
+  bfloat16, flat attention        1.5e-2  (2e-3 .. 7e-3)
+  bfloat16, last layer sharp      4e-2    (see the runs)
+A key read from a wrong place moves a sharpened model's logits by tenths.  On
+the float32 path the logits must moreover be bit-equal however the tokens are
+cut into steps or batched: every kernel there reduces in an order that does not
+depend on the batch, so any difference is a fault of the cache or the batch.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+from tiny_configs import ALL
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 3e-6
+F32_SHARP_TOL = 1e-3
+BF16_TOL = 1.5e-2
+BF16_SHARP_TOL = 4e-2
+
+
+def tol(dtype, sharp=False):
+    if dtype == "float32":
+        return F32_SHARP_TOL if sharp else F32_TOL
+    return BF16_SHARP_TOL if sharp else BF16_TOL
+
+
+def sharp_folder(name, seed, dtype):
+    if dtype == "float32":
+        return helpers.model_folder(name, seed, "float32", sharp=3.0, sharp_layers="all")
+    return helpers.model_folder(name, seed, "bfloat16", sharp=3.0, sharp_layers="last")
+
+
+def stored(dtype):
+    return "float32" if dtype == "float32" else "bfloat16"
+
+
+CASES = [(n, d) for n in ALL for d in ("float32", "bfloat16")]
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_whole_and_tail_one_by_one(name, dtype):
+    V = ALL[name]["vocab_size"]
+    folder = helpers.model_folder(name, 7, stored(dtype))
+    eng = helpers.make_engine(folder, dtype, max_tokens=1024)
+    for n, seed in ((100, 3), (33, 4)):
+        toks = helpers.random_tokens(n, V, seed)
+        ref = helpers.plain_logits(folder, toks)
+        whole = helpers.run_whole(eng, toks)
+        tail = helpers.run_tail_one_by_one(eng, toks, 32)
+        assert whole.shape == ref.shape == tail.shape
+        assert helpers.rel_err(whole, ref) < tol(dtype)
+        assert helpers.rel_err(tail, ref) < tol(dtype)
+        if dtype == "float32":
+            assert np.array_equal(whole, tail), "float32 logits depend on how tokens are cut"
+    assert eng.cache.slots.held_count == 0
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_unequal_batches_early_ends_slot_reuse(name, dtype):
+    V = ALL[name]["vocab_size"]
+    folder = sharp_folder(name, 7, dtype)
+    # fewer slots than requests: batches of 3 follow one another in reused slots
+    eng = helpers.make_engine(folder, dtype, max_tokens=64 * 8, max_slots=3)
+    lengths = (5, 17, 32, 1, 70, 129, 64, 2, 65)
+    reqs = [helpers.random_tokens(n, V, 100 + n) for n in lengths]
+    got = helpers.run_batches(eng, reqs, 3, [5, 17, 20, 1, 64])
+    alone = helpers.make_engine(folder, dtype, max_tokens=64 * 8)
+    for r, g in zip(reqs, got):
+        ref = helpers.plain_logits(folder, r)
+        assert g.shape == ref.shape
+        assert helpers.rel_err(g, ref) < tol(dtype, sharp=True), len(r)
+        if dtype == "float32":
+            assert np.array_equal(g, helpers.run_whole(alone, r)), "batching changed float32 logits"
+    assert eng.cache.slots.held_count == 0
+    assert all(g.pool.held_count == 0 for g in eng.cache.kv_groups)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_over_page_and_window_edges(dtype):
+    """300 tokens one by one on the model with sliding layers (window 37):
+    crosses four page edges; the window group gives pages back under way."""
+    name = "C"
+    V = ALL[name]["vocab_size"]
+    folder = sharp_folder(name, 11, dtype)
+    eng = helpers.make_engine(folder, dtype, max_tokens=512)
+    toks = helpers.random_tokens(300, V, 5)
+    ref = helpers.plain_logits(folder, toks)
+    got = helpers.run_tail_one_by_one(eng, toks, tail=299)
+    err = np.abs(got - ref).max(axis=1) / np.abs(ref).max()
+    assert err.max() < tol(dtype, sharp=True), int(err.argmax())
+    wg = [g for g in eng.cache.kv_groups if g.spec.window]
+    assert wg and wg[0].pool.held_count == 0
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_first_tokens_of_a_sequence(name, dtype):
+    V = ALL[name]["vocab_size"]
+    folder = helpers.model_folder(name, 7, stored(dtype))
+    eng = helpers.make_engine(folder, dtype, max_tokens=256)
+    toks = helpers.random_tokens(4, V, 9)
+    ref = helpers.plain_logits(folder, toks)
+    one = helpers.run_tail_one_by_one(eng, toks, tail=3)  # 1 token, then 1, 1, 1
+    assert helpers.rel_err(one, ref) < tol(dtype)
+    s = eng.open()
+    only_last = eng.step([(s, toks, [3])]).float().cpu().numpy()
+    eng.close(s)
+    assert only_last.shape == (1, V)
+    assert helpers.rel_err(only_last, ref[3:4]) < tol(dtype) * 2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_step_and_no_wanted_logits(dtype):
+    """A step may mix a chunk of one request with one token of another, and
+    may ask for no logits at all (it then only fills the cache)."""
+    name = "B"
+    V = ALL[name]["vocab_size"]
+    folder = sharp_folder(name, 7, dtype)
+    eng = helpers.make_engine(folder, dtype, max_tokens=512)
+    a, b = helpers.random_tokens(90, V, 1), helpers.random_tokens(40, V, 2)
+    sa, sb = eng.open(), eng.open()
+    out = eng.step([(sa, a[:50], []), (sb, b[:39], [])])
+    assert out.shape == (0, V)
+    out = eng.step([(sa, a[50:], list(range(40))), (sb, b[39:], [0])]).float().cpu().numpy()
+    ra, rb = helpers.plain_logits(folder, a), helpers.plain_logits(folder, b)
+    assert helpers.rel_err(out[:40], ra[50:]) < tol(dtype, sharp=True)
+    assert helpers.rel_err(out[40:], rb[39:]) < tol(dtype, sharp=True)
+    eng.close(sa)
+    eng.close(sb)
+
+
+def test_decode_graphs_equal_eager_steps():
+    name = "B"
+    V = ALL[name]["vocab_size"]
+    folder = helpers.model_folder(name, 7, "bfloat16")
+    toks = helpers.random_tokens(80, V, 3)
+    a = helpers.run_tail_one_by_one(helpers.make_engine(folder, "bfloat16", use_graphs=False), toks, 40)
+    eng = helpers.make_engine(folder, "bfloat16", use_graphs=True)
+    b = helpers.run_tail_one_by_one(eng, toks, 40)
+    assert eng._graphs and eng._graphs[1].graph is not None
+    assert np.array_equal(a, b)
+
+
+def test_step_errors_leave_the_cache_as_it_was():
+    from reflex_b200 import ContextOverflow, InvalidInput, OutOfMemory
+
+    folder = helpers.model_folder("A", 7, "float32")
+    eng = helpers.make_engine(folder, "float32", max_tokens=128)
+    s = eng.open()
+    with pytest.raises(InvalidInput):
+        eng.step([(s, [1, 2, 99999], [0])])
+    with pytest.raises(InvalidInput):
+        eng.step([(s, [], [])])
+    with pytest.raises(InvalidInput):
+        eng.step([(s, [1], [1])])
+    with pytest.raises(InvalidInput):
+        eng.step([(s, [1], [0]), (s, [2], [0])])
+    with pytest.raises(OutOfMemory):
+        eng.step([(s, [1] * 200, [0])])
+    with pytest.raises(ContextOverflow):
+        eng.step([(s, [1] * 300, [0])])
+    assert eng.length(s) == 0 and all(g.pool.held_count == 0 for g in eng.cache.kv_groups)
+    out = eng.step([(s, [1, 2, 3], [2])])
+    assert out.shape == (1, 512) and eng.length(s) == 3
+    eng.close(s)

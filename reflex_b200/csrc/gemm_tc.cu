@@ -1,0 +1,328 @@
+// Tensor-core matrix product for the bfloat16 path:  y[r, n] = sum_k x[r, k] W[n, k].
+//
+// The weight matrix is the M operand of tcgen05.mma (tiles of 128 weight rows),
+// the activation rows are its N operand (16 .. 256 rows a tile), so that a
+// decode step's few rows still fill the 128-lane datapath and every weight
+// byte is read from HBM exactly once.  Per CTA: one warp issues TMA tile loads
+// (128-byte swizzle) into a ring of shared-memory stages, one thread issues the
+// MMAs with the accumulator in tensor memory, four warps read the accumulator
+// back and store.  With few weight-row tiles the K dimension is split over a
+// thread-block cluster of up to 8 CTAs so that all SMs stream weights; the
+// partial sums are reduced through distributed shared memory in rank order
+// (no scratch in global memory, no atomics, a fixed summation order).
+//
+// It replaces the reference's warp-per-row f16 GEMV for decode
+// (src/kernels_cuda/gemv_f16.cuh:23-69, gemv_fused.cu) and can stand in for
+// the library product in prefill.  Every wait on an mbarrier is bounded: when
+// it runs out the kernel records where, stops issuing, still frees its tensor
+// memory and returns.
+#include <cooperative_groups.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace {
+
+using namespace sm100;
+
+constexpr int BM = 128;        // weight rows per tile (MMA M)
+constexpr int BK = 64;         // elements along K per stage: 128 bytes of bfloat16
+constexpr int MAX_STAGES = 12;
+constexpr int THREADS = 192;   // warp 0: TMA, warp 1: MMA, warps 2..5: epilogue
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+
+template <int BN>
+struct Shape {
+    static constexpr int B_STAGE_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    static constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+};
+
+template <int BN, typename TO>
+__global__ void __launch_bounds__(THREADS)
+gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               TO* __restrict__ y, int R, int N, int K, int ksplit, int stages,
+               int* __restrict__ err) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
+    __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
+    __shared__ __align__(8) uint64_t tmem_full_bar;
+    __shared__ uint32_t tmem_base_smem;
+    __shared__ int abort_flag;
+
+    using S = Shape<BN>;
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                                ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BM, r0 = blockIdx.y * BN, z = blockIdx.z;
+    const int num_kb = (K + BK - 1) / BK;
+    const int per = (num_kb + ksplit - 1) / ksplit;
+    const int kb0 = z * per;
+    const int nkb = max(0, min(num_kb, kb0 + per) - kb0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&tmem_full_bar, 1);
+        abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 0 && lane == 0) {
+        prefetch_tensormap(&map_w);
+        prefetch_tensormap(&map_x);
+    }
+    if (warp == 1) {
+        tmem_alloc(&tmem_base_smem, S::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_d = tmem_base_smem;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % stages;
+                const uint32_t ph = (i / stages) & 1;
+                if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
+                    atomicExch(err, 1);
+                    abort_flag = 1;
+                    break;
+                }
+                uint8_t* a = tiles + (size_t)s * S::STAGE_BYTES;
+                uint8_t* b = a + A_STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
+                tma_load_2d(a, &map_w, &full_bar[s], (kb0 + i) * BK, n0);
+                tma_load_2d(b, &map_x, &full_bar[s], (kb0 + i) * BK, r0);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (elect_one()) {
+            constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; ++i) {
+                const int s = i % stages;
+                const uint32_t ph = (i / stages) & 1;
+                if (!mbar_wait(&full_bar[s], ph)) {
+                    atomicExch(err, 2);
+                    abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t a = smem_u32(tiles + (size_t)s * S::STAGE_BYTES);
+                const uint64_t da = umma_desc_k_sw128(a);
+                const uint64_t db = umma_desc_k_sw128(a + A_STAGE_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k)  // 32 bytes along K per MMA: +2 in 16-byte units
+                    umma_bf16(tmem_d, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&empty_bar[s]);
+            }
+            if (ok && nkb > 0) umma_commit(&tmem_full_bar);
+        }
+        __syncwarp();
+    } else {
+        const int q = warp & 3;  // this warp may read TMEM lanes [32 q, 32 q + 32)
+        const int m = q * 32 + lane;
+        bool have = nkb > 0;
+        if (have && !mbar_wait(&tmem_full_bar, 0)) {
+            if (lane == 0) atomicExch(err, 3);
+            have = false;
+        }
+        tc_fence_after_sync();
+        float* partial = reinterpret_cast<float*>(tiles);  // [BN][BM], reuses the drained stages
+#pragma unroll 1
+        for (int c = 0; c < BN / 16; ++c) {
+            float v[16];
+            if (have) {
+                tmem_ld_16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 16), v);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+            }
+            if (ksplit == 1) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int r = r0 + c * 16 + j;
+                    if (r < R && n0 + m < N) rfx::st<TO>(y, (size_t)r * N + n0 + m, v[j]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) partial[(c * 16 + j) * BM + m] = v[j];
+            }
+        }
+        tc_fence_before_sync();
+    }
+
+    if (ksplit > 1) {
+        // every CTA of the cluster has its partial tile in shared memory; rank z
+        // sums rows [z BM/ksplit, (z+1) BM/ksplit) over the ranks in rank order
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        float* partial = reinterpret_cast<float*>(tiles);
+        const int mw = BM / ksplit;
+        for (int e = threadIdx.x; e < BN * mw; e += THREADS) {
+            const int rr = e / mw, mm = z * mw + e % mw;
+            float acc = 0.0f;
+            for (int p = 0; p < ksplit; ++p) {
+                const float* remote = cluster.map_shared_rank(partial, p);
+                acc += remote[rr * BM + mm];
+            }
+            const int r = r0 + rr;
+            if (r < R && n0 + mm < N) rfx::st<TO>(y, (size_t)r * N + n0 + mm, acc);
+        }
+        cluster.sync();  // nobody leaves while its shared memory is still read
+    }
+
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_d, S::TMEM_COLS);
+    }
+}
+
+// ---- host side ---------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+                cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// A [rows, cols] row-major bfloat16 matrix, tiles of box_rows x 64 columns,
+// 128-byte swizzle, zero fill outside.
+bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct MapKey {
+    const void* p;
+    int rows, cols, box;
+    bool operator<(const MapKey& o) const {
+        return std::tie(p, rows, cols, box) < std::tie(o.p, o.rows, o.cols, o.box);
+    }
+};
+
+// Weight maps are made once per (pointer, shape); activation maps per call.
+const CUtensorMap* cached_map(const void* base, int rows, int cols, int box_rows) {
+    static std::map<MapKey, CUtensorMap> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    MapKey key{base, rows, cols, box_rows};
+    auto it = cache.find(key);
+    if (it != cache.end()) return &it->second;
+    CUtensorMap m;
+    if (!make_map(&m, base, rows, cols, box_rows)) return nullptr;
+    return &cache.emplace(key, m).first->second;
+}
+
+int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <int BN, typename TO>
+int launch(const void* x, const void* W, void* y, int R, int N, int K, int ksplit_req, int* err,
+           cudaStream_t s) {
+    using S = Shape<BN>;
+    const CUtensorMap* mw = cached_map(W, N, K, BM);
+    CUtensorMap mx;
+    if (!mw || !make_map(&mx, x, R, K, BN)) return RFX_ERR_UNSUPPORTED;
+    const int n_tiles = (N + BM - 1) / BM, r_tiles = (R + BN - 1) / BN;
+    const int num_kb = (K + BK - 1) / BK;
+    // split K over a cluster while there are fewer CTAs than two per SM
+    int ks = 1;
+    if (ksplit_req > 0) {
+        ks = ksplit_req;
+    } else {
+        while (ks < 8 && n_tiles * r_tiles * ks * 2 <= 2 * sm_count() && num_kb >= ks * 4) ks *= 2;
+    }
+    if (ks != 1 && ks != 2 && ks != 4 && ks != 8) return RFX_ERR_BAD_ARG;
+    // two CTAs per SM: at most ~110 KB of stages each
+    int stages = (110 * 1024) / S::STAGE_BYTES;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages < 2) stages = 2;
+    if (ks > 1 && stages * S::STAGE_BYTES < BN * BM * 4) return RFX_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)stages * S::STAGE_BYTES + 1024;
+    auto kernel = gemm_wt_kernel<BN, TO>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_tiles, r_tiles, ks);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = ks;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, kernel, *mw, mx, (TO*)y, R, N, K, ks, stages, err);
+    if (e != cudaSuccess) return (int)e;
+    return 0;
+}
+
+template <typename TO>
+int dispatch(const void* x, const void* W, void* y, int R, int N, int K, int ksplit, int* err,
+             cudaStream_t s) {
+    if (R <= 16) return launch<16, TO>(x, W, y, R, N, K, ksplit, err, s);
+    if (R <= 32) return launch<32, TO>(x, W, y, R, N, K, ksplit, err, s);
+    if (R <= 64) return launch<64, TO>(x, W, y, R, N, K, ksplit, err, s);
+    return launch<128, TO>(x, W, y, R, N, K, ksplit, err, s);
+}
+
+}  // namespace
+
+// y [R, N] = x [R, K] . W [N, K]^T, bfloat16 inputs, float32 accumulation,
+// y float32 or bfloat16.  K must be a multiple of 8 and the pointers 16-byte
+// aligned (TMA).  ksplit: 0 = choose, else 1, 2, 4 or 8.  `err` is a device
+// word that receives a non-zero code if a bounded wait ran out.
+extern "C" int rfx_gemm_bf16_tc(const void* x, const void* W, void* y, int y_dt, int R, int N,
+                                int K, int ksplit, int* err, void* stream) {
+    if (R <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0) return RFX_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(W)) & 15) return RFX_ERR_BAD_ARG;
+    if ((N + BM - 1) / BM > 2147483647 || (R + 127) / 128 > 65535) return RFX_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (y_dt == RFX_DT_F32) return dispatch<float>(x, W, y, R, N, K, ksplit, err, s);
+    if (y_dt == RFX_DT_BF16) return dispatch<__nv_bfloat16>(x, W, y, R, N, K, ksplit, err, s);
+    return RFX_ERR_BAD_ARG;
+}

@@ -26,6 +26,7 @@ class DecodeGraph:
         self.graph = None
         self.logits = None
         self.calls = 0
+        self.kernels = 0
 
     def run(self, tokens, slots, starts, want) -> torch.Tensor:
         eng = self.engine
@@ -37,8 +38,12 @@ class DecodeGraph:
             # capture: the eager call above has already sized every lazy buffer
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
+            from .. import ops
+
+            before = ops.launch_count()
             with torch.cuda.graph(g):
                 self.logits = eng.model.forward(batch, eng.cache)
+            self.kernels = ops.launch_count() - before  # this library's kernels in the graph
             self.graph = g
         self.graph.replay()
         return self.logits

@@ -109,3 +109,9 @@ class Engine:
             g = DecodeGraph(self, n)
             self._graphs[n] = g
         return g.run(tokens, slots, starts, want)
+
+    def launches_per_decode_step(self, n_seqs: int) -> int:
+        """This library's kernels in one decode step of `n_seqs` sequences
+        (counted when the step's graph was captured; 0 if it never ran)."""
+        g = self._graphs.get(n_seqs)
+        return g.kernels if g is not None else 0

@@ -18,6 +18,12 @@ from . import native
 F32, BF16 = 0, 1
 
 
+def launch_count() -> int:
+    """Kernels of this library launched directly so far (graph replays are
+    counted by the engine, which knows how many a captured step holds)."""
+    return native.LAUNCHES
+
+
 def dt_code(dtype: torch.dtype) -> int:
     if dtype == torch.float32:
         return F32
@@ -98,7 +104,40 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
 
 
 # -------------------------------------------------------------------- linear
-GEMV_MAX_ROWS = 16
+GEMV_MAX_ROWS = 64  # up to here the weight-streaming tensor-core kernel runs
+
+_ERR = {}
+
+
+def device_error_word(device) -> torch.Tensor:
+    """One int32 word per device that kernels with bounded waits set to a
+    non-zero code when a wait ran out."""
+    key = torch.device(device).index or 0
+    if key not in _ERR:
+        _ERR[key] = torch.zeros((1,), dtype=torch.int32, device=device)
+    return _ERR[key]
+
+
+def check_device_errors(device="cuda:0") -> None:
+    """Synchronises; raises if a kernel reported that a bounded wait ran out."""
+    code = int(device_error_word(device).item())
+    if code:
+        device_error_word(device).zero_()
+        raise CudaError(f"a kernel gave up a bounded wait (code {code}); its results are not valid")
+
+
+def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.float32,
+            ksplit: int = 0) -> torch.Tensor:
+    """The tcgen05/TMA product y = x @ weight.T (bfloat16 in, float32 accumulate)."""
+    R, K = x.shape
+    N = weight.shape[0]
+    _chk(x, "x", torch.bfloat16)
+    _chk(weight, "weight", torch.bfloat16)
+    y = torch.empty((R, N), dtype=out_dtype, device=x.device)
+    st = native.lib().rfx_gemm_bf16_tc(x.data_ptr(), weight.data_ptr(), y.data_ptr(), dt_code(out_dtype),
+                                       R, N, K, ksplit, device_error_word(x.device).data_ptr(), _stream())
+    native.check(st, f"gemm_bf16_tc (R={R}, N={N}, K={K})")
+    return y
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -106,9 +145,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
 
     float32: this library's own CUDA-core product (no reduced-precision matrix
     mode; each output element reduced over k in index order).
-    bfloat16: the weight-streaming kernel for a few rows, the library matrix
-    product (cuBLAS, 32-bit accumulation) above that, where the reference uses
-    a library product too (src/model/kernels.rs:2518-2561)."""
+    bfloat16: the weight-streaming tcgen05 kernel for up to GEMV_MAX_ROWS rows
+    (decode), the library matrix product (cuBLAS, 32-bit accumulation) above
+    that, where the reference uses a library product too
+    (src/model/kernels.rs:2518-2561)."""
     R, K = x.shape
     N, K2 = weight.shape
     if K != K2:
@@ -124,11 +164,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
         return y
     out_dtype = out_dtype or torch.bfloat16
     if R <= GEMV_MAX_ROWS and K % 8 == 0:
-        y = torch.empty((R, N), dtype=out_dtype, device=x.device)
-        st = native.lib().rfx_gemv_bf16(x.data_ptr(), weight.data_ptr(), y.data_ptr(),
-                                        dt_code(out_dtype), R, N, K, _stream())
-        native.check(st, f"gemv_bf16 (R={R}, N={N}, K={K})")
-        return y
+        return gemm_tc(x, weight, out_dtype)
     if out_dtype == torch.float32:
         return torch.mm(x, weight.t(), out_dtype=torch.float32)
     return torch.mm(x, weight.t())
@@ -170,6 +206,18 @@ def attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         out.data_ptr(), R, nq, nkv, head_dim, int(window or 0), float(scale), _stream())
     native.check(st, f"attention_plain (head_dim={head_dim})")
     return out
+
+
+def gemv_simple(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """The plain CUDA-core bfloat16 product (one warp per output column); kept
+    as the readable counterpart of `gemm_tc` for tests."""
+    R, K = x.shape
+    N = weight.shape[0]
+    y = torch.empty((R, N), dtype=out_dtype, device=x.device)
+    st = native.lib().rfx_gemv_bf16(_chk(x, "x", torch.bfloat16), _chk(weight, "weight", torch.bfloat16),
+                                    y.data_ptr(), dt_code(out_dtype), R, N, K, _stream())
+    native.check(st, f"gemv_bf16 (R={R}, N={N}, K={K})")
+    return y
 
 
 def attention(q, k_pages, v_pages, page_table, page_size, batch, nq, nkv, head_dim, window, scale):

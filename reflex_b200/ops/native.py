@@ -27,6 +27,7 @@ _SIGNATURES = {
     "rfx_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "rfx_add": [c_void_p, c_void_p, c_int, c_longlong, c_void_p],
     "rfx_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "rfx_gemm_bf16_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "rfx_gemv_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "rfx_qkv_post": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p, c_int,
                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
@@ -75,7 +76,12 @@ def register_signature(name: str, argtypes) -> None:
         fn.restype = c_int
 
 
+LAUNCHES = 0  # kernels of this library launched (or captured into a graph) so far
+
+
 def check(status: int, what: str) -> None:
+    global LAUNCHES
+    LAUNCHES += 1
     if status != 0:
         msg = lib().rfx_error_string(status).decode("utf-8", "replace")
         raise CudaError(f"{what} failed: {msg} (status {status})")

@@ -1,0 +1,227 @@
+// Decode attention on tensor cores: one query position per row, split over
+// the keys.
+//
+// A CTA serves one (row, kv head, tile of up to 16 query heads of that kv
+// head's group, split of the key range).  The query heads that share the kv
+// head are the 16 rows of the MMA tile, so each K/V page is read once for the
+// whole group (the reference's decode kernel does the same with CUDA cores:
+// src/kernels_cuda/attention_decode.cuh:34-176).  Pages of 64 keys stream
+// through a double-buffered pair of shared-memory tiles; warp w takes keys
+// [16 w, 16 w + 16) of every page with its own running (max, sum, acc), and
+// the four warps are merged at the end.  With more than one split the CTA
+// writes an unnormalised partial (acc, max, sum) to scratch and a second
+// kernel combines the splits in split order
+// (src/kernels_cuda/attention_online.cu:51-78).  Softmax runs in 32-bit on
+// base-2 exponentials: p = 2^((s - m) * scale * log2 e).
+#include "attn_mma.cuh"
+#include "common.cuh"
+#include "paged.cuh"
+
+namespace {
+
+using namespace attn;
+using rfx::PagedKV;
+
+constexpr int PAGE = 64;
+constexpr int DEC_THREADS = 128;
+
+template <int D>
+__global__ void __launch_bounds__(DEC_THREADS)
+attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
+                        const __nv_bfloat16* __restrict__ v_pages, PagedKV cache,
+                        const int* __restrict__ row_pos, const int* __restrict__ row_slot,
+                        __nv_bfloat16* __restrict__ out, float* __restrict__ partial, int nq,
+                        int n_htiles, int n_splits, int window, float scale_log2) {
+    constexpr int LD = D + 8;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [16][LD]
+    __nv_bfloat16* kbuf = qs + 16 * LD;                               // [2][PAGE][LD]
+    __nv_bfloat16* vbuf = kbuf + 2 * PAGE * LD;                       // [2][PAGE][LD]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int r = blockIdx.x;
+    const int kvh = blockIdx.y / n_htiles, ht = blockIdx.y % n_htiles;
+    const int split = blockIdx.z;
+    const int g = nq / cache.n_kv_heads;
+    const int h0 = kvh * g + ht * 16;
+    const int nh = min(16, g - ht * 16);
+    const int pos = row_pos[r], slot = row_slot[r];
+    const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+    const int first_page = lo / PAGE, last_page = pos / PAGE;
+    const int n_pg = last_page - first_page + 1;
+    const int pps = (n_pg + n_splits - 1) / n_splits;
+    const int pg0 = first_page + split * pps;
+    const int pg1 = min(last_page + 1, pg0 + pps);
+
+    // the query heads of this tile; rows beyond the group are zero
+    for (int i = tid; i < 16 * (D / 8); i += DEC_THREADS) {
+        const int row = i / (D / 8), c = i % (D / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < nh) v = *reinterpret_cast<const uint4*>(q + ((size_t)r * nq + h0 + row) * D + c * 8);
+        *reinterpret_cast<uint4*>(qs + row * LD + c * 8) = v;
+    }
+
+    const int* table = cache.page_table + (size_t)slot * cache.max_pages;
+    auto issue = [&](int pg, int buf) {
+        const int page = table[pg];
+        const size_t off = ((size_t)page * cache.n_kv_heads + kvh) * PAGE * D;
+        const int valid = min(PAGE, pos + 1 - pg * PAGE);
+        load_tile_async<D>(kbuf + buf * PAGE * LD, k_pages + off, PAGE, valid, tid, DEC_THREADS);
+        load_tile_async<D>(vbuf + buf * PAGE * LD, v_pages + off, PAGE, valid, tid, DEC_THREADS);
+        cp_async_commit();
+    };
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    float acc[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
+
+    if (pg0 < pg1) issue(pg0, 0);
+    for (int pg = pg0; pg < pg1; ++pg) {
+        const int buf = (pg - pg0) & 1;
+        if (pg + 1 < pg1) {
+            issue(pg + 1, buf ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int base = pg * PAGE;
+        auto visible = [&](int key, int) { return base + key >= lo && base + key <= pos; };
+        attend_tile<D, 2>(qs, kbuf + buf * PAGE * LD, vbuf + buf * PAGE * LD, warp * 16, scale_log2,
+                          visible, m, l, acc);
+        __syncthreads();  // the buffer is free for the load after next
+    }
+    if (pg0 >= pg1) __syncthreads();  // the query tile writes above
+
+    // merge the four warps: each holds (m, l, acc) over its quarter of the keys
+    float* red = reinterpret_cast<float*>(kbuf);       // [4][16][D] acc, then [4][16] m, [4][16] l
+    float* red_m = red + 4 * 16 * D;
+    float* red_l = red_m + 4 * 16;
+    {
+        const int g0 = lane >> 2, c = lane & 3;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            float* a0 = red + ((size_t)(warp * 16 + g0) * D) + n * 8 + 2 * c;
+            float* a1 = red + ((size_t)(warp * 16 + g0 + 8) * D) + n * 8 + 2 * c;
+            a0[0] = acc[n][0];
+            a0[1] = acc[n][1];
+            a1[0] = acc[n][2];
+            a1[1] = acc[n][3];
+        }
+        if (c == 0) {
+            red_m[warp * 16 + g0] = m[0];
+            red_m[warp * 16 + g0 + 8] = m[1];
+            red_l[warp * 16 + g0] = l[0];
+            red_l[warp * 16 + g0 + 8] = l[1];
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < nh * D; i += DEC_THREADS) {
+        const int row = i / D, e = i % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, red_m[w * 16 + row]);
+        float L = 0.0f, A = 0.0f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float f = exp2f(red_m[w * 16 + row] - M);
+                L += red_l[w * 16 + row] * f;
+                A += red[(size_t)(w * 16 + row) * D + e] * f;
+            }
+        }
+        const size_t head = (size_t)r * nq + h0 + row;
+        if (n_splits == 1) {
+            out[head * D + e] = __float2bfloat16_rn(A / L);
+        } else {
+            float* p = partial + (head * n_splits + split) * (D + 2);
+            p[e] = A;
+            if (e == 0) {
+                p[D] = M;
+                p[D + 1] = L;
+            }
+        }
+    }
+}
+
+// out[head] = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in order
+__global__ void attention_combine_kernel(const float* __restrict__ partial,
+                                         __nv_bfloat16* __restrict__ out, int D, int n_splits) {
+    const size_t head = blockIdx.x;
+    const float* p = partial + head * n_splits * (D + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, p[s * (D + 2) + D]);
+    float L = 0.0f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = p[s * (D + 2) + D];
+        if (ms != -INFINITY) L += p[s * (D + 2) + D + 1] * exp2f(ms - M);
+    }
+    for (int e = threadIdx.x; e < D; e += blockDim.x) {
+        float A = 0.0f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = p[s * (D + 2) + D];
+            if (ms != -INFINITY) A += p[s * (D + 2) + e] * exp2f(ms - M);
+        }
+        out[head * D + e] = __float2bfloat16_rn(A / L);
+    }
+}
+
+template <int D>
+int launch_decode(const void* q, const void* k_pages, const void* v_pages, const PagedKV& cache,
+                  const int* row_pos, const int* row_slot, void* out, float* partial, int R, int nq,
+                  int n_splits, int window, float scale, cudaStream_t s) {
+    constexpr int LD = D + 8;
+    const int g = nq / cache.n_kv_heads;
+    const int n_htiles = (g + 15) / 16;
+    size_t smem = (size_t)(16 + 4 * PAGE) * LD * 2;
+    const size_t red = (size_t)(4 * 16 * D + 2 * 4 * 16) * 4;
+    if (red > (size_t)4 * PAGE * LD * 2) return RFX_ERR_UNSUPPORTED;
+    auto kernel = attention_decode_kernel<D>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid(R, cache.n_kv_heads * n_htiles, n_splits);
+    kernel<<<grid, DEC_THREADS, smem, s>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, cache,
+        row_pos, row_slot, (__nv_bfloat16*)out, partial, nq, n_htiles, n_splits, window,
+        scale * 1.4426950408889634f);
+    RFX_CHECK_LAUNCH();
+    if (n_splits > 1) {
+        attention_combine_kernel<<<R * nq, D <= 128 ? 64 : 128, 0, s>>>(partial, (__nv_bfloat16*)out,
+                                                                         D, n_splits);
+        RFX_CHECK_LAUNCH();
+    }
+    return 0;
+}
+
+}  // namespace
+
+// bfloat16 q [R, nq, D], paged K/V, one query position per row.  `partial` is
+// scratch of R * nq * n_splits * (D + 2) floats, needed when n_splits > 1.
+// head_dim: multiples of 16 up to 256; the page size must be 64.
+extern "C" int rfx_attention_decode(const void* q, const void* k_pages, const void* v_pages,
+                                    const int* page_table, int max_pages, int page_size,
+                                    const int* row_pos, const int* row_slot, void* out,
+                                    float* partial, int R, int nq, int nkv, int head_dim,
+                                    int n_splits, int window, float scale, void* stream) {
+    if (R <= 0) return 0;
+    if (page_size != PAGE || nkv <= 0 || nq % nkv != 0 || n_splits < 1) return RFX_ERR_BAD_ARG;
+    if (n_splits > 1 && !partial) return RFX_ERR_BAD_ARG;
+    if (n_splits > 65535 || (long long)nkv * ((nq / nkv + 15) / 16) > 65535) return RFX_ERR_UNSUPPORTED;
+    PagedKV cache{page_table, max_pages, page_size, nkv, head_dim};
+    cudaStream_t s = (cudaStream_t)stream;
+#define RFX_CASE(DD)                                                                            \
+    case DD:                                                                                    \
+        return launch_decode<DD>(q, k_pages, v_pages, cache, row_pos, row_slot, out, partial, R, \
+                                 nq, n_splits, window, scale, s);
+    switch (head_dim) {
+        RFX_CASE(16) RFX_CASE(32) RFX_CASE(48) RFX_CASE(64) RFX_CASE(80) RFX_CASE(96)
+        RFX_CASE(112) RFX_CASE(128) RFX_CASE(144) RFX_CASE(160) RFX_CASE(176) RFX_CASE(192)
+        RFX_CASE(208) RFX_CASE(224) RFX_CASE(240) RFX_CASE(256)
+        default:
+            return RFX_ERR_UNSUPPORTED;
+    }
+#undef RFX_CASE
+}

@@ -220,9 +220,46 @@ def gemv_simple(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = 
     return y
 
 
+SM_COUNT = 148
+DECODE_MAX_SPLITS = 16
+
+
+def decode_splits(n_rows: int, nq: int, nkv: int) -> int:
+    """Key-range splits of the decode kernel: enough CTAs for two per SM.  It
+    depends on the batch size only, so a captured decode step stays valid while
+    contexts grow."""
+    ctas = n_rows * nkv * ((nq // nkv + 15) // 16)
+    return max(1, min(DECODE_MAX_SPLITS, -(-2 * SM_COUNT // ctas)))
+
+
+def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_slot, nq, nkv,
+                     head_dim, window, scale, n_splits: Optional[int] = None) -> torch.Tensor:
+    """bfloat16 tensor-core attention for rows that are each one query
+    position (decode), split over the keys."""
+    R = q.shape[0]
+    _chk(q, "q", torch.bfloat16)
+    if head_dim % 16 or not (16 <= head_dim <= 256):
+        raise InvalidInput(f"attention_decode takes head_dim in steps of 16 up to 256, got {head_dim}")
+    n_splits = n_splits or decode_splits(R, nq, nkv)
+    out = torch.empty_like(q)
+    partial = (torch.empty((R * nq * n_splits * (head_dim + 2),), dtype=torch.float32, device=q.device)
+               if n_splits > 1 else None)
+    st = native.lib().rfx_attention_decode(
+        q.data_ptr(), _chk(k_pages, "k_pages", torch.bfloat16), _chk(v_pages, "v_pages", torch.bfloat16),
+        _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
+        _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32), out.data_ptr(),
+        partial.data_ptr() if partial is not None else 0, R, nq, nkv, head_dim, n_splits,
+        int(window or 0), float(scale), _stream())
+    native.check(st, f"attention_decode (head_dim={head_dim}, splits={n_splits})")
+    return out
+
+
 def attention(q, k_pages, v_pages, page_table, page_size, batch, nq, nkv, head_dim, window, scale):
     """Attention of the step's rows over their sequences' cached keys and
     values; picks the kernel for the dtype and the kind of step."""
+    if q.dtype == torch.bfloat16 and batch.is_decode and head_dim % 16 == 0 and head_dim <= 256:
+        return attention_decode(q, k_pages, v_pages, page_table, page_size, batch.row_pos,
+                                batch.row_slot, nq, nkv, head_dim, window, scale)
     return attention_plain(q, k_pages, v_pages, page_table, page_size, batch.row_pos,
                            batch.row_slot, nq, nkv, head_dim, window, scale)
 

@@ -34,6 +34,8 @@ _SIGNATURES = {
                      c_int, c_int, c_int, c_int, c_int, c_void_p],
     "rfx_attention_plain": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "rfx_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "rfx_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
     "rfx_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                    c_void_p, c_void_p, c_void_p],

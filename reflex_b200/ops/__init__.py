@@ -254,12 +254,38 @@ def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_sl
     return out
 
 
+def attention_prefill(q, k_pages, v_pages, page_table, page_size, seq_slot, seq_start, seq_new,
+                      seq_row0, max_new: int, nq, nkv, head_dim, window, scale) -> torch.Tensor:
+    """bfloat16 tensor-core attention for a packed batch of sequences that
+    each bring one or more rows (prefill, chunks, mixed steps)."""
+    _chk(q, "q", torch.bfloat16)
+    if head_dim % 16 or not (16 <= head_dim <= 256):
+        raise InvalidInput(f"attention_prefill takes head_dim in steps of 16 up to 256, got {head_dim}")
+    if nq // nkv > 128:
+        raise InvalidInput(f"attention_prefill takes up to 128 query heads per kv head, got {nq // nkv}")
+    out = torch.empty_like(q)
+    S = seq_slot.numel()
+    st = native.lib().rfx_attention_prefill(
+        q.data_ptr(), _chk(k_pages, "k_pages", torch.bfloat16), _chk(v_pages, "v_pages", torch.bfloat16),
+        _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
+        _chk(seq_slot, "seq_slot", torch.int32), _chk(seq_start, "seq_start", torch.int32),
+        _chk(seq_new, "seq_new", torch.int32), _chk(seq_row0, "seq_row0", torch.int32), out.data_ptr(),
+        S, int(max_new), nq, nkv, head_dim, int(window or 0), float(scale), _stream())
+    native.check(st, f"attention_prefill (head_dim={head_dim})")
+    return out
+
+
 def attention(q, k_pages, v_pages, page_table, page_size, batch, nq, nkv, head_dim, window, scale):
     """Attention of the step's rows over their sequences' cached keys and
     values; picks the kernel for the dtype and the kind of step."""
-    if q.dtype == torch.bfloat16 and batch.is_decode and head_dim % 16 == 0 and head_dim <= 256:
+    fast = q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256
+    if fast and batch.is_decode:
         return attention_decode(q, k_pages, v_pages, page_table, page_size, batch.row_pos,
                                 batch.row_slot, nq, nkv, head_dim, window, scale)
+    if fast and nq // nkv <= 128:
+        return attention_prefill(q, k_pages, v_pages, page_table, page_size, batch.seq_slot,
+                                 batch.seq_start, batch.seq_new, batch.seq_row0, batch.max_new, nq,
+                                 nkv, head_dim, window, scale)
     return attention_plain(q, k_pages, v_pages, page_table, page_size, batch.row_pos,
                            batch.row_slot, nq, nkv, head_dim, window, scale)
 

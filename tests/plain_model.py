@@ -80,20 +80,21 @@ def rope_neox(t: np.ndarray, positions: np.ndarray, theta_base: float, rotary_di
 
 
 def causal_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float,
-                     window: Optional[int]) -> np.ndarray:
+                     window: Optional[int], first_row: int = 0) -> np.ndarray:
     """q: [T, nq, d], k, v: [T, nkv, d] of one whole sequence.  Query i of head h
     reads kv head h // (nq/nkv) (src/kernels_cuda/attention_online.cuh:56) and
     keys j <= i, with a window only those with i - j < window
     (src/model/config.rs:1184-1185); s_j = (q . k_j) * scale, softmax with the
     maximum subtracted, out = sum_j p_j v_j
-    (plain form: src/kernels_cuda/attention.cu:36-74)."""
+    (plain form: src/kernels_cuda/attention.cu:36-74).  Rows before `first_row`
+    are left zero (tests that need only a sequence's last rows skip the rest)."""
     T, nq, d = q.shape
     nkv = k.shape[1]
     g = nq // nkv
     out = np.zeros_like(q)
     for h in range(nq):
         kh = h // g
-        for i in range(T):
+        for i in range(first_row, T):
             lo = 0 if not window else max(0, i - window + 1)
             s = (k[lo:i + 1, kh, :] @ q[i, h, :]) * scale
             p = np.exp(s - s.max())

@@ -1,0 +1,358 @@
+"""Each kernel alone against a plain float64 reference of the same op, at sizes
+other than the engine's tiny models (and at the benchmark's head shapes).
+References are the plain implementation's functions or one-line NumPy/torch
+formulas; inputs are made so that faults show (a far key that dominates, keys
+at a window's edge, scrambled page tables, stale data in unused cache rows)."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model as pm
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ops():
+    from reflex_b200 import ops as o
+
+    return o
+
+
+def relerr(got, ref):
+    got = got.double().cpu().numpy() if isinstance(got, torch.Tensor) else np.asarray(got, dtype=np.float64)
+    return float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+# ------------------------------------------------------------------ elementwise
+@pytest.mark.parametrize("R,H", [(1, 64), (3, 100), (5, 4096), (2, 5120), (4, 24)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_with_add_gather_and_offset(R, H, out_dtype):
+    g = torch.Generator().manual_seed(R * 1000 + H)
+    x = torch.randn(R, H, generator=g) * 3
+    d = torch.randn(R, H, generator=g)
+    w = 1 + 0.1 * torch.randn(H, generator=g)
+    eps = 1e-5
+    tol = 2e-6 if out_dtype == torch.float32 else 5e-3
+    xd = x.to(DEV)
+    out = ops().rmsnorm(xd, w.to(DEV), eps, out_dtype)
+    assert relerr(out, pm.rms_norm(x.double().numpy(), w.double().numpy(), eps)) < tol
+    # fused residual add: the residual is updated in place, in 32-bit
+    for delta in (d.to(DEV), d.to(DEV).bfloat16()):
+        xd = x.to(DEV).clone()
+        out = ops().rmsnorm(xd, w.to(DEV), eps, out_dtype, delta=delta)
+        t = x.double().numpy() + delta.double().cpu().numpy()
+        assert relerr(xd, t) < 1e-6
+        assert relerr(out, pm.rms_norm(t, w.double().numpy(), eps)) < tol
+    # gathered rows, residual untouched, and the (1 + w) variant
+    rows = torch.tensor([R - 1, 0], dtype=torch.int32, device=DEV)
+    xd = x.to(DEV).clone()
+    out = ops().rmsnorm(xd, w.to(DEV), eps, out_dtype, delta=d.to(DEV), rows=rows, weight_offset=1.0)
+    t = (x + d).double().numpy()[[R - 1, 0]]
+    assert relerr(out, pm.rms_norm(t, 1.0 + w.double().numpy(), eps)) < tol
+    assert torch.equal(xd.cpu(), x)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_embed_add(dtype):
+    g = torch.Generator().manual_seed(1)
+    gu = (torch.randn(7, 2 * 333, generator=g) * 3).to(dtype)
+    out = ops().swiglu(gu.to(DEV))
+    a, b = gu[:, :333].double().numpy(), gu[:, 333:].double().numpy()
+    assert relerr(out, a / (1 + np.exp(-a)) * b) < (1e-6 if dtype == torch.float32 else 5e-3)
+    table = torch.randn(1000, 96, generator=g).to(dtype)
+    ids = torch.tensor([999, 0, 17, 17, 500], dtype=torch.int32)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    e = ops().embed(table.to(DEV), ids.to(DEV), 2.0, flag)
+    assert e.dtype == torch.float32
+    assert torch.equal(e.cpu(), table[ids.long()].float() * 2.0)
+    assert int(flag.item()) == 0
+    ops().embed(table.to(DEV), torch.tensor([3, 1000], dtype=torch.int32, device=DEV), 1.0, flag)
+    assert int(flag.item()) == 2  # 1 + the row of the bad id
+    acc = torch.randn(5, 77, generator=g)
+    d = torch.randn(5, 77, generator=g).to(dtype)
+    got = ops().add_(acc.to(DEV).clone(), d.to(DEV))
+    assert relerr(got, acc.double().numpy() + d.double().numpy()) < 1e-6
+
+
+# ----------------------------------------------------------------------- linear
+@pytest.mark.parametrize("R,N,K", [(1, 7, 5), (3, 1000, 96), (65, 130, 257), (200, 64, 1024), (16, 6144, 512)])
+def test_gemm_f32_is_exact_to_rounding_and_row_independent(R, N, K):
+    g = torch.Generator().manual_seed(R + N + K)
+    x = torch.randn(R, K, generator=g)
+    w = torch.randn(N, K, generator=g) * 0.05
+    y = ops().linear(x.to(DEV), w.to(DEV))
+    ref = x.double().numpy() @ w.double().numpy().T
+    assert relerr(y, ref) < 5e-7 * math.sqrt(K)
+    # a row's result must not depend on what else is in the batch: bit-equal alone
+    alone = ops().linear(x[R // 2:R // 2 + 1].to(DEV).contiguous(), w.to(DEV))
+    assert torch.equal(alone[0], y[R // 2])
+
+
+@pytest.mark.parametrize("R,N,K", [(1, 128, 64), (5, 1000, 96), (8, 4096, 4096), (33, 6144, 4096),
+                                   (64, 777, 80), (17, 151936, 512), (2, 4096, 12288)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_tc_any_shape(R, N, K, out_dtype):
+    g = torch.Generator().manual_seed(R + N + K)
+    x = torch.randn(R, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    ref = (x.double() @ w.double().T).numpy()
+    tol = 2e-6 * math.sqrt(K) if out_dtype == torch.float32 else 5e-3
+    for ks in (0, 1, 2, 4, 8):
+        if ks > 1 and (K + 63) // 64 < ks:
+            continue
+        y = ops().gemm_tc(x.to(DEV), w.to(DEV), out_dtype, ksplit=ks)
+        assert relerr(y, ref) < tol, ks
+    ops().check_device_errors(DEV)
+    simple = ops().gemv_simple(x.to(DEV), w.to(DEV), out_dtype)
+    assert relerr(simple, ref) < tol
+
+
+def test_gemm_tc_refuses_what_it_cannot_do():
+    from reflex_b200 import CudaError
+
+    x = torch.zeros(2, 100, dtype=torch.bfloat16, device=DEV)  # K = 100 is no multiple of 8
+    w = torch.zeros(16, 100, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(CudaError) as e:
+        ops().gemm_tc(x, w)
+    assert "not supported" in str(e.value)
+
+
+# ------------------------------------------------------------------- qkv_post
+@pytest.mark.parametrize("nq,nkv,d,rd,theta", [(4, 2, 16, 16, 1e4), (6, 1, 32, 32, 1e6), (3, 1, 48, 32, 5e4),
+                                               (32, 8, 128, 128, 1e6), (2, 2, 256, 64, 1e4)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_qkv_post_norm_rope_cache(nq, nkv, d, rd, theta, dtype):
+    g = torch.Generator().manual_seed(nq * d)
+    R = 6
+    positions = [0, 1, 63, 64, 200, 3000]
+    slots = [2, 0, 1, 2, 0, 1]
+    n_pages, max_pages = 64, 50
+    table = torch.randperm(n_pages * 3, generator=g)[: 3 * max_pages].reshape(3, max_pages).int() % n_pages
+    # make the (slot, page index) pairs that are used distinct pages
+    used = {}
+    for s, p in zip(slots, positions):
+        used[(s, p // 64)] = len(used)
+    for (s, pi), page in used.items():
+        table[s, pi] = page
+    qkv = torch.randn(R, (nq + 2 * nkv) * d, generator=g) * 2
+    qw = 1 + 0.1 * torch.randn(d, generator=g)
+    kw = 1 + 0.1 * torch.randn(d, generator=g)
+    eps = 1e-6
+    k_pages = torch.full((n_pages, nkv, 64, d), 7.0, dtype=dtype, device=DEV)
+    v_pages = torch.full((n_pages, nkv, 64, d), 7.0, dtype=dtype, device=DEV)
+    denom = torch.pow(torch.tensor(theta, dtype=torch.float64), torch.arange(rd // 2, dtype=torch.float64) * 2 / rd)
+    q = ops().qkv_post(qkv.to(DEV), qw.to(DEV), kw.to(DEV), eps, 0.0, denom.float().to(DEV), rd,
+                       torch.tensor(positions, dtype=torch.int32, device=DEV),
+                       torch.tensor(slots, dtype=torch.int32, device=DEV), k_pages, v_pages, table.to(DEV), 64,
+                       nq, nkv, d, True, dtype)
+    x = qkv.double().numpy()
+    pos = np.array(positions)
+    qr = pm.rope_neox(pm.rms_norm(x[:, : nq * d].reshape(R, nq, d), qw.double().numpy(), eps), pos, theta, rd)
+    kr = pm.rope_neox(pm.rms_norm(x[:, nq * d:(nq + nkv) * d].reshape(R, nkv, d), kw.double().numpy(), eps), pos, theta, rd)
+    vr = x[:, (nq + nkv) * d:].reshape(R, nkv, d)
+    # 32-bit angles are off by up to position * 2^-24 against double
+    tol = 5e-4 if dtype == torch.float32 else 8e-3
+    assert relerr(q.reshape(R, nq, d), qr) < tol
+    for i, (s, p) in enumerate(zip(slots, positions)):
+        page = int(table[s, p // 64])
+        assert relerr(k_pages[page, :, p % 64, :], kr[i]) < tol
+        assert relerr(v_pages[page, :, p % 64, :], vr[i]) < (1e-6 if dtype == torch.float32 else 5e-3)
+    # nothing else in the cache was touched
+    touched = torch.zeros(n_pages, 64, dtype=torch.bool)
+    for s, p in zip(slots, positions):
+        touched[int(table[s, p // 64]), p % 64] = True
+    untouched = ~touched[:, None, :, None].expand(n_pages, nkv, 64, d)
+    assert bool((k_pages.float().cpu()[untouched] == 7.0).all())
+    assert bool((v_pages.float().cpu()[untouched] == 7.0).all())
+
+
+# ------------------------------------------------------------------ attention
+def _paged(seqs, nkv, d, dtype, g, fill=float("nan")):
+    """Random K/V for sequences of the given total lengths in a scrambled
+    paged store whose unused rows hold `fill` (NaN: reading one shows)."""
+    n_pages_per = [(n + 63) // 64 for n in seqs]
+    total = sum(n_pages_per) + 5
+    perm = torch.randperm(total, generator=g)
+    table = torch.full((len(seqs) + 3, max(n_pages_per) + 2), -12345, dtype=torch.int32)
+    slots = torch.randperm(len(seqs) + 3, generator=g)[: len(seqs)].tolist()
+    k_pages = torch.full((total, nkv, 64, d), fill, dtype=torch.float32)
+    v_pages = torch.full((total, nkv, 64, d), fill, dtype=torch.float32)
+    ks, vs, o = [], [], 0
+    for i, n in enumerate(seqs):
+        k = torch.randn(n, nkv, d, generator=g)
+        v = torch.randn(n, nkv, d, generator=g)
+        for p in range(n_pages_per[i]):
+            page = int(perm[o + p])
+            table[slots[i], p] = page
+            m = min(64, n - p * 64)
+            k_pages[page, :, :m] = k[p * 64:p * 64 + m].transpose(0, 1)
+            v_pages[page, :, :m] = v[p * 64:p * 64 + m].transpose(0, 1)
+        o += n_pages_per[i]
+        ks.append(k)
+        vs.append(v)
+    return slots, table, k_pages.to(dtype), v_pages.to(dtype), ks, vs
+
+
+def _ref_rows(q, ks, vs, seqs, scale, window, dtype):
+    """seqs: (start, n_new) per sequence; q packed [rows, nq, d]."""
+    outs, r = [], 0
+    for (start, n), k, v in zip(seqs, ks, vs):
+        T = start + n
+        kk, vv = k.to(dtype).double().numpy(), v.to(dtype).double().numpy()
+        qfull = np.zeros((T, q.shape[1], q.shape[2]))
+        qfull[start:] = q[r:r + n].to(dtype).double().numpy()
+        outs.append(pm.causal_attention(qfull, kk[:T], vv[:T], scale, window, first_row=start)[start:])
+        r += n
+    return np.concatenate(outs, axis=0)
+
+
+ATT_CASES = [
+    # nq, nkv, d, [(start, n_new)], window
+    (4, 2, 16, [(0, 1)], None),
+    (4, 2, 16, [(0, 5), (0, 17), (0, 32)], None),
+    (6, 1, 32, [(0, 1), (0, 7), (0, 64), (0, 100), (0, 129)], None),
+    (3, 1, 48, [(0, 300), (0, 38)], 37),
+    (3, 1, 48, [(100, 37), (700, 300)], 37),
+    (32, 8, 128, [(1489, 41), (0, 1), (63, 2)], None),
+    (7, 7, 80, [(0, 255), (5, 251)], 64),
+    (16, 1, 64, [(31, 34)], None),
+]
+
+
+@pytest.mark.parametrize("nq,nkv,d,seqs,window", ATT_CASES)
+@pytest.mark.parametrize("kernel", ["plain_f32", "plain_bf16", "prefill_bf16"])
+def test_attention_over_the_paged_cache(nq, nkv, d, seqs, window, kernel):
+    g = torch.Generator().manual_seed(nq * 31 + d)
+    dtype = torch.float32 if kernel == "plain_f32" else torch.bfloat16
+    slots, table, kp, vp, ks, vs = _paged([a + b for a, b in seqs], nkv, d, dtype, g)
+    R = sum(b for _, b in seqs)
+    q = torch.randn(R, nq, d, generator=g) * 1.5
+    scale = d ** -0.5
+    ref = _ref_rows(q, ks, vs, seqs, scale, window, dtype)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    row_pos = i32([a + j for a, b in seqs for j in range(b)])
+    row_slot = i32([slots[i] for i, (a, b) in enumerate(seqs) for _ in range(b)])
+    qd = q.reshape(R, nq * d).to(dtype).to(DEV)
+    if kernel.startswith("plain"):
+        out = ops().attention_plain(qd, kp.to(DEV), vp.to(DEV), table.to(DEV), 64, row_pos, row_slot,
+                                    nq, nkv, d, window, scale)
+    else:
+        row0 = [0]
+        for _, b in seqs:
+            row0.append(row0[-1] + b)
+        out = ops().attention_prefill(qd, kp.to(DEV), vp.to(DEV), table.to(DEV), 64, i32(slots),
+                                      i32([a for a, _ in seqs]), i32([b for _, b in seqs]), i32(row0),
+                                      max(b for _, b in seqs), nq, nkv, d, window, scale)
+    assert not bool(torch.isnan(out.float()).any()), "read a cache row that was never written"
+    assert relerr(out.reshape(R, nq, d), ref) < (2e-6 if dtype == torch.float32 else 8e-3)
+
+
+@pytest.mark.parametrize("nq,nkv,d,ctxs,window,splits", [
+    (4, 2, 16, [1, 17, 64, 65], None, None), (6, 1, 32, [100, 129], None, 3), (3, 1, 48, [300, 38, 37], 37, 5),
+    (32, 8, 128, [640] * 4, None, None), (32, 8, 128, [1, 63, 64, 4000], None, 16), (40, 2, 256, [999], None, 4),
+    (7, 7, 80, [255, 256], 100, 2)])
+def test_attention_decode_splits(nq, nkv, d, ctxs, window, splits):
+    g = torch.Generator().manual_seed(nq + d)
+    slots, table, kp, vp, ks, vs = _paged(ctxs, nkv, d, torch.bfloat16, g)
+    R = len(ctxs)
+    q = torch.randn(R, nq, d, generator=g) * 1.5
+    ref = _ref_rows(q, ks, vs, [(c - 1, 1) for c in ctxs], d ** -0.5, window, torch.bfloat16)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    out = ops().attention_decode(q.reshape(R, nq * d).bfloat16().to(DEV), kp.to(DEV), vp.to(DEV), table.to(DEV),
+                                 64, i32([c - 1 for c in ctxs]), i32(slots), nq, nkv, d, window, d ** -0.5,
+                                 n_splits=splits)
+    assert not bool(torch.isnan(out.float()).any())
+    assert relerr(out.reshape(R, nq, d), ref) < 8e-3
+
+
+@pytest.mark.parametrize("kernel", ["plain_f32", "plain_bf16", "prefill_bf16", "decode_bf16"])
+def test_a_far_key_among_hundreds_and_the_windows_edge(kernel):
+    """One key gets a score far above the rest, so the output must be its value
+    row; the key sits far back (position 3 of 900), and then exactly at the
+    window's edge: visible at i - j = window - 1, gone at i - j = window."""
+    nq, nkv, d, n = 4, 2, 64, 900
+    dtype = torch.float32 if kernel == "plain_f32" else torch.bfloat16
+    g = torch.Generator().manual_seed(5)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    for far, window, expect_hit in ((3, None, True), (n - 1 - 99, 100, True), (n - 1 - 100, 100, False)):
+        slots, table, kp, vp, ks, vs = _paged([n], nkv, d, torch.float32, g, fill=0.0)
+        q = torch.randn(1, nq, d, generator=g) * 0.1
+        # plant: key `far` of every kv head is 8 * the unit query direction of head 0 / head 2
+        page, tok = int(table[slots[0], far // 64]), far % 64
+        for kvh, h in ((0, 0), (1, 2)):
+            u = q[0, h] / q[0, h].norm()
+            q[0, h] = u * 6.0
+            kp[page, kvh, tok] = u * 60.0
+        qd = q.reshape(1, nq * d).to(dtype).to(DEV)
+        args = (kp.to(dtype).to(DEV), vp.to(dtype).to(DEV), table.to(DEV), 64)
+        if kernel.startswith("plain"):
+            out = ops().attention_plain(qd, *args, i32([n - 1]), i32(slots), nq, nkv, d, window, d ** -0.5)
+        elif kernel == "decode_bf16":
+            out = ops().attention_decode(qd, *args, i32([n - 1]), i32(slots), nq, nkv, d, window, d ** -0.5, n_splits=4)
+        else:
+            out = ops().attention_prefill(qd, *args, i32(slots), i32([n - 1]), i32([1]), i32([0, 1]), 1,
+                                          nq, nkv, d, window, d ** -0.5)
+        out = out.float().cpu().reshape(nq, d)
+        for kvh, h in ((0, 0), (1, 2)):
+            target = vp[page, kvh, tok].to(dtype).float()
+            close = float((out[h] - target).abs().max()) < 2e-2
+            assert close == expect_hit, (far, window, h)
+
+
+# -------------------------------------------------------------------- sampling
+def test_argmax_ties_go_to_the_highest_index():
+    g = torch.Generator().manual_seed(3)
+    l = torch.randn(5, 151936, generator=g)
+    l[1, 77] = l[1, 150000] = 50.0
+    l[2, 0] = 60.0
+    l[3, -1] = 60.0
+    l[4] = 0.0
+    got = ops().argmax(l.to(DEV)).tolist()
+    assert got == [pm.argmax_last(r.numpy()) for r in l]
+    assert got[1] == 150000 and got[2] == 0 and got[3] == 151935 and got[4] == 151935
+
+
+@pytest.mark.parametrize("V", [1000, 151936])
+@pytest.mark.parametrize("top_k,top_p", [(None, None), (1, None), (50, None), (None, 0.9), (40, 0.5), (None, 0.0)])
+def test_sampling_matches_the_plain_sampler_given_the_same_uniforms(V, top_k, top_p):
+    g = torch.Generator().manual_seed(V + (top_k or 0))
+    B = 12
+    logits = torch.randn(B, V, generator=g) * 3
+    logits[3, 5] = logits[3, 900] = logits[3].max() + 1  # a tie at the top
+    u = torch.rand(B, generator=g)
+    u[0], u[1] = 0.0, 0.99999994
+    T = 0.8
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    got = ops().sample(logits.to(DEV), torch.full((B,), T, device=DEV), u.to(DEV),
+                       top_k=i32([top_k] * B) if top_k else None,
+                       top_p=torch.full((B,), top_p, device=DEV) if top_p is not None else None).tolist()
+    for b in range(B):
+        want = pm.sample_token(logits[b].numpy(), T, float(u[b]), top_k, top_p)
+        if got[b] != want:
+            # parallel sums round differently: accept only a neighbour in the walk
+            # whose cumulative boundary lies within rounding of the draw
+            p = np.exp((logits[b].double().numpy() - float(logits[b].max())) / T)
+            kept = np.sort(np.argsort(-p, kind="stable")[: top_k or V]) if top_p is None else None
+            assert kept is not None, (b, got[b], want)
+            cum = np.cumsum(p[kept])
+            draw = float(u[b]) * cum[-1]
+            i_w, i_g = int(np.searchsorted(kept, want)), int(np.searchsorted(kept, got[b]))
+            assert abs(i_w - i_g) == 1 and abs(cum[min(i_w, i_g)] - draw) < 1e-5 * cum[-1], (b, got[b], want)
+    if top_k == 1 or top_p == 0.0:
+        assert got == [int(torch.nonzero(r == r.max())[0]) for r in logits]  # the most probable, lowest index
+
+
+def test_sampling_distribution():
+    V, n = 50, 4000
+    g = torch.Generator().manual_seed(9)
+    row = torch.randn(V, generator=g) * 2
+    logits = row.repeat(n, 1).to(DEV)
+    u = ((torch.arange(n) + 0.5) / n).to(DEV)
+    got = ops().sample(logits, torch.full((n,), 0.7, device=DEV), u).cpu().numpy()
+    p = np.exp(row.double().numpy() / 0.7)
+    p /= p.sum()
+    np.testing.assert_allclose(np.bincount(got, minlength=V) / n, p, atol=1.5e-3)

@@ -13,8 +13,11 @@
 // kernel combines the splits in split order
 // (src/kernels_cuda/attention_online.cu:51-78).  Softmax runs in 32-bit on
 // base-2 exponentials: p = 2^((s - m) * scale * log2 e).
+#include <mutex>
+
 #include "attn_mma.cuh"
 #include "common.cuh"
+#include "noalloc.h"
 #include "paged.cuh"
 
 namespace {
@@ -224,4 +227,62 @@ extern "C" int rfx_attention_decode(const void* q, const void* k_pages, const vo
             return RFX_ERR_UNSUPPORTED;
     }
 #undef RFX_CASE
+}
+
+// ---------------------------------------------------------------------------
+// The same kernel behind an entry point that allocates nothing (noalloc.h).
+// Its split partials live in this file-scope device array instead of a buffer
+// the caller allocates.  In host code the array's name is only a stand-in for
+// the device symbol, never a device address, so the address is asked for once
+// per device, with that device current, and that pointer is what the kernel
+// gets.
+namespace {
+
+static __device__ __align__(256) float g_noalloc_partial[RFX_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+std::mutex g_noalloc_mu;
+
+// Device address of the array on the current device; looked up on the first
+// call per device.
+int noalloc_scratch(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return RFX_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (!g_noalloc_ptr[dev]) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_noalloc_partial);
+        if (e != cudaSuccess) return (int)e;
+        g_noalloc_ptr[dev] = p;
+    }
+    *out = g_noalloc_ptr[dev];
+    return 0;
+}
+
+}  // namespace
+
+extern "C" long long rfx_attention_decode_noalloc_capacity(void) {
+    return (long long)RFX_NOALLOC_SCRATCH_FLOATS;
+}
+
+extern "C" int rfx_attention_decode_noalloc(const void* q, const void* k_pages, const void* v_pages,
+                                            const int* page_table, int max_pages, int page_size,
+                                            const int* row_pos, const int* row_slot, void* out, int R,
+                                            int nq, int nkv, int head_dim, int n_splits, int window,
+                                            float scale, void* stream) {
+    if (R <= 0) return 0;
+    if (n_splits < 1 || nq <= 0 || head_dim <= 0) return RFX_ERR_BAD_ARG;
+    const long long need = (long long)R * nq * n_splits * (head_dim + 2);
+    if (n_splits > 1 && need > (long long)RFX_NOALLOC_SCRATCH_FLOATS) return RFX_ERR_SCRATCH;
+    float* scratch = nullptr;
+    const int st = noalloc_scratch(&scratch);
+    if (st != 0) return st;
+    // every split writes its whole partial (empty splits write max = -inf, sum = 0)
+    // before the combine reads it, so nothing in the array has to start at zero
+    return rfx_attention_decode(q, k_pages, v_pages, page_table, max_pages, page_size, row_pos,
+                                row_slot, out, scratch, R, nq, nkv, head_dim, n_splits, window, scale,
+                                stream);
 }

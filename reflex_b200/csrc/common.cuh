@@ -14,6 +14,7 @@
 #define RFX_ERR_BAD_ARG (-1)
 #define RFX_ERR_UNSUPPORTED (-2)
 #define RFX_ERR_TIMEOUT (-3)
+#define RFX_ERR_SCRATCH (-4)
 
 #define RFX_CHECK_LAUNCH()                         \
     do {                                           \

@@ -179,5 +179,6 @@ extern "C" const char* rfx_error_string(int code) {
     if (code == RFX_ERR_BAD_ARG) return "bad argument";
     if (code == RFX_ERR_UNSUPPORTED) return "size not supported by this kernel";
     if (code == RFX_ERR_TIMEOUT) return "bounded device wait ran out";
+    if (code == RFX_ERR_SCRATCH) return "the call needs more scratch than the built-in array holds";
     return cudaGetErrorString((cudaError_t)code);
 }

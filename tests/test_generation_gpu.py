@@ -1,0 +1,179 @@
+"""Generation through the entry points: greedy and sampled generation against
+the plain implementation, the command line, and trace replay as a user runs it."""
+
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import helpers
+import plain_model as pm
+from tiny_configs import ALL
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def plain_generate(folder, prompt, n, pick):
+    cfg, w = pm.read_model(folder)
+    seq, out, margins = list(prompt), [], []
+    for step in range(n):
+        logits = pm.forward(cfg, w, seq)[-1]
+        tok = pick(logits, step)
+        top2 = np.sort(logits)[-2:]
+        margins.append(float(top2[1] - top2[0]))
+        out.append(tok)
+        seq.append(tok)
+    return out, margins
+
+
+@pytest.mark.parametrize("name,weights", [("A", "f32"), ("B", "f32"), ("B", "bf16"), ("C", "bf16")])
+def test_greedy_generation_of_an_unequal_batch(name, weights):
+    import reflex_b200
+
+    folder = helpers.model_folder(name, 7, "float32" if weights == "f32" else "bfloat16")
+    V = ALL[name]["vocab_size"]
+    lengths = (5, 17, 32) if name == "A" else (1, 7, 64, 100, 129)
+    n_new = 16 if name == "A" else 24
+    prompts = [helpers.random_tokens(n, V, 40 + n) for n in lengths]
+    model = reflex_b200.Model.load(folder, weights=weights, max_tokens=4096, max_batch=4)
+    got = model.generate(prompts, n_new)
+    assert model.last_stats.batches == (1 if name == "A" else 2)
+    for p, g in zip(prompts, got):
+        assert len(g) == n_new
+        want, margins = plain_generate(folder, p, n_new, lambda l, s: pm.argmax_last(l))
+        for i, (a, b) in enumerate(zip(g, want)):
+            if a != b:
+                # only a near tie may differ, and then the sequences part ways
+                limit = 1e-5 if weights == "f32" else 2e-2
+                assert margins[i] < limit * max(1.0, margins[i]), (len(p), i, a, b, margins[i])
+                break
+    one = model.generate(prompts[1], 3)
+    assert one == got[1][:3]  # alone or in a batch: the same tokens
+
+
+def test_sampled_generation_follows_the_plain_sampler_with_the_same_uniforms():
+    import reflex_b200
+    from reflex_b200.sampling import uniform
+
+    folder = helpers.model_folder("B", 7, "float32")
+    V = ALL["B"]["vocab_size"]
+    prompts = [helpers.random_tokens(n, V, 60 + n) for n in (1, 7, 64)]
+    model = reflex_b200.Model.load(folder, weights="f32", max_tokens=2048)
+    params = reflex_b200.SamplingParams(temperature=0.8, seed=1234, top_k=50, top_p=0.95)
+    got = model.generate(prompts, 12, params)
+    assert got == model.generate(prompts, 12, params)  # a seed makes it reproducible
+    assert got != model.generate(prompts, 12, reflex_b200.SamplingParams(temperature=0.8, seed=99))
+    for r, (p, g) in enumerate(zip(prompts, got)):
+        want, _ = plain_generate(folder, p, 12, lambda l, s: pm.sample_token(l, 0.8, uniform(1234, r, s), 50, 0.95))
+        assert g == want
+    alone = model.generate([prompts[2]], 12, params)[0]
+    assert len(alone) == 12 and all(0 <= t < V for t in alone)
+
+
+def test_stop_tokens_and_limits_through_the_entry_point():
+    import reflex_b200
+    from reflex_b200 import InvalidInput
+
+    folder = helpers.model_folder("A", 7, "float32")
+    model = reflex_b200.Model.load(folder, weights="f32", max_tokens=1024)
+    prompt = helpers.random_tokens(9, 512, 1)
+    free = model.generate(prompt, 10)
+    stop = free[3]
+    cut = model.generate(prompt, 10, reflex_b200.SamplingParams(stop_token_ids=(stop,)))
+    assert cut == free[: free.index(stop) + 1]  # the stop token is kept, then it ends
+    with pytest.raises(InvalidInput):
+        model.generate(prompt, 0)
+    with pytest.raises(InvalidInput):
+        model.generate([prompt, []], 2)
+    with pytest.raises(reflex_b200.ContextOverflow):
+        model.generate(prompt, 250)  # max_position_embeddings is 256
+
+
+def test_system1_scores_candidates_in_one_step():
+    import reflex_b200
+
+    folder = helpers.model_folder("B", 7, "float32")
+    cfg, w = pm.read_model(folder)
+    model = reflex_b200.Model.load(folder, weights="f32", max_tokens=2048)
+    prompt = helpers.random_tokens(11, 1000, 3)
+    cands = [[5], [77, 3, 910], [400, 401]]
+    steps = model.engine.steps_run
+    resp = model.system1_evaluate(prompt, cands, temperature=0.5)
+    assert model.engine.steps_run == steps + 1
+    scores = []
+    for c in cands:
+        logits = pm.forward(cfg, w, prompt + c[:-1])
+        scores.append(sum(float(logits[len(prompt) - 1 + i, t]) for i, t in enumerate(c)))
+    np.testing.assert_allclose([r.score for r in resp.results], scores, rtol=1e-4, atol=1e-5)
+    e = np.exp((np.array(scores) - max(scores)) / 0.5)
+    np.testing.assert_allclose(resp.probabilities, e / e.sum(), rtol=1e-3)
+    assert resp.best_idx == int(np.argmax(scores))
+    assert abs(resp.entropy + float((e / e.sum() * np.log2(e / e.sum())).sum())) < 1e-3
+
+
+def test_command_line_generate_and_system1():
+    folder = helpers.model_folder("A", 7, "float32")
+    exe = [sys.executable, os.path.join(ROOT, "bin", "reflex")]
+    out = subprocess.run(exe + ["generate", folder, "5,17,3", "--max-tokens", "4", "--weights", "f32",
+                                "--prompt-ids", "9,9"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    lines = [l for l in out.stdout.splitlines() if l.startswith("REFLEX_GENERATE_OK")]
+    assert len(lines) == 2 and "num_generated=4" in lines[0] and "weights_dtype=f32" in lines[0]
+    ids = [int(t) for t in lines[0].split("token_ids=[")[1].split("]")[0].split(",")]
+    want, _ = plain_generate(folder, [5, 17, 3], 4, lambda l, s: pm.argmax_last(l))
+    assert ids == want
+    out = subprocess.run(exe + ["system1", folder, "5,17,3", "--candidate", "1", "--candidate", "2,3", "--json"],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    recs = [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")]
+    assert recs[-1]["num_candidates"] == 2 and len(recs) == 3
+    bad = subprocess.run(exe + ["generate", folder, "5", "--max-tokens", "0"], capture_output=True, text=True, timeout=300)
+    assert bad.returncode == 1 and "error:" in bad.stderr
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_replays_steps_and_writes_logits(dtype, tmp_path):
+    """bin/trace_run as a subprocess: two requests start together with unequal
+    lengths, go on one token a step, the shorter one ends earlier, and a third
+    request then starts in the freed slot (the cache holds two requests)."""
+    name = "B"
+    V = ALL[name]["vocab_size"]
+    folder = helpers.model_folder(name, 7, "float32" if dtype == "float32" else "bfloat16")
+    a, b, c = (helpers.random_tokens(n, V, 80 + n) for n in (70, 9, 40))
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:60], "want": list(range(60))},
+                                     {"id": "b", "tokens": b[:5], "want": [0, 4]}], "end": []}]
+    for i in range(4):
+        steps.append({"step": 1 + i, "entries": [{"id": "a", "tokens": [a[60 + i]], "want": [0]},
+                                                 {"id": "b", "tokens": [b[5 + i]], "want": [0]}],
+                      "end": ["b"] if i == 3 else []})
+    steps.append({"step": 5, "entries": [{"id": "a", "tokens": a[64:70], "want": []}], "end": ["a"]})
+    steps.append({"step": 6, "entries": [{"id": "c", "tokens": c, "want": [39]}], "end": ["c"]})
+    out_dir = str(tmp_path / "out")
+    proc = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
+                           "--out", out_dir, "--max-tokens", "128"],
+                          input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True,
+                          timeout=600)
+    assert proc.returncode == 0, proc.stderr
+    assert proc.stdout.split() == [w for i in range(7) for w in ("done", str(i))]
+    tol = 3e-6 if dtype == "float32" else 1.5e-2
+    ra, rb, rc = (helpers.plain_logits(folder, t) for t in (a, b, c))
+    scale = max(np.abs(ra).max(), np.abs(rb).max(), np.abs(rc).max())
+
+    def load(step, rows):
+        x = np.fromfile(os.path.join(out_dir, f"{step}.f32"), dtype="<f4")
+        assert x.size == rows * V
+        return x.reshape(rows, V)
+
+    x = load(0, 62)
+    assert np.abs(x[:60] - ra[:60]).max() < tol * scale
+    assert np.abs(x[60:] - rb[[0, 4]]).max() < tol * scale
+    for i in range(4):
+        x = load(1 + i, 2)
+        assert np.abs(x[0] - ra[60 + i]).max() < tol * scale
+        assert np.abs(x[1] - rb[5 + i]).max() < tol * scale
+    assert not os.path.exists(os.path.join(out_dir, "5.f32"))  # nothing was wanted
+    assert np.abs(load(6, 1)[0] - rc[39]).max() < tol * scale

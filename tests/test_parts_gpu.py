@@ -1,0 +1,215 @@
+"""Each part of a layer alone against the plain implementation, the run order as
+data (a layer named twice, a layer reading another layer's cache), and a toy
+mixer with state of its own that is defined here, registered, built and stepped
+without a change to the framework's files."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_model as pm
+from tiny_configs import TINY_B
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def relerr(got, ref):
+    got = got.double().cpu().numpy() if isinstance(got, torch.Tensor) else got
+    return float(np.abs(got - ref).max() / np.abs(ref).max())
+
+
+def test_norm_rope_and_mlp_parts():
+    from reflex_b200.config.spec import FeedForwardSpec, NormSpec, PositionSpec
+    from reflex_b200.parts import FEED_FORWARDS, NORMS, POSITIONS
+
+    g = torch.Generator().manual_seed(0)
+    for dtype, tol in ((torch.float32, 3e-6), (torch.bfloat16, 1.2e-2)):
+        norm = NORMS.get("rmsnorm")(NormSpec("rmsnorm", 72, 1e-4), dtype, DEV)
+        w = 1 + 0.1 * torch.randn(72, generator=g)
+        norm.bind({"weight": w.to(dtype)})
+        x = torch.randn(5, 72, generator=g)
+        out = norm(x.to(DEV))
+        assert out.dtype == dtype
+        assert relerr(out, pm.rms_norm(x.double().numpy(), w.to(dtype).double().numpy(), 1e-4)) < max(tol, 5e-3 if dtype == torch.bfloat16 else 0)
+
+        spec = FeedForwardSpec("swiglu", hidden_size=72, intermediate_size=136)
+        mlp = FEED_FORWARDS.get("swiglu")(spec, dtype, DEV)
+        ws = {k: (torch.randn(*i.shape, generator=g) * 0.1).to(dtype) for k, i in mlp.tensor_specs(spec).items()}
+        mlp.bind(ws)
+        xin = torch.randn(7, 72, generator=g).to(dtype)
+        got = mlp.forward(xin.to(DEV))
+        assert got.dtype == torch.float32  # the delta joins the 32-bit residual stream
+        ref = pm.swiglu(xin.double().numpy(), *(ws[k].double().numpy() for k in ("gate_proj", "up_proj", "down_proj")))
+        assert relerr(got, ref) < tol
+
+    rope = POSITIONS.get("rope_neox")(PositionSpec("rope_neox", head_dim=48, rotary_dim=32, theta=5e4), torch.float32, DEV)
+    denom, rd = rope.rotation()
+    assert rd == 32 and denom.dtype == torch.float32
+    want = np.power(5e4, np.arange(16) * 2.0 / 32)
+    np.testing.assert_allclose(denom.cpu().numpy(), want, rtol=1e-7)
+
+
+def _one_layer_engine(dtype, run_order=None, n_layers=1):
+    """TINY_B's sizes with `n_layers` layers and an optional run order."""
+    from reflex_b200 import models  # noqa: F401
+    from reflex_b200.config import RunEntry, spec_from_config_dict
+    from reflex_b200.engine import CausalLM, Engine
+    from reflex_b200.weights import random_tensors
+
+    cfg = dict(TINY_B, num_hidden_layers=n_layers)
+    _, spec = spec_from_config_dict(cfg)
+    if run_order is not None:
+        spec.run_order = [RunEntry(*r) for r in run_order]
+    model = CausalLM(spec, dtype, DEV)
+    tensors = dict(random_tensors(spec, 3, torch.float32))
+    # sharpen the attention so that the cache matters; in float32 only: a peaked
+    # softmax multiplies bfloat16's rounding noise layer after layer
+    if dtype == torch.float32:
+        for k in tensors:
+            if k.endswith(("q_norm.weight", "k_norm.weight")):
+                tensors[k] = tensors[k] * 2.5
+    if dtype == torch.bfloat16:
+        tensors = {k: v.bfloat16() for k, v in tensors.items()}
+    model.bind(tensors)
+    w = {k: v.double().numpy() for k, v in tensors.items()}
+    return cfg, w, Engine(model, max_tokens=512)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_part_and_block_against_the_plain_layer(dtype):
+    """The pre-norm block with its attention and feed-forward, stepped through
+    the cache in two chunks, against the plain decoder layer on the whole."""
+    cfg, w, eng = _one_layer_engine(dtype)
+    toks = helpers.random_tokens(70, cfg["vocab_size"], 1)
+    from reflex_b200 import ops
+    from reflex_b200.engine.batch import make_batch
+
+    model, cache = eng.model, eng.cache
+    s = cache.take_slot()
+    hs = []
+    for part, start in ((toks[:41], 0), (toks[41:], 41)):
+        cache.reserve([(s, len(part))])
+        batch = make_batch([part], [s], [start], [[0]], DEV)
+        h, pending = model.hidden_states(batch, cache)
+        hs.append(ops.add_(h.clone(), pending))
+        cache.commit([(s, len(part))])
+    got = torch.cat(hs)
+    h0 = w["model.embed_tokens.weight"][np.array(toks)]
+    ref = pm.decoder_layer(h0, w, "model.layers.0.", cfg, np.arange(70), None)
+    assert relerr(got, ref) < (3e-6 if dtype == torch.float32 else 1.5e-2)
+    cache.give_slot(s)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_run_order_is_data_a_layer_twice_and_a_shared_cache(dtype):
+    """Run order [L0, L1, L0 again with a cache entry of its own, L1 reading the
+    keys and values that its first run wrote] against the same order spelled out
+    with the plain implementation's parts."""
+    order = [(0, 0, True), (1, 1, True), (0, 2, True), (1, 1, False)]
+    cfg, w, eng = _one_layer_engine(dtype, run_order=order, n_layers=2)
+    assert len(eng.cache.kv_groups) == 1 and len(eng.cache.kv_groups[0].entries) == 3
+    toks = helpers.random_tokens(45, cfg["vocab_size"], 2)
+    got = helpers.run_tail_one_by_one(eng, toks, tail=20)
+
+    nq, nkv, d, eps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["rms_norm_eps"]
+    T = len(toks)
+    pos = np.arange(T)
+    h = w["model.embed_tokens.weight"][np.array(toks)]
+    kv_of_run1 = None
+    for layer, _cache, writes in order:
+        p = f"model.layers.{layer}."
+        x = pm.rms_norm(h, w[p + "input_layernorm.weight"], eps)
+        q = pm.rope_neox(pm.rms_norm((x @ w[p + "self_attn.q_proj.weight"].T).reshape(T, nq, d),
+                                     w[p + "self_attn.q_norm.weight"], eps), pos, cfg["rope_theta"], d)
+        if writes:
+            k = pm.rope_neox(pm.rms_norm((x @ w[p + "self_attn.k_proj.weight"].T).reshape(T, nkv, d),
+                                         w[p + "self_attn.k_norm.weight"], eps), pos, cfg["rope_theta"], d)
+            v = (x @ w[p + "self_attn.v_proj.weight"].T).reshape(T, nkv, d)
+            if layer == 1:
+                kv_of_run1 = (k, v)
+        else:
+            k, v = kv_of_run1
+        a = pm.causal_attention(q, k, v, 1 / math.sqrt(d), None).reshape(T, nq * d)
+        h = h + a @ w[p + "self_attn.o_proj.weight"].T
+        x = pm.rms_norm(h, w[p + "post_attention_layernorm.weight"], eps)
+        h = h + pm.swiglu(x, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    ref = pm.rms_norm(h, w["model.norm.weight"], eps) @ w["lm_head.weight"].T
+    assert helpers.rel_err(got, ref) < (2e-5 if dtype == torch.float32 else 1.5e-2)
+
+
+def test_a_toy_mixer_with_state_of_its_own():
+    """An exponential moving average over a sequence's tokens: state [hidden]
+    per sequence, fixed size, zero at the start, updated token by token.  It is
+    registered from here; config, weights, cache, step and replay take it as
+    they take attention."""
+    from reflex_b200.cache import StateSpec
+    from reflex_b200.config.spec import FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec
+    from reflex_b200.engine import CausalLM, Engine, expected_tensors
+    from reflex_b200.parts import TensorInfo, register_mixer
+    from reflex_b200.weights import random_tensors
+
+    @register_mixer("toy_ema")
+    class ToyEma:
+        def __init__(self, spec, dtype, device):
+            self.spec, self.dtype, self.device = spec, dtype, device
+            self.decay = dict(spec.params)["decay"]
+
+        @classmethod
+        def tensor_specs(cls, spec):
+            return {"mix": TensorInfo((spec.hidden_size, spec.hidden_size), "matrix")}
+
+        def cache_spec(self):
+            return StateSpec((self.spec.hidden_size,), "float32")
+
+        def bind(self, tensors):
+            self.mix = tensors["mix"].to(self.device, torch.float32)
+
+        def forward(self, x, ctx):
+            out = torch.empty((x.shape[0], self.spec.hidden_size), dtype=torch.float32, device=x.device)
+            b = ctx.batch
+            for i, slot in enumerate(b.slots):  # each sequence's rows, in order
+                state = ctx.state[slot]
+                for r in range(b.row0[i], b.row0[i + 1]):
+                    state.mul_(self.decay).add_(x[r].float(), alpha=1 - self.decay)
+                    out[r] = state
+            return out @ self.mix.T
+
+    H, V = 40, 97
+    mixer = MixerSpec("toy_ema", hidden_size=H, names=(("mix", "ema.mix.weight"),), params=(("decay", 0.75),))
+    ffn = FeedForwardSpec("swiglu", H, 56, names=(("gate_proj", "ff.g"), ("up_proj", "ff.u"), ("down_proj", "ff.d")))
+    layers = [LayerSpec("prenorm", f"blocks.{i}.", mixer, ffn, NormSpec("rmsnorm", H, 1e-5), NormSpec("rmsnorm", H, 1e-5),
+                        names=(("mixer_norm", "n1"), ("feed_forward_norm", "n2"))) for i in range(2)]
+    spec = ModelSpec("toy", V, H, layers, NormSpec("rmsnorm", H, 1e-5), tie_word_embeddings=True, max_positions=256,
+                     embedding_name="emb", final_norm_name="fn")
+    assert "blocks.1.ema.mix.weight" in expected_tensors(spec)
+    model = CausalLM(spec, torch.float32, DEV)
+    tensors = dict(random_tensors(spec, 1, torch.float32))
+    model.bind(tensors)
+    eng = Engine(model, max_tokens=256)
+    assert len(eng.cache.state_groups) == 1 and not eng.cache.kv_groups
+
+    w = {k: v.double().numpy() for k, v in tensors.items()}
+
+    def plain(tokens):
+        h = w["emb"][np.array(tokens)]
+        for i in range(2):
+            p = f"blocks.{i}."
+            x = pm.rms_norm(h, w[p + "n1"], 1e-5)
+            state, outs = np.zeros(H), []
+            for t in range(len(tokens)):
+                state = 0.75 * state + 0.25 * x[t]
+                outs.append(state)
+            h = h + np.stack(outs) @ w[p + "ema.mix.weight"].T
+            x = pm.rms_norm(h, w[p + "n2"], 1e-5)
+            h = h + pm.swiglu(x, w[p + "ff.g"], w[p + "ff.u"], w[p + "ff.d"])
+        return pm.rms_norm(h, w["fn"], 1e-5) @ w["emb"].T
+
+    reqs = [helpers.random_tokens(n, V, n) for n in (9, 3, 14, 6)]
+    got = helpers.run_batches(eng, reqs, 2, [4, 3, 1])  # unequal batches, slots (and state) used again
+    for r, g in zip(reqs, got):
+        assert helpers.rel_err(g, plain(r)) < 1e-5
+    assert eng.cache.slots.held_count == 0

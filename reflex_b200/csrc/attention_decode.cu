@@ -41,6 +41,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     __nv_bfloat16* kbuf = qs + 16 * LD;                               // [2][PAGE][LD]
     __nv_bfloat16* vbuf = kbuf + 2 * PAGE * LD;                       // [2][PAGE][LD]
 
+    rfx::pdl_prologue();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r = blockIdx.x;
     const int kvh = blockIdx.y / n_htiles, ht = blockIdx.y % n_htiles;
@@ -153,6 +154,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 // out[head] = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in order
 __global__ void attention_combine_kernel(const float* __restrict__ partial,
                                          __nv_bfloat16* __restrict__ out, int D, int n_splits) {
+    rfx::pdl_prologue();
     const size_t head = blockIdx.x;
     const float* p = partial + head * n_splits * (D + 2);
     float M = -INFINITY;
@@ -186,16 +188,13 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(R, cache.n_kv_heads * n_htiles, n_splits);
-    kernel<<<grid, DEC_THREADS, smem, s>>>(
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, cache,
-        row_pos, row_slot, (__nv_bfloat16*)out, partial, nq, n_htiles, n_splits, window,
-        scale * 1.4426950408889634f);
-    RFX_CHECK_LAUNCH();
-    if (n_splits > 1) {
-        attention_combine_kernel<<<R * nq, D <= 128 ? 64 : 128, 0, s>>>(partial, (__nv_bfloat16*)out,
-                                                                         D, n_splits);
-        RFX_CHECK_LAUNCH();
-    }
+    RFX_LAUNCH(kernel, grid, DEC_THREADS, smem, s, (const __nv_bfloat16*)q,
+               (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, cache, row_pos, row_slot,
+               (__nv_bfloat16*)out, partial, nq, n_htiles, n_splits, window,
+               scale * 1.4426950408889634f);
+    if (n_splits > 1)
+        RFX_LAUNCH(attention_combine_kernel, R * nq, D <= 128 ? 64 : 128, 0, s, (const float*)partial,
+                   (__nv_bfloat16*)out, D, n_splits);
     return 0;
 }
 

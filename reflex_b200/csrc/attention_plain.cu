@@ -25,6 +25,7 @@ attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
                        const T* __restrict__ v_pages, PagedKV cache,
                        const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                        T* __restrict__ out, int nq, int window, float scale) {
+    pdl_prologue();
     const int d = cache.head_dim;
     const int r = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -88,15 +89,14 @@ extern "C" int rfx_attention_plain(const void* q, const void* k_pages, const voi
     if (grid.y > 65535) return RFX_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     if (dt == RFX_DT_F32)
-        attention_plain_kernel<float><<<grid, 128, 0, s>>>(
-            (const float*)q, (const float*)k_pages, (const float*)v_pages, cache, row_pos,
-            row_slot, (float*)out, nq, window, scale);
+        RFX_LAUNCH(attention_plain_kernel<float>, grid, 128, 0, s, (const float*)q,
+                   (const float*)k_pages, (const float*)v_pages, cache, row_pos, row_slot,
+                   (float*)out, nq, window, scale);
     else if (dt == RFX_DT_BF16)
-        attention_plain_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(
-            (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
-            cache, row_pos, row_slot, (__nv_bfloat16*)out, nq, window, scale);
+        RFX_LAUNCH(attention_plain_kernel<__nv_bfloat16>, grid, 128, 0, s, (const __nv_bfloat16*)q,
+                   (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, cache, row_pos,
+                   row_slot, (__nv_bfloat16*)out, nq, window, scale);
     else
         return RFX_ERR_BAD_ARG;
-    RFX_CHECK_LAUNCH();
     return 0;
 }

@@ -37,6 +37,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     __nv_bfloat16* kbuf = qs + PF_ROWS * LD;                          // [2][PAGE][LD]
     __nv_bfloat16* vbuf = kbuf + 2 * PAGE * LD;
 
+    rfx::pdl_prologue();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = blockIdx.y, kvh = blockIdx.z;
     const int n_new = seq_new[seq];
@@ -145,11 +146,9 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, cons
     if (e != cudaSuccess) return (int)e;
     dim3 grid((max_new + bq - 1) / bq, S, cache.n_kv_heads);
     if (grid.y > 65535 || grid.z > 65535) return RFX_ERR_UNSUPPORTED;
-    kernel<<<grid, PF_THREADS, smem, s>>>(
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, cache,
-        seq_slot, seq_start, seq_new, seq_row0, (__nv_bfloat16*)out, nq, bq, window,
-        scale * 1.4426950408889634f);
-    RFX_CHECK_LAUNCH();
+    RFX_LAUNCH(kernel, grid, PF_THREADS, smem, s, (const __nv_bfloat16*)q,
+               (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, cache, seq_slot, seq_start,
+               seq_new, seq_row0, (__nv_bfloat16*)out, nq, bq, window, scale * 1.4426950408889634f);
     return 0;
 }
 

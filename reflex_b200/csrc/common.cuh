@@ -5,6 +5,9 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
+
+#include <utility>
 
 #define RFX_DT_F32 0
 #define RFX_DT_BF16 1
@@ -23,6 +26,68 @@
     } while (0)
 
 namespace rfx {
+
+// ---- programmatic dependent launch -------------------------------------------
+// Every kernel of the library is launched with programmatic stream
+// serialization: the next kernel's CTAs may start while this one drains, run
+// whatever does not depend on it (barrier set-up, weight prefetch), and block
+// in pdl_wait() until this kernel has completed and its writes are visible.
+// Rules every kernel keeps: no global write and no read of another kernel's
+// output before pdl_wait(); every kernel executes pdl_wait() (so completion
+// stays transitive along the stream).  REFLEX_B200_PDL=0 turns the launch
+// attribute off; the device calls are then no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_prologue() {
+    pdl_launch_dependents();
+    pdl_wait();
+}
+
+inline bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("REFLEX_B200_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
+
+// Launch with the library's attributes; cluster_z > 1 asks for a thread-block
+// cluster of (1, 1, cluster_z).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                          cudaStream_t stream, int cluster_z, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_z > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = cluster_z;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+#define RFX_LAUNCH(kernel, grid, block, smem, stream, ...)                                   \
+    do {                                                                                     \
+        cudaError_t e__ = rfx::launch(kernel, grid, block, smem, stream, 1, __VA_ARGS__);    \
+        if (e__ != cudaSuccess) return (int)e__;                                             \
+    } while (0)
 
 template <typename T> __device__ __forceinline__ float ld(const T* p, size_t i);
 template <> __device__ __forceinline__ float ld<float>(const float* p, size_t i) { return p[i]; }

@@ -13,6 +13,7 @@ template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ out, int H, int V, float scale,
                              int* __restrict__ err) {
+    pdl_prologue();
     const int r = blockIdx.x;
     const int id = ids[r];
     if (id < 0 || id >= V) {
@@ -40,31 +41,62 @@ __global__ void rmsnorm_kernel(const float* x, const TD* __restrict__ delta,
                                TO* __restrict__ out, const int* __restrict__ rows, int H,
                                float eps, float w_offset) {
     __shared__ float scratch[32];
-    extern __shared__ float row_buf[];  // H floats
+    extern __shared__ __align__(16) float row_buf[];  // H floats
+    pdl_prologue();
     const int src = rows ? rows[blockIdx.x] : blockIdx.x;
     const float* xr = x + (size_t)src * H;
     float ss = 0.0f;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        float t = xr[c];
-        if (delta) t += ld<TD>(delta, (size_t)src * H + c);
-        row_buf[c] = t;
-        ss = fmaf(t, t, ss);
-    }
-    if (x_out) {
-        for (int c = threadIdx.x; c < H; c += blockDim.x) x_out[(size_t)src * H + c] = row_buf[c];
+    const bool vec = (H & 3) == 0;  // rows then start on 16-byte boundaries
+    if (vec) {
+        const float4* x4 = reinterpret_cast<const float4*>(xr);
+        for (int c = threadIdx.x; c < H / 4; c += blockDim.x) {
+            float4 t = x4[c];
+            if (delta) {
+                t.x += ld<TD>(delta, (size_t)src * H + 4 * c);
+                t.y += ld<TD>(delta, (size_t)src * H + 4 * c + 1);
+                t.z += ld<TD>(delta, (size_t)src * H + 4 * c + 2);
+                t.w += ld<TD>(delta, (size_t)src * H + 4 * c + 3);
+            }
+            reinterpret_cast<float4*>(row_buf)[c] = t;
+            if (x_out) reinterpret_cast<float4*>(x_out + (size_t)src * H)[c] = t;
+            ss = fmaf(t.x, t.x, ss);
+            ss = fmaf(t.y, t.y, ss);
+            ss = fmaf(t.z, t.z, ss);
+            ss = fmaf(t.w, t.w, ss);
+        }
+    } else {
+        for (int c = threadIdx.x; c < H; c += blockDim.x) {
+            float t = xr[c];
+            if (delta) t += ld<TD>(delta, (size_t)src * H + c);
+            row_buf[c] = t;
+            if (x_out) x_out[(size_t)src * H + c] = t;
+            ss = fmaf(t, t, ss);
+        }
     }
     if (!out) return;
     const float total = block_sum(ss, scratch);
     const float r = 1.0f / sqrtf(total / (float)H + eps);
     TO* orow = out + (size_t)blockIdx.x * H;
-    for (int c = threadIdx.x; c < H; c += blockDim.x)
-        st<TO>(orow, c, (row_buf[c] * r) * (w_offset + w[c]));
+    if (vec) {
+        for (int c = threadIdx.x; c < H / 4; c += blockDim.x) {
+            const float4 t = reinterpret_cast<const float4*>(row_buf)[c];
+            const float4 ww = reinterpret_cast<const float4*>(w)[c];
+            st<TO>(orow, 4 * c, (t.x * r) * (w_offset + ww.x));
+            st<TO>(orow, 4 * c + 1, (t.y * r) * (w_offset + ww.y));
+            st<TO>(orow, 4 * c + 2, (t.z * r) * (w_offset + ww.z));
+            st<TO>(orow, 4 * c + 3, (t.w * r) * (w_offset + ww.w));
+        }
+    } else {
+        for (int c = threadIdx.x; c < H; c += blockDim.x)
+            st<TO>(orow, c, (row_buf[c] * r) * (w_offset + w[c]));
+    }
 }
 
 // out[r, i] = silu(gu[r, i]) * gu[r, I + i],  silu(g) = g / (1 + exp(-g))
 // (src/kernels_cuda/silu_and_mul.cu:7-23)
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int R, int I) {
+    pdl_prologue();
     const size_t n = (size_t)R * I;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (size_t)gridDim.x * blockDim.x) {
@@ -78,15 +110,18 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 // y[i] = a[i] + b[i] in 32-bit (src/kernels_cuda/elementwise.cu:8-24)
 template <typename T>
 __global__ void add_kernel(float* __restrict__ a, const T* __restrict__ b, size_t n) {
+    pdl_prologue();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (size_t)gridDim.x * blockDim.x)
         a[i] += ld<T>(b, i);
 }
 
+// A function of H alone, so that a row's sum of squares is reduced in the same
+// order whatever the batch.
 int norm_threads(int H) {
     int t = ((H + 3) / 4 + 31) / 32 * 32;
     if (t < 32) t = 32;
-    if (t > 512) t = 512;
+    if (t > 1024) t = 1024;
     return t;
 }
 
@@ -98,13 +133,12 @@ extern "C" int rfx_embed(const void* table, int table_dt, const int* ids, int R,
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dt == RFX_DT_F32)
-        embed_kernel<float><<<R, threads, 0, s>>>((const float*)table, ids, out, H, V, scale, err);
+        RFX_LAUNCH(embed_kernel<float>, R, threads, 0, s, (const float*)table, ids, out, H, V, scale, err);
     else if (table_dt == RFX_DT_BF16)
-        embed_kernel<__nv_bfloat16>
-            <<<R, threads, 0, s>>>((const __nv_bfloat16*)table, ids, out, H, V, scale, err);
+        RFX_LAUNCH(embed_kernel<__nv_bfloat16>, R, threads, 0, s, (const __nv_bfloat16*)table, ids, out,
+                   H, V, scale, err);
     else
         return RFX_ERR_BAD_ARG;
-    RFX_CHECK_LAUNCH();
     return 0;
 }
 
@@ -125,8 +159,8 @@ extern "C" int rfx_rmsnorm(const float* x, const void* delta, int delta_dt, floa
                                                  (int)smem);                                   \
             if (e != cudaSuccess) return (int)e;                                               \
         }                                                                                      \
-        rmsnorm_kernel<TD, TO><<<R_out, threads, smem, s>>>(x, (const TD*)delta, x_out, w,     \
-                                                            (TO*)out, rows, H, eps, w_offset); \
+        RFX_LAUNCH((rmsnorm_kernel<TD, TO>), R_out, threads, smem, s, x, (const TD*)delta, x_out, \
+                   w, (TO*)out, rows, H, eps, w_offset);                                       \
     } while (0)
     const bool dbf = delta && delta_dt == RFX_DT_BF16;
     if (out_dt == RFX_DT_BF16) {
@@ -139,7 +173,6 @@ extern "C" int rfx_rmsnorm(const float* x, const void* delta, int delta_dt, floa
         return RFX_ERR_BAD_ARG;
     }
 #undef RFX_NORM
-    RFX_CHECK_LAUNCH();
     return 0;
 }
 
@@ -150,13 +183,12 @@ extern "C" int rfx_swiglu(const void* gate_up, void* out, int dt, int R, int I, 
     int blocks = (int)((n + 255) / 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dt == RFX_DT_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, s>>>((const float*)gate_up, (float*)out, R, I);
+        RFX_LAUNCH(swiglu_kernel<float>, blocks, 256, 0, s, (const float*)gate_up, (float*)out, R, I);
     else if (dt == RFX_DT_BF16)
-        swiglu_kernel<__nv_bfloat16>
-            <<<blocks, 256, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, R, I);
+        RFX_LAUNCH(swiglu_kernel<__nv_bfloat16>, blocks, 256, 0, s, (const __nv_bfloat16*)gate_up,
+                   (__nv_bfloat16*)out, R, I);
     else
         return RFX_ERR_BAD_ARG;
-    RFX_CHECK_LAUNCH();
     return 0;
 }
 
@@ -166,12 +198,11 @@ extern "C" int rfx_add(float* a, const void* b, int b_dt, long long n, void* str
     int blocks = (int)((n + 255) / 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (b_dt == RFX_DT_F32)
-        add_kernel<float><<<blocks, 256, 0, s>>>(a, (const float*)b, (size_t)n);
+        RFX_LAUNCH(add_kernel<float>, blocks, 256, 0, s, a, (const float*)b, (size_t)n);
     else if (b_dt == RFX_DT_BF16)
-        add_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(a, (const __nv_bfloat16*)b, (size_t)n);
+        RFX_LAUNCH(add_kernel<__nv_bfloat16>, blocks, 256, 0, s, a, (const __nv_bfloat16*)b, (size_t)n);
     else
         return RFX_ERR_BAD_ARG;
-    RFX_CHECK_LAUNCH();
     return 0;
 }
 

@@ -88,9 +88,24 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     tc_fence_after_sync();
     const uint32_t tmem_d = tmem_base_smem;
 
+    // Let the next kernel's CTAs start as soon as every CTA of this one runs.
+    rfx::pdl_launch_dependents();
+
     if (warp == 0) {
         if (elect_one()) {
-            for (int i = 0; i < nkb; ++i) {
+            // The weights do not depend on the kernel before this one: fill the
+            // ring with weight tiles first, then wait for that kernel, then add
+            // the activation tiles.  HBM keeps streaming across the launch.
+            const int pre = min(nkb, stages);
+            for (int i = 0; i < pre; ++i) {
+                mbar_expect_tx(&full_bar[i], S::STAGE_BYTES);
+                tma_load_2d(tiles + (size_t)i * S::STAGE_BYTES, &map_w, &full_bar[i], (kb0 + i) * BK, n0);
+            }
+            rfx::pdl_wait();
+            for (int i = 0; i < pre; ++i)
+                tma_load_2d(tiles + (size_t)i * S::STAGE_BYTES + A_STAGE_BYTES, &map_x, &full_bar[i],
+                            (kb0 + i) * BK, r0);
+            for (int i = pre; i < nkb; ++i) {
                 const int s = i % stages;
                 const uint32_t ph = (i / stages) & 1;
                 if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
@@ -132,6 +147,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         __syncwarp();
     } else {
+        rfx::pdl_wait();         // y may still be read by an earlier kernel
         const int q = warp & 3;  // this warp may read TMEM lanes [32 q, 32 q + 32)
         const int m = q * 32 + lane;
         bool have = nkb > 0;
@@ -168,6 +184,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // every CTA of the cluster has its partial tile in shared memory; rank z
         // sums rows [z BM/ksplit, (z+1) BM/ksplit) over the ranks in rank order
         cg::cluster_group cluster = cg::this_cluster();
+        rfx::pdl_wait();
         cluster.sync();
         float* partial = reinterpret_cast<float*>(tiles);
         const int mw = BM / ksplit;
@@ -283,19 +300,8 @@ int launch(const void* x, const void* W, void* y, int R, int N, int K, int kspli
     auto kernel = gemm_wt_kernel<BN, TO>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(n_tiles, r_tiles, ks);
-    cfg.blockDim = dim3(THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = ks;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, kernel, *mw, mx, (TO*)y, R, N, K, ks, stages, err);
+    e = rfx::launch(kernel, dim3(n_tiles, r_tiles, ks), dim3(THREADS), smem, s, ks, *mw, mx, (TO*)y, R,
+                    N, K, ks, stages, err);
     if (e != cudaSuccess) return (int)e;
     return 0;
 }

@@ -20,6 +20,7 @@ gemm_f32_kernel(const float* __restrict__ x, const float* __restrict__ W, float*
                 int R, int N, int K) {
     __shared__ float xs[TK][TM + 1];
     __shared__ float ws[TK][TN + 1];
+    pdl_prologue();
     const int r0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;  // 16 x 16 threads, 4 x 4 outputs
     float acc[4][4];
@@ -71,6 +72,7 @@ template <int RT, typename TO>
 __global__ void __launch_bounds__(256)
 gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W,
                  TO* __restrict__ y, int R, int N, int K) {
+    pdl_prologue();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x * 8 + warp;
     if (n >= N) return;
@@ -120,8 +122,7 @@ extern "C" int rfx_gemm_f32(const float* x, const float* W, float* y, int R, int
     if (K <= 0) return RFX_ERR_BAD_ARG;
     dim3 grid((N + TN - 1) / TN, (R + TM - 1) / TM);
     if (grid.y > 65535) return RFX_ERR_UNSUPPORTED;
-    gemm_f32_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(x, W, y, R, N, K);
-    RFX_CHECK_LAUNCH();
+    RFX_LAUNCH(gemm_f32_kernel, grid, 256, 0, (cudaStream_t)stream, x, W, y, R, N, K);
     return 0;
 }
 
@@ -137,10 +138,10 @@ extern "C" int rfx_gemv_bf16(const void* x, const void* W, void* y, int y_dt, in
 #define RFX_GEMV(RT)                                                                             \
     do {                                                                                         \
         if (y_dt == RFX_DT_F32)                                                                  \
-            gemv_bf16_kernel<RT, float><<<blocks, 256, 0, s>>>(xb, wb, (float*)y, R, N, K);      \
+            RFX_LAUNCH((gemv_bf16_kernel<RT, float>), blocks, 256, 0, s, xb, wb, (float*)y, R, N, K); \
         else if (y_dt == RFX_DT_BF16)                                                            \
-            gemv_bf16_kernel<RT, __nv_bfloat16>                                                  \
-                <<<blocks, 256, 0, s>>>(xb, wb, (__nv_bfloat16*)y, R, N, K);                     \
+            RFX_LAUNCH((gemv_bf16_kernel<RT, __nv_bfloat16>), blocks, 256, 0, s, xb, wb,         \
+                       (__nv_bfloat16*)y, R, N, K);                                              \
         else                                                                                     \
             return RFX_ERR_BAD_ARG;                                                              \
     } while (0)
@@ -149,6 +150,5 @@ extern "C" int rfx_gemv_bf16(const void* x, const void* W, void* y, int y_dt, in
     else if (R <= 4) RFX_GEMV(4);
     else RFX_GEMV(8);
 #undef RFX_GEMV
-    RFX_CHECK_LAUNCH();
     return 0;
 }

@@ -29,6 +29,7 @@ qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restr
                 TO* __restrict__ q_out, TO* __restrict__ k_pages, TO* __restrict__ v_pages,
                 PagedKV cache, int nq, int nkv_in) {
     extern __shared__ float smem[];  // [warps][head_dim]
+    pdl_prologue();
     const int d = cache.head_dim;
     const int r = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
@@ -38,7 +39,8 @@ qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restr
     const int half = rotary_dim / 2;
     const int total = nq + 2 * nkv_in;
 
-    for (int hh = warp; hh < total; hh += nwarps) {
+    // one warp per (row, head): blockIdx.y walks the heads in groups of nwarps
+    for (int hh = blockIdx.y * nwarps + warp; hh < total; hh += gridDim.y * nwarps) {
         const TI* src = qkv + (size_t)r * row_stride + (size_t)hh * d;
         const bool is_q = hh < nq;
         const bool is_k = !is_q && hh < nq + nkv_in;
@@ -120,15 +122,16 @@ extern "C" int rfx_qkv_post(const void* qkv, int in_dt, int row_stride, const fl
     const int threads = 128;
     const size_t smem = (size_t)(threads / 32) * head_dim * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
+    const int head_blocks = (nq + 2 * nkv_in + threads / 32 - 1) / (threads / 32);
+    dim3 grid(R, head_blocks < 65535 ? head_blocks : 65535);
 #define RFX_POST(TI, TO)                                                                        \
-    qkv_post_kernel<TI, TO><<<R, threads, smem, s>>>(                                           \
-        (const TI*)qkv, row_stride, q_w, k_w, eps, w_offset, rope_denom, rotary_dim, row_pos,   \
-        row_slot, (TO*)q_out, (TO*)k_pages, (TO*)v_pages, cache, nq, nkv_in)
+    RFX_LAUNCH((qkv_post_kernel<TI, TO>), grid, threads, smem, s, (const TI*)qkv, row_stride, q_w, \
+               k_w, eps, w_offset, rope_denom, rotary_dim, row_pos, row_slot, (TO*)q_out,          \
+               (TO*)k_pages, (TO*)v_pages, cache, nq, nkv_in)
     if (in_dt == RFX_DT_F32 && out_dt == RFX_DT_F32) RFX_POST(float, float);
     else if (in_dt == RFX_DT_F32 && out_dt == RFX_DT_BF16) RFX_POST(float, __nv_bfloat16);
     else if (in_dt == RFX_DT_BF16 && out_dt == RFX_DT_BF16) RFX_POST(__nv_bfloat16, __nv_bfloat16);
     else return RFX_ERR_BAD_ARG;
 #undef RFX_POST
-    RFX_CHECK_LAUNCH();
     return 0;
 }

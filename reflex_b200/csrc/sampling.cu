@@ -2,7 +2,8 @@
 //
 //  * argmax: ties go to the highest index, as the reference's host argmax does
 //    (src/model/mod.rs:1371-1380: `max_by` keeps the last maximum).  NaN never
-//    wins.
+//    wins.  Two stages for a large vocabulary: 64 chunks a row, then the
+//    winners of the chunks.
 //  * sample: temperature softmax, optional top-k, optional top-p, then an
 //    inverse-CDF draw with a uniform number the caller supplies
 //    (src/sampling.rs:241-294).  p_i = exp((l_i - max) / T); top-k keeps the k
@@ -21,29 +22,37 @@ namespace {
 using namespace rfx;
 
 constexpr int SAMPLE_THREADS = 1024;
+constexpr int ARGMAX_CHUNKS = 64;
 
-__global__ void __launch_bounds__(1024)
-argmax_kernel(const float* __restrict__ logits, long long stride, int V, int* __restrict__ out) {
-    __shared__ float sv[32];
-    __shared__ int si[32];
-    const float* row = logits + (size_t)blockIdx.x * stride;
+__device__ __forceinline__ bool argmax_better(float v, int i, float bv, int bidx) {
+    return i >= 0 && v == v && (bidx < 0 || v > bv || (v == bv && i > bidx));
+}
+
+// Stage 1: block (row, chunk) scans its chunk of the row; stage 2 (chunks == 1
+// input) reduces the per-chunk winners.  `src_idx` is null in stage 1.
+__global__ void __launch_bounds__(256)
+argmax_kernel(const float* __restrict__ vals, const int* __restrict__ src_idx, long long stride,
+              int n, int chunk, float* __restrict__ out_val, int* __restrict__ out_idx) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    pdl_prologue();
+    const float* row = vals + (size_t)blockIdx.x * stride;
+    const int lo = blockIdx.y * chunk, hi = min(n, lo + chunk);
     float best = -INFINITY;
     int bi = -1;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
         const float v = row[i];
-        if (v >= best) {  // ascending i: a later equal value replaces
+        const int id = src_idx ? src_idx[(size_t)blockIdx.x * stride + i] : i;
+        if (argmax_better(v, id, best, bi)) {
             best = v;
-            bi = i;
+            bi = id;
         }
     }
-    auto better = [](float v, int i, float bv, int bidx) {
-        return i >= 0 && (bidx < 0 || v > bv || (v == bv && i > bidx));
-    };
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
         const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (better(ov, oi, best, bi)) {
+        if (argmax_better(ov, oi, best, bi)) {
             best = ov;
             bi = oi;
         }
@@ -57,11 +66,13 @@ argmax_kernel(const float* __restrict__ logits, long long stride, int V, int* __
     if (threadIdx.x == 0) {
         const int nw = (blockDim.x + 31) >> 5;
         for (int w = 1; w < nw; ++w)
-            if (better(sv[w], si[w], best, bi)) {
+            if (argmax_better(sv[w], si[w], best, bi)) {
                 best = sv[w];
                 bi = si[w];
             }
-        out[blockIdx.x] = bi < 0 ? 0 : bi;
+        const size_t o = (size_t)blockIdx.x * gridDim.y + blockIdx.y;
+        if (out_val) out_val[o] = best;
+        out_idx[o] = (bi < 0 && !out_val) ? 0 : bi;
     }
 }
 
@@ -158,6 +169,7 @@ sample_kernel(const float* __restrict__ logits, long long stride, int V,
     __shared__ int tie_base[SAMPLE_THREADS];
     __shared__ int sh_pick;
 
+    pdl_prologue();
     const int b = blockIdx.x;
     const float* row = logits + (size_t)b * stride;
     float* p = probs + (size_t)b * V;
@@ -280,12 +292,25 @@ sample_kernel(const float* __restrict__ logits, long long stride, int V,
 
 }  // namespace
 
+// `scratch` holds B * ARGMAX_CHUNKS floats followed by as many ints.
 extern "C" int rfx_argmax(const float* logits, long long stride, int B, int V, int* out,
-                          void* stream) {
+                          void* scratch, void* stream) {
     if (B <= 0) return 0;
     if (V <= 0) return RFX_ERR_BAD_ARG;
-    argmax_kernel<<<B, 1024, 0, (cudaStream_t)stream>>>(logits, stride, V, out);
-    RFX_CHECK_LAUNCH();
+    cudaStream_t s = (cudaStream_t)stream;
+    if (V <= 4096 || !scratch) {
+        RFX_LAUNCH(argmax_kernel, dim3(B, 1), 256, 0, s, logits, (const int*)nullptr, stride, V, V,
+                   (float*)nullptr, out);
+        return 0;
+    }
+    const int chunks = ARGMAX_CHUNKS;
+    const int chunk = (V + chunks - 1) / chunks;
+    float* pv = (float*)scratch;
+    int* pi = (int*)(pv + (size_t)B * chunks);
+    RFX_LAUNCH(argmax_kernel, dim3(B, chunks), 256, 0, s, logits, (const int*)nullptr, stride, V, chunk,
+               pv, pi);
+    RFX_LAUNCH(argmax_kernel, dim3(B, 1), 64, 0, s, (const float*)pv, (const int*)pi, (long long)chunks,
+               chunks, chunks, (float*)nullptr, out);
     return 0;
 }
 
@@ -296,8 +321,7 @@ extern "C" int rfx_sample(const float* logits, long long stride, int B, int V,
                           const float* uniform, float* probs, int* out, void* stream) {
     if (B <= 0) return 0;
     if (V <= 0 || !probs) return RFX_ERR_BAD_ARG;
-    sample_kernel<<<B, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(
-        logits, stride, V, temperature, top_k, top_p, uniform, probs, out);
-    RFX_CHECK_LAUNCH();
+    RFX_LAUNCH(sample_kernel, B, SAMPLE_THREADS, 0, (cudaStream_t)stream, logits, stride, V,
+               temperature, top_k, top_p, uniform, probs, out);
     return 0;
 }

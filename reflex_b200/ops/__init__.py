@@ -295,7 +295,8 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     B, V = logits.shape
     _chk(logits, "logits", torch.float32)
     out = torch.empty((B,), dtype=torch.int32, device=logits.device)
-    st = native.lib().rfx_argmax(logits.data_ptr(), V, B, V, out.data_ptr(), _stream())
+    scratch = torch.empty((B * 64 * 2,), dtype=torch.float32, device=logits.device)
+    st = native.lib().rfx_argmax(logits.data_ptr(), V, B, V, out.data_ptr(), scratch.data_ptr(), _stream())
     native.check(st, "argmax")
     return out
 

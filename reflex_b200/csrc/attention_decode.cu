@@ -27,6 +27,7 @@ using rfx::PagedKV;
 
 constexpr int PAGE = 64;
 constexpr int DEC_THREADS = 128;
+constexpr int DEC_STAGES = 3;  // pages in flight per CTA
 
 template <int D>
 __global__ void __launch_bounds__(DEC_THREADS)
@@ -38,10 +39,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     constexpr int LD = D + 8;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [16][LD]
-    __nv_bfloat16* kbuf = qs + 16 * LD;                               // [2][PAGE][LD]
-    __nv_bfloat16* vbuf = kbuf + 2 * PAGE * LD;                       // [2][PAGE][LD]
+    __nv_bfloat16* kbuf = qs + 16 * LD;                               // [STAGES][PAGE][LD]
+    __nv_bfloat16* vbuf = kbuf + DEC_STAGES * PAGE * LD;              // [STAGES][PAGE][LD]
 
-    rfx::pdl_prologue();
+    rfx::pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r = blockIdx.x;
     const int kvh = blockIdx.y / n_htiles, ht = blockIdx.y % n_htiles;
@@ -57,17 +58,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     const int pg0 = first_page + split * pps;
     const int pg1 = min(last_page + 1, pg0 + pps);
 
-    // the query heads of this tile; rows beyond the group are zero
-    for (int i = tid; i < 16 * (D / 8); i += DEC_THREADS) {
-        const int row = i / (D / 8), c = i % (D / 8);
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (row < nh) v = *reinterpret_cast<const uint4*>(q + ((size_t)r * nq + h0 + row) * D + c * 8);
-        *reinterpret_cast<uint4*>(qs + row * LD + c * 8) = v;
-    }
-
     const int* table = cache.page_table + (size_t)slot * cache.max_pages;
-    auto issue = [&](int pg, int buf) {
-        const int page = table[pg];
+    auto issue = [&](int pg, int page, int buf) {
         const size_t off = ((size_t)page * cache.n_kv_heads + kvh) * PAGE * D;
         const int valid = min(PAGE, pos + 1 - pg * PAGE);
         load_tile_async<D>(kbuf + buf * PAGE * LD, k_pages + off, PAGE, valid, tid, DEC_THREADS);
@@ -82,23 +74,57 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
 
-    if (pg0 < pg1) issue(pg0, 0);
-    for (int pg = pg0; pg < pg1; ++pg) {
-        const int buf = (pg - pg0) & 1;
-        if (pg + 1 < pg1) {
-            issue(pg + 1, buf ^ 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
+    // a ring of DEC_STAGES pages: one commit group per page, empty groups past the end
+    // The page id of a load is read one iteration before the load is issued, so
+    // the page-table read never stalls the loop.
+    int pages_first[DEC_STAGES];
+#pragma unroll
+    for (int i = 0; i < DEC_STAGES; ++i) pages_first[i] = pg0 + i < pg1 ? table[pg0 + i] : 0;
+    // Pages before the one that holds this row's own position were written by
+    // earlier steps: their loads start before the wait on the preceding kernel,
+    // which writes only the new key, value and query.  Positions, slots and the
+    // page table are the step's inputs, uploaded before the step's kernels.
+    int issued = 0;
+#pragma unroll
+    for (int i = 0; i < DEC_STAGES - 1; ++i) {
+        if (issued == i && pg0 + i < pg1 && pg0 + i < last_page) {
+            issue(pg0 + i, pages_first[i], i);
+            ++issued;
         }
-        __syncthreads();
+    }
+    rfx::pdl_wait();
+    // the query heads of this tile; rows beyond the group are zero
+    for (int i = tid; i < 16 * (D / 8); i += DEC_THREADS) {
+        const int row = i / (D / 8), c = i % (D / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < nh) v = *reinterpret_cast<const uint4*>(q + ((size_t)r * nq + h0 + row) * D + c * 8);
+        *reinterpret_cast<uint4*>(qs + row * LD + c * 8) = v;
+    }
+
+#pragma unroll
+    for (int i = 0; i < DEC_STAGES - 1; ++i) {
+        if (i >= issued) {
+            if (pg0 + i < pg1) issue(pg0 + i, pages_first[i], i);
+            else cp_async_commit();
+        }
+    }
+    int page_ahead = pages_first[DEC_STAGES - 1];
+    for (int pg = pg0; pg < pg1; ++pg) {
+        const int buf = (pg - pg0) % DEC_STAGES;
+        cp_async_wait<DEC_STAGES - 2>();  // page pg has landed (this thread's part)
+        __syncthreads();                  // everyone's part; and buffer (pg - 1) is free
+        const int nxt = pg + DEC_STAGES - 1;
+        const int page_now = page_ahead;
+        if (nxt + 1 < pg1) page_ahead = table[nxt + 1];
+        if (nxt < pg1) issue(nxt, page_now, (nxt - pg0) % DEC_STAGES);
+        else cp_async_commit();
         const int base = pg * PAGE;
         auto visible = [&](int key, int) { return base + key >= lo && base + key <= pos; };
         attend_tile<D, 2>(qs, kbuf + buf * PAGE * LD, vbuf + buf * PAGE * LD, warp * 16, scale_log2,
                           visible, m, l, acc);
-        __syncthreads();  // the buffer is free for the load after next
     }
-    if (pg0 >= pg1) __syncthreads();  // the query tile writes above
+    cp_async_wait<0>();
+    __syncthreads();  // all warps are done with the tiles before they are reused below
 
     // merge the four warps: each holds (m, l, acc) over its quarter of the keys
     float* red = reinterpret_cast<float*>(kbuf);       // [4][16][D] acc, then [4][16] m, [4][16] l
@@ -151,26 +177,48 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     }
 }
 
-// out[head] = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in order
+// out[head] = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in order.
+// The splits' weights 2^(m_s - M) / L are computed once into shared memory.
+constexpr int MAX_SPLITS = 64;
 __global__ void attention_combine_kernel(const float* __restrict__ partial,
                                          __nv_bfloat16* __restrict__ out, int D, int n_splits) {
+    __shared__ float wgt[MAX_SPLITS];
+    __shared__ float lw[MAX_SPLITS];
+    __shared__ float inv_l;
     rfx::pdl_prologue();
     const size_t head = blockIdx.x;
     const float* p = partial + head * n_splits * (D + 2);
-    float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, p[s * (D + 2) + D]);
-    float L = 0.0f;
-    for (int s = 0; s < n_splits; ++s) {
-        const float ms = p[s * (D + 2) + D];
-        if (ms != -INFINITY) L += p[s * (D + 2) + D + 1] * exp2f(ms - M);
+    if (threadIdx.x < 32) {
+        float ms[MAX_SPLITS / 32], ls[MAX_SPLITS / 32];
+        float M = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < MAX_SPLITS / 32; ++i) {
+            const int sidx = threadIdx.x + 32 * i;
+            ms[i] = sidx < n_splits ? p[sidx * (D + 2) + D] : -INFINITY;
+            ls[i] = sidx < n_splits ? p[sidx * (D + 2) + D + 1] : 0.0f;
+            M = fmaxf(M, ms[i]);
+        }
+        M = rfx::warp_max(M);
+#pragma unroll
+        for (int i = 0; i < MAX_SPLITS / 32; ++i) {
+            const float e = ms[i] == -INFINITY ? 0.0f : exp2f(ms[i] - M);
+            wgt[threadIdx.x + 32 * i] = e;
+            lw[threadIdx.x + 32 * i] = ls[i] * e;
+        }
+        __syncwarp();
+        if (threadIdx.x == 0) {  // in split order, by one lane: the same bits every time
+            float L = 0.0f;
+            for (int sidx = 0; sidx < n_splits; ++sidx) L += lw[sidx];
+            inv_l = 1.0f / L;
+        }
     }
+    __syncthreads();
+    const float inv = inv_l;
     for (int e = threadIdx.x; e < D; e += blockDim.x) {
         float A = 0.0f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float ms = p[s * (D + 2) + D];
-            if (ms != -INFINITY) A += p[s * (D + 2) + e] * exp2f(ms - M);
-        }
-        out[head * D + e] = __float2bfloat16_rn(A / L);
+#pragma unroll 4
+        for (int sidx = 0; sidx < n_splits; ++sidx) A += p[sidx * (D + 2) + e] * wgt[sidx];
+        out[head * D + e] = __float2bfloat16_rn(A * inv);
     }
 }
 
@@ -181,9 +229,9 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
     constexpr int LD = D + 8;
     const int g = nq / cache.n_kv_heads;
     const int n_htiles = (g + 15) / 16;
-    size_t smem = (size_t)(16 + 4 * PAGE) * LD * 2;
+    size_t smem = (size_t)(16 + 2 * DEC_STAGES * PAGE) * LD * 2;
     const size_t red = (size_t)(4 * 16 * D + 2 * 4 * 16) * 4;
-    if (red > (size_t)4 * PAGE * LD * 2) return RFX_ERR_UNSUPPORTED;
+    if (red > (size_t)2 * DEC_STAGES * PAGE * LD * 2) return RFX_ERR_UNSUPPORTED;
     auto kernel = attention_decode_kernel<D>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -211,6 +259,7 @@ extern "C" int rfx_attention_decode(const void* q, const void* k_pages, const vo
     if (R <= 0) return 0;
     if (page_size != PAGE || nkv <= 0 || nq % nkv != 0 || n_splits < 1) return RFX_ERR_BAD_ARG;
     if (n_splits > 1 && !partial) return RFX_ERR_BAD_ARG;
+    if (n_splits > MAX_SPLITS) return RFX_ERR_UNSUPPORTED;
     if (n_splits > 65535 || (long long)nkv * ((nq / nkv + 15) / 16) > 65535) return RFX_ERR_UNSUPPORTED;
     PagedKV cache{page_table, max_pages, page_size, nkv, head_dim};
     cudaStream_t s = (cudaStream_t)stream;

@@ -61,8 +61,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     }
 
     const int* table = cache.page_table + (size_t)slot * cache.max_pages;
-    auto issue = [&](int pg, int buf) {
-        const int page = table[pg];
+    auto issue = [&](int pg, int page, int buf) {
         const size_t off = ((size_t)page * cache.n_kv_heads + kvh) * PAGE * D;
         const int valid = min(PAGE, pos_last + 1 - pg * PAGE);
         load_tile_async<D>(kbuf + buf * PAGE * LD, k_pages + off, PAGE, valid, tid, PF_THREADS);
@@ -93,11 +92,15 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
 
     const int pg0 = lo_tile / PAGE, pg1 = pos_last / PAGE + 1;
-    issue(pg0, 0);
+    // page ids are read one iteration ahead of their loads
+    issue(pg0, table[pg0], 0);
+    int page_ahead = pg0 + 1 < pg1 ? table[pg0 + 1] : 0;
     for (int pg = pg0; pg < pg1; ++pg) {
         const int buf = (pg - pg0) & 1;
         if (pg + 1 < pg1) {
-            issue(pg + 1, buf ^ 1);
+            const int page_now = page_ahead;
+            if (pg + 2 < pg1) page_ahead = table[pg + 2];
+            issue(pg + 1, page_now, buf ^ 1);
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();

@@ -13,7 +13,11 @@ template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ out, int H, int V, float scale,
                              int* __restrict__ err) {
-    pdl_prologue();
+    // The first kernel of every step.  It does not let its dependents start
+    // early: kernels of this step may read, before their own wait, cache pages
+    // that earlier steps wrote, so no kernel of this step may run before every
+    // kernel of the step before has completed, which this kernel's wait ensures.
+    pdl_wait();
     const int r = blockIdx.x;
     const int id = ids[r];
     if (id < 0 || id >= V) {

@@ -293,6 +293,10 @@ int launch(const void* x, const void* W, void* y, int R, int N, int K, int kspli
     if (ks != 1 && ks != 2 && ks != 4 && ks != 8) return RFX_ERR_BAD_ARG;
     // two CTAs per SM: at most ~110 KB of stages each
     int stages = (110 * 1024) / S::STAGE_BYTES;
+    if (const char* e = getenv("REFLEX_B200_GEMM_STAGES")) {  // tuning aid
+        const int v = atoi(e);
+        if (v >= 2) stages = v;
+    }
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 2) stages = 2;
     if (ks > 1 && stages * S::STAGE_BYTES < BN * BM * 4) return RFX_ERR_UNSUPPORTED;

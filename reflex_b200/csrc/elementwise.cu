@@ -96,17 +96,19 @@ __global__ void rmsnorm_kernel(const float* x, const TD* __restrict__ delta,
     }
 }
 
-// out[r, i] = silu(gu[r, i]) * gu[r, I + i],  silu(g) = g / (1 + exp(-g))
-// (src/kernels_cuda/silu_and_mul.cu:7-23)
+// out[r, i] = silu(gate_i) * up_i,  silu(g) = g / (1 + exp(-g))
+// (src/kernels_cuda/silu_and_mul.cu:7-23).  A row of `gu` holds the gates in its
+// first half and the ups in its second, or (alternating) gate_i at 2i, up_i at 2i+1.
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int R, int I) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int R, int I,
+                              int alternating) {
     pdl_prologue();
     const size_t n = (size_t)R * I;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / I, c = i % I;
-        const float g = ld<T>(gu, r * 2 * I + c);
-        const float u = ld<T>(gu, r * 2 * I + I + c);
+        const float g = ld<T>(gu, r * 2 * I + (alternating ? 2 * c : c));
+        const float u = ld<T>(gu, r * 2 * I + (alternating ? 2 * c + 1 : I + c));
         st<T>(out, i, (g / (1.0f + expf(-g))) * u);
     }
 }
@@ -180,17 +182,19 @@ extern "C" int rfx_rmsnorm(const float* x, const void* delta, int delta_dt, floa
     return 0;
 }
 
-extern "C" int rfx_swiglu(const void* gate_up, void* out, int dt, int R, int I, void* stream) {
+extern "C" int rfx_swiglu(const void* gate_up, void* out, int dt, int R, int I, int alternating,
+                          void* stream) {
     if (R <= 0 || I <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t n = (size_t)R * I;
     int blocks = (int)((n + 255) / 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dt == RFX_DT_F32)
-        RFX_LAUNCH(swiglu_kernel<float>, blocks, 256, 0, s, (const float*)gate_up, (float*)out, R, I);
+        RFX_LAUNCH(swiglu_kernel<float>, blocks, 256, 0, s, (const float*)gate_up, (float*)out, R, I,
+                   alternating);
     else if (dt == RFX_DT_BF16)
         RFX_LAUNCH(swiglu_kernel<__nv_bfloat16>, blocks, 256, 0, s, (const __nv_bfloat16*)gate_up,
-                   (__nv_bfloat16*)out, R, I);
+                   (__nv_bfloat16*)out, R, I, alternating);
     else
         return RFX_ERR_BAD_ARG;
     return 0;

@@ -44,11 +44,17 @@ struct Shape {
     static constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
 };
 
-template <int BN, typename TO>
+// EPI 0: y = x W^T.  EPI 1: W's rows alternate gate, up (row 2j gate_j, row 2j+1
+// up_j) and y[r, j] = silu(gate_j) * up_j, so the SwiGLU activation costs no
+// launch and no round trip of the [R, 2I] intermediate
+// (src/kernels_cuda/silu_and_mul.cu:7-23 is the reference's separate kernel).
+__device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+
+template <int BN, typename TO, int EPI>
 __global__ void __launch_bounds__(THREADS)
 gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               TO* __restrict__ y, int R, int N, int K, int ksplit, int stages,
-               int* __restrict__ err) {
+               TO* __restrict__ y, int R, int N, int K, int ksplit, int stages, int bm,
+               int l2_ahead, int* __restrict__ err) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
     __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
@@ -60,7 +66,10 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                 ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BM, r0 = blockIdx.y * BN, z = blockIdx.z;
+    // a tile is `bm` <= 128 weight rows: the MMA always spans 128 rows of shared
+    // memory, rows past bm hold whatever was there and give output rows nobody reads
+    const int n0 = blockIdx.x * bm, r0 = blockIdx.y * BN, z = blockIdx.z;
+    const uint32_t stage_tx = (uint32_t)bm * BK * 2 + S::B_STAGE_BYTES;
     const int num_kb = (K + BK - 1) / BK;
     const int per = (num_kb + ksplit - 1) / ksplit;
     const int kb0 = z * per;
@@ -98,9 +107,13 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             // the activation tiles.  HBM keeps streaming across the launch.
             const int pre = min(nkb, stages);
             for (int i = 0; i < pre; ++i) {
-                mbar_expect_tx(&full_bar[i], S::STAGE_BYTES);
+                mbar_expect_tx(&full_bar[i], stage_tx);
                 tma_load_2d(tiles + (size_t)i * S::STAGE_BYTES, &map_w, &full_bar[i], (kb0 + i) * BK, n0);
             }
+            // ... and while still waiting, pull the next weight tiles into L2: the
+            // kernels before this one leave HBM idle for microseconds at a time
+            const int ahead = min(nkb, pre + l2_ahead);
+            for (int i = pre; i < ahead; ++i) tma_prefetch_l2_2d(&map_w, (kb0 + i) * BK, n0);
             rfx::pdl_wait();
             for (int i = 0; i < pre; ++i)
                 tma_load_2d(tiles + (size_t)i * S::STAGE_BYTES + A_STAGE_BYTES, &map_x, &full_bar[i],
@@ -115,7 +128,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 uint8_t* a = tiles + (size_t)s * S::STAGE_BYTES;
                 uint8_t* b = a + A_STAGE_BYTES;
-                mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
+                mbar_expect_tx(&full_bar[s], stage_tx);
                 tma_load_2d(a, &map_w, &full_bar[s], (kb0 + i) * BK, n0);
                 tma_load_2d(b, &map_x, &full_bar[s], (kb0 + i) * BK, r0);
             }
@@ -166,11 +179,19 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] = 0.0f;
             }
-            if (ksplit == 1) {
+            if (ksplit == 1 && EPI == 0) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int r = r0 + c * 16 + j;
-                    if (r < R && n0 + m < N) rfx::st<TO>(y, (size_t)r * N + n0 + m, v[j]);
+                    if (r < R && m < bm && n0 + m < N) rfx::st<TO>(y, (size_t)r * N + n0 + m, v[j]);
+                }
+            } else if (ksplit == 1) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float up = __shfl_down_sync(0xffffffffu, v[j], 1);  // the odd row above
+                    const int r = r0 + c * 16 + j;
+                    if ((m & 1) == 0 && r < R && m + 1 < bm && n0 + m + 1 < N)
+                        rfx::st<TO>(y, (size_t)r * (N / 2) + (n0 + m) / 2, silu_mul(v[j], up));
                 }
             } else {
 #pragma unroll
@@ -182,21 +203,40 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     if (ksplit > 1) {
         // every CTA of the cluster has its partial tile in shared memory; rank z
-        // sums rows [z BM/ksplit, (z+1) BM/ksplit) over the ranks in rank order
+        // sums its share of the tile's rows over the ranks in rank order
         cg::cluster_group cluster = cg::this_cluster();
         rfx::pdl_wait();
         cluster.sync();
         float* partial = reinterpret_cast<float*>(tiles);
-        const int mw = BM / ksplit;
-        for (int e = threadIdx.x; e < BN * mw; e += THREADS) {
-            const int rr = e / mw, mm = z * mw + e % mw;
-            float acc = 0.0f;
-            for (int p = 0; p < ksplit; ++p) {
-                const float* remote = cluster.map_shared_rank(partial, p);
-                acc += remote[rr * BM + mm];
+        int mw = (bm + ksplit - 1) / ksplit;
+        if (EPI == 1) mw = (mw + 1) & ~1;  // gate and up of a pair stay with one rank
+        if (EPI == 0) {
+            for (int e = threadIdx.x; e < BN * mw; e += THREADS) {
+                const int rr = e / mw, mm = z * mw + e % mw;
+                if (mm >= bm) continue;
+                float acc = 0.0f;
+                for (int p = 0; p < ksplit; ++p) {
+                    const float* remote = cluster.map_shared_rank(partial, p);
+                    acc += remote[rr * BM + mm];
+                }
+                const int r = r0 + rr;
+                if (r < R && n0 + mm < N) rfx::st<TO>(y, (size_t)r * N + n0 + mm, acc);
             }
-            const int r = r0 + rr;
-            if (r < R && n0 + mm < N) rfx::st<TO>(y, (size_t)r * N + n0 + mm, acc);
+        } else {
+            const int pw = mw / 2;
+            for (int e = threadIdx.x; e < BN * pw; e += THREADS) {
+                const int rr = e / pw, mm = z * mw + 2 * (e % pw);
+                if (mm + 1 >= bm) continue;
+                float g = 0.0f, u = 0.0f;
+                for (int p = 0; p < ksplit; ++p) {
+                    const float* remote = cluster.map_shared_rank(partial, p);
+                    g += remote[rr * BM + mm];
+                    u += remote[rr * BM + mm + 1];
+                }
+                const int r = r0 + rr;
+                if (r < R && n0 + mm + 1 < N)
+                    rfx::st<TO>(y, (size_t)r * (N / 2) + (n0 + mm) / 2, silu_mul(g, u));
+            }
         }
         cluster.sync();  // nobody leaves while its shared memory is still read
     }
@@ -274,49 +314,99 @@ int sm_count() {
     return n;
 }
 
-template <int BN, typename TO>
+int env_int(const char* name, int dflt) {
+    const char* e = getenv(name);
+    return e ? atoi(e) : dflt;
+}
+
+// How a product is cut into CTAs.  Streaming weights at HBM speed needs every SM
+// pulling all the time (one SM tops out near 55 GB/s), so the grid is made a
+// whole multiple of the SM count with equal work per CTA: `tiles` row tiles of
+// `bm` <= 128 weight rows (a tile need not be 128 rows: TMA boxes take any
+// height) times a K split of `ks` CTAs that form a cluster.  When no such cut
+// exists (small matrices) tiles are 128 rows and K is split while CTAs are few.
+struct Cut {
+    int bm, tiles, ks;
+};
+
+Cut choose_cut(int N, int r_tiles, int num_kb, int ks_req) {
+    if (ks_req > 0) return Cut{BM, (N + BM - 1) / BM, ks_req};
+    const int sms = sm_count();
+    const int cps_first = env_int("REFLEX_B200_GEMM_CPS", 0);  // tuning aid: CTAs per SM to try first
+    for (int pass = 0; pass < 2 && cps_first > 0; ++pass) {
+        const int c = cps_first ? (pass == 0 ? cps_first : 3 - cps_first) : (pass == 0 ? 1 : 2);
+        if (c < 1 || c > 2) continue;
+        int best_ks = 0, best_bm = 0, best_tiles = 0;
+        for (int ks = 1; ks <= 8; ks *= 2) {
+            const int total = sms * c;
+            if (total % (ks * r_tiles)) continue;
+            const int tiles = total / (ks * r_tiles);
+            const int bm = (N + tiles - 1) / tiles;
+            if (bm > BM || bm < 32 || num_kb < 4 * ks) continue;
+            if ((N + bm - 1) / bm != tiles) continue;  // the last tiles would be empty
+            if (bm > best_bm) {  // the tallest tile reuses each activation tile most
+                best_bm = bm;
+                best_ks = ks;
+                best_tiles = tiles;
+            }
+        }
+        if (best_ks) return Cut{best_bm, best_tiles, best_ks};
+    }
+    const int tiles = (N + BM - 1) / BM;
+    int ks = 1;
+    while (ks < 8 && tiles * r_tiles * ks * 2 <= 2 * sms && num_kb >= ks * 4) ks *= 2;
+    return Cut{BM, tiles, ks};
+}
+
+template <int BN, typename TO, int EPI>
 int launch(const void* x, const void* W, void* y, int R, int N, int K, int ksplit_req, int* err,
            cudaStream_t s) {
     using S = Shape<BN>;
-    const CUtensorMap* mw = cached_map(W, N, K, BM);
+    const int r_tiles = (R + BN - 1) / BN;
+    const int num_kb = (K + BK - 1) / BK;
+    Cut cut = choose_cut(N, r_tiles, num_kb, ksplit_req);
+    if (EPI == 1 && (cut.bm & 1)) {  // pairs must not straddle tiles
+        cut.bm += 1;
+        if (cut.bm > BM) return RFX_ERR_UNSUPPORTED;
+        cut.tiles = (N + cut.bm - 1) / cut.bm;
+    }
+    const int ks = cut.ks;
+    if (ks != 1 && ks != 2 && ks != 4 && ks != 8) return RFX_ERR_BAD_ARG;
+    const CUtensorMap* mw = cached_map(W, N, K, cut.bm);
     CUtensorMap mx;
     if (!mw || !make_map(&mx, x, R, K, BN)) return RFX_ERR_UNSUPPORTED;
-    const int n_tiles = (N + BM - 1) / BM, r_tiles = (R + BN - 1) / BN;
-    const int num_kb = (K + BK - 1) / BK;
-    // split K over a cluster while there are fewer CTAs than two per SM
-    int ks = 1;
-    if (ksplit_req > 0) {
-        ks = ksplit_req;
-    } else {
-        while (ks < 8 && n_tiles * r_tiles * ks * 2 <= 2 * sm_count() && num_kb >= ks * 4) ks *= 2;
-    }
-    if (ks != 1 && ks != 2 && ks != 4 && ks != 8) return RFX_ERR_BAD_ARG;
-    // two CTAs per SM: at most ~110 KB of stages each
-    int stages = (110 * 1024) / S::STAGE_BYTES;
-    if (const char* e = getenv("REFLEX_B200_GEMM_STAGES")) {  // tuning aid
-        const int v = atoi(e);
-        if (v >= 2) stages = v;
-    }
+    // A ring of about 72 KB: three CTAs fit an SM, so the kernels that follow
+    // (launched early, see common.cuh) are resident and prefetch their weights
+    // while this one runs; a deeper ring measured slower for that reason.
+    int stages = (env_int("REFLEX_B200_GEMM_SMEM_KB", 110) * 1024) / S::STAGE_BYTES;
+    if (stages < 3) stages = 3;
+    const int st_env = env_int("REFLEX_B200_GEMM_STAGES", 0);  // tuning aid
+    if (st_env >= 2) stages = st_env;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 2) stages = 2;
     if (ks > 1 && stages * S::STAGE_BYTES < BN * BM * 4) return RFX_ERR_UNSUPPORTED;
     const size_t smem = (size_t)stages * S::STAGE_BYTES + 1024;
-    auto kernel = gemm_wt_kernel<BN, TO>;
+    auto kernel = gemm_wt_kernel<BN, TO, EPI>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    e = rfx::launch(kernel, dim3(n_tiles, r_tiles, ks), dim3(THREADS), smem, s, ks, *mw, mx, (TO*)y, R,
-                    N, K, ks, stages, err);
+    // L2 prefetch before the dependency wait: up to a budget for the whole grid
+    const long long budget = (long long)env_int("REFLEX_B200_GEMM_L2PF_MB", 0) << 20;
+    const long long ctas = (long long)cut.tiles * r_tiles * ks;
+    int l2_ahead = (int)(budget / (ctas * cut.bm * BK * 2));
+    if (r_tiles > 1) l2_ahead = 0;  // prefill-sized calls are not bandwidth-bound
+    e = rfx::launch(kernel, dim3(cut.tiles, r_tiles, ks), dim3(THREADS), smem, s, ks, *mw, mx, (TO*)y, R,
+                    N, K, ks, stages, cut.bm, l2_ahead, err);
     if (e != cudaSuccess) return (int)e;
     return 0;
 }
 
-template <typename TO>
+template <typename TO, int EPI>
 int dispatch(const void* x, const void* W, void* y, int R, int N, int K, int ksplit, int* err,
              cudaStream_t s) {
-    if (R <= 16) return launch<16, TO>(x, W, y, R, N, K, ksplit, err, s);
-    if (R <= 32) return launch<32, TO>(x, W, y, R, N, K, ksplit, err, s);
-    if (R <= 64) return launch<64, TO>(x, W, y, R, N, K, ksplit, err, s);
-    return launch<128, TO>(x, W, y, R, N, K, ksplit, err, s);
+    if (R <= 16) return launch<16, TO, EPI>(x, W, y, R, N, K, ksplit, err, s);
+    if (R <= 32) return launch<32, TO, EPI>(x, W, y, R, N, K, ksplit, err, s);
+    if (R <= 64) return launch<64, TO, EPI>(x, W, y, R, N, K, ksplit, err, s);
+    return launch<128, TO, EPI>(x, W, y, R, N, K, ksplit, err, s);
 }
 
 }  // namespace
@@ -325,14 +415,23 @@ int dispatch(const void* x, const void* W, void* y, int R, int N, int K, int ksp
 // y float32 or bfloat16.  K must be a multiple of 8 and the pointers 16-byte
 // aligned (TMA).  ksplit: 0 = choose, else 1, 2, 4 or 8.  `err` is a device
 // word that receives a non-zero code if a bounded wait ran out.
+// epilogue 1: W's rows alternate gate/up, N is even, y is [R, N / 2] =
+// silu(gate) * up.
 extern "C" int rfx_gemm_bf16_tc(const void* x, const void* W, void* y, int y_dt, int R, int N,
-                                int K, int ksplit, int* err, void* stream) {
+                                int K, int ksplit, int epilogue, int* err, void* stream) {
     if (R <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0) return RFX_ERR_UNSUPPORTED;
+    if (epilogue != 0 && epilogue != 1) return RFX_ERR_BAD_ARG;
+    if (epilogue == 1 && (N & 1)) return RFX_ERR_BAD_ARG;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(W)) & 15) return RFX_ERR_BAD_ARG;
     if ((N + BM - 1) / BM > 2147483647 || (R + 127) / 128 > 65535) return RFX_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    if (y_dt == RFX_DT_F32) return dispatch<float>(x, W, y, R, N, K, ksplit, err, s);
-    if (y_dt == RFX_DT_BF16) return dispatch<__nv_bfloat16>(x, W, y, R, N, K, ksplit, err, s);
+    if (epilogue == 0) {
+        if (y_dt == RFX_DT_F32) return dispatch<float, 0>(x, W, y, R, N, K, ksplit, err, s);
+        if (y_dt == RFX_DT_BF16) return dispatch<__nv_bfloat16, 0>(x, W, y, R, N, K, ksplit, err, s);
+    } else {
+        if (y_dt == RFX_DT_F32) return dispatch<float, 1>(x, W, y, R, N, K, ksplit, err, s);
+        if (y_dt == RFX_DT_BF16) return dispatch<__nv_bfloat16, 1>(x, W, y, R, N, K, ksplit, err, s);
+    }
     return RFX_ERR_BAD_ARG;
 }

@@ -92,13 +92,15 @@ def add_(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return a
 
 
-def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
-    """[R, 2I] -> silu(gate) * up, [R, I]; gate is the first half of a row."""
+def swiglu(gate_up: torch.Tensor, alternating: bool = False) -> torch.Tensor:
+    """[R, 2I] -> silu(gate) * up, [R, I].  A row holds the gates in its first
+    half and the ups in its second, or (`alternating`) gate_i at 2i and up_i at
+    2i + 1."""
     R, two_i = gate_up.shape
     I = two_i // 2
     out = torch.empty((R, I), dtype=gate_up.dtype, device=gate_up.device)
     st = native.lib().rfx_swiglu(_chk(gate_up, "gate_up"), out.data_ptr(), dt_code(gate_up.dtype),
-                                 R, I, _stream())
+                                 R, I, 1 if alternating else 0, _stream())
     native.check(st, "swiglu")
     return out
 
@@ -127,15 +129,18 @@ def check_device_errors(device="cuda:0") -> None:
 
 
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.float32,
-            ksplit: int = 0) -> torch.Tensor:
-    """The tcgen05/TMA product y = x @ weight.T (bfloat16 in, float32 accumulate)."""
+            ksplit: int = 0, swiglu_pairs: bool = False) -> torch.Tensor:
+    """The tcgen05/TMA product y = x @ weight.T (bfloat16 in, float32 accumulate).
+    With `swiglu_pairs` the weight's rows alternate gate, up and the result is
+    silu(gate) * up, [R, N / 2]."""
     R, K = x.shape
     N = weight.shape[0]
     _chk(x, "x", torch.bfloat16)
     _chk(weight, "weight", torch.bfloat16)
-    y = torch.empty((R, N), dtype=out_dtype, device=x.device)
+    y = torch.empty((R, N // 2 if swiglu_pairs else N), dtype=out_dtype, device=x.device)
     st = native.lib().rfx_gemm_bf16_tc(x.data_ptr(), weight.data_ptr(), y.data_ptr(), dt_code(out_dtype),
-                                       R, N, K, ksplit, device_error_word(x.device).data_ptr(), _stream())
+                                       R, N, K, ksplit, 1 if swiglu_pairs else 0,
+                                       device_error_word(x.device).data_ptr(), _stream())
     native.check(st, f"gemm_bf16_tc (R={R}, N={N}, K={K})")
     return y
 
@@ -168,6 +173,16 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     if out_dtype == torch.float32:
         return torch.mm(x, weight.t(), out_dtype=torch.float32)
     return torch.mm(x, weight.t())
+
+
+def linear_swiglu(x: torch.Tensor, weight_pairs: torch.Tensor) -> torch.Tensor:
+    """silu(x @ gate.T) * (x @ up.T) for a weight whose rows alternate gate_j,
+    up_j; [R, I] in x's dtype.  For a few bfloat16 rows the activation is the
+    product kernel's epilogue; otherwise product, then the SwiGLU kernel."""
+    R, K = x.shape
+    if x.dtype == torch.bfloat16 and R <= GEMV_MAX_ROWS and K % 8 == 0:
+        return gemm_tc(x, weight_pairs, torch.bfloat16, swiglu_pairs=True)
+    return swiglu(linear(x, weight_pairs), alternating=True)
 
 
 # ----------------------------------------------------------------- attention

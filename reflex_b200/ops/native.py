@@ -24,10 +24,11 @@ _SIGNATURES = {
     "rfx_embed": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p],
     "rfx_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p, c_int,
                     c_void_p, c_int, c_int, c_void_p],
-    "rfx_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "rfx_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "rfx_add": [c_void_p, c_void_p, c_int, c_longlong, c_void_p],
     "rfx_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-    "rfx_gemm_bf16_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "rfx_gemm_bf16_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                         c_void_p],
     "rfx_gemv_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "rfx_qkv_post": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p, c_int,
                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,

@@ -2,9 +2,10 @@
 
 gate = x Wg^T, up = x Wu^T, act = gate / (1 + exp(-gate)) * up, out = act Wd^T
 (src/model/dense.rs:1476-1481, src/kernels_cuda/silu_and_mul.cu:7-23).  The
-gate and up weights are stacked into one [2I, H] matrix at load so that one
-product serves both, as the reference's decode path fuses them by kernel
-(src/kernels_cuda/gemv_fused.cu:143-203); stacking rows changes no output.
+gate and up weights are woven into one [2I, H] matrix at load, row 2j = gate_j
+and row 2j + 1 = up_j, so that one product serves both (the reference's decode
+path fuses them by kernel, src/kernels_cuda/gemv_fused.cu:143-203) and the
+activation can be that product's epilogue; reordering rows changes no output.
 """
 
 from __future__ import annotations
@@ -40,10 +41,10 @@ class SwiGLU:
         def dev(t):
             return t.to(device=self.device, dtype=self.dtype)
 
-        self.gate_up = torch.cat([dev(tensors["gate_proj"]), dev(tensors["up_proj"])], dim=0).contiguous()
+        g, u = dev(tensors["gate_proj"]), dev(tensors["up_proj"])
+        self.gate_up = torch.stack([g, u], dim=1).reshape(2 * g.shape[0], g.shape[1]).contiguous()
         self.down = dev(tensors["down_proj"]).contiguous()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        gu = ops.linear(x, self.gate_up)
-        act = ops.swiglu(gu)
+        act = ops.linear_swiglu(x, self.gate_up)
         return ops.linear(act, self.down, out_dtype=torch.float32)

@@ -63,6 +63,9 @@ def test_swiglu_embed_add(dtype):
     out = ops().swiglu(gu.to(DEV))
     a, b = gu[:, :333].double().numpy(), gu[:, 333:].double().numpy()
     assert relerr(out, a / (1 + np.exp(-a)) * b) < (1e-6 if dtype == torch.float32 else 5e-3)
+    out = ops().swiglu(gu.to(DEV), alternating=True)
+    a, b = gu[:, 0::2].double().numpy(), gu[:, 1::2].double().numpy()
+    assert relerr(out, a / (1 + np.exp(-a)) * b) < (1e-6 if dtype == torch.float32 else 5e-3)
     table = torch.randn(1000, 96, generator=g).to(dtype)
     ids = torch.tensor([999, 0, 17, 17, 500], dtype=torch.int32)
     flag = torch.zeros(1, dtype=torch.int32, device=DEV)
@@ -109,6 +112,24 @@ def test_gemm_tc_any_shape(R, N, K, out_dtype):
     ops().check_device_errors(DEV)
     simple = ops().gemv_simple(x.to(DEV), w.to(DEV), out_dtype)
     assert relerr(simple, ref) < tol
+
+
+@pytest.mark.parametrize("R,I,K", [(1, 64, 64), (5, 160, 96), (8, 12288, 4096), (64, 555, 80), (33, 2048, 4096)])
+def test_gemm_tc_with_the_swiglu_epilogue(R, I, K):
+    g = torch.Generator().manual_seed(R + I + K)
+    x = torch.randn(R, K, generator=g).bfloat16()
+    gate = (torch.randn(I, K, generator=g) * 0.08).bfloat16()
+    up = (torch.randn(I, K, generator=g) * 0.08).bfloat16()
+    ref = pm.swiglu(x.double().numpy(), gate.double().numpy(), up.double().numpy(), np.eye(I))
+    pairs = torch.stack([gate, up], dim=1).reshape(2 * I, K).contiguous()
+    for ks in (0, 1, 2, 4, 8):
+        if ks > 1 and (K + 63) // 64 < ks:
+            continue
+        y = ops().gemm_tc(x.to(DEV), pairs.to(DEV), torch.bfloat16, ksplit=ks, swiglu_pairs=True)
+        assert y.shape == (R, I)
+        assert relerr(y, ref) < 8e-3, ks
+    assert relerr(ops().linear_swiglu(x.to(DEV), pairs.to(DEV)), ref) < 8e-3
+    ops().check_device_errors(DEV)
 
 
 def test_gemm_tc_refuses_what_it_cannot_do():

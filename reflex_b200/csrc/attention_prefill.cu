@@ -41,7 +41,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = blockIdx.y, kvh = blockIdx.z;
     const int n_new = seq_new[seq];
-    const int q0 = blockIdx.x * bq;  // first query of the tile, within this step's rows
+    // Tiles late in a sequence see the most keys: they are handed out first, so
+    // the longest CTAs do not start last (src/kernels_cuda/attention_tiled.cuh
+    // orders its row tiles the same way).
+    const int q0 = (gridDim.x - 1 - blockIdx.x) * bq;  // first query of the tile, within this step's rows
     if (q0 >= n_new) return;
     const int g = nq / cache.n_kv_heads;
     const int slot = seq_slot[seq], start = seq_start[seq], row0 = seq_row0[seq];

@@ -113,6 +113,53 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     }
 }
 
+// bfloat16, I a multiple of 8: eight outputs a thread, 16-byte loads and stores
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu,
+                                     __nv_bfloat16* __restrict__ out, int R, int I, int alternating) {
+    pdl_prologue();
+    const size_t n8 = (size_t)R * (I / 8);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / (I / 8), c = (i % (I / 8)) * 8;
+        const __nv_bfloat16* row = gu + r * 2 * I;
+        float g[8], u[8];
+        if (alternating) {
+            const uint4 a = *reinterpret_cast<const uint4*>(row + 2 * c);
+            const uint4 b = *reinterpret_cast<const uint4*>(row + 2 * c + 8);
+            const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+            const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 fa = __bfloat1622float2(pa[j]), fb = __bfloat1622float2(pb[j]);
+                g[j] = fa.x;
+                u[j] = fa.y;
+                g[4 + j] = fb.x;
+                u[4 + j] = fb.y;
+            }
+        } else {
+            const uint4 a = *reinterpret_cast<const uint4*>(row + c);
+            const uint4 b = *reinterpret_cast<const uint4*>(row + I + c);
+            const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+            const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 fa = __bfloat1622float2(pa[j]), fb = __bfloat1622float2(pb[j]);
+                g[2 * j] = fa.x;
+                g[2 * j + 1] = fa.y;
+                u[2 * j] = fb.x;
+                u[2 * j + 1] = fb.y;
+            }
+        }
+        uint4 o;
+        __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            po[j] = __floats2bfloat162_rn((g[2 * j] / (1.0f + expf(-g[2 * j]))) * u[2 * j],
+                                          (g[2 * j + 1] / (1.0f + expf(-g[2 * j + 1]))) * u[2 * j + 1]);
+        *reinterpret_cast<uint4*>(out + r * I + c) = o;
+    }
+}
+
 // y[i] = a[i] + b[i] in 32-bit (src/kernels_cuda/elementwise.cu:8-24)
 template <typename T>
 __global__ void add_kernel(float* __restrict__ a, const T* __restrict__ b, size_t n) {
@@ -125,9 +172,9 @@ __global__ void add_kernel(float* __restrict__ a, const T* __restrict__ b, size_
 // A function of H alone, so that a row's sum of squares is reduced in the same
 // order whatever the batch.
 int norm_threads(int H) {
-    int t = ((H + 3) / 4 + 31) / 32 * 32;
+    int t = ((H + 15) / 16 + 31) / 32 * 32;  // about four 16-byte loads a thread
     if (t < 32) t = 32;
-    if (t > 1024) t = 1024;
+    if (t > 256) t = 256;
     return t;
 }
 
@@ -192,7 +239,13 @@ extern "C" int rfx_swiglu(const void* gate_up, void* out, int dt, int R, int I, 
     if (dt == RFX_DT_F32)
         RFX_LAUNCH(swiglu_kernel<float>, blocks, 256, 0, s, (const float*)gate_up, (float*)out, R, I,
                    alternating);
-    else if (dt == RFX_DT_BF16)
+    else if (dt == RFX_DT_BF16 && I % 8 == 0 &&
+             ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+        int b8 = (int)((n / 8 + 255) / 256);
+        if (b8 > 148 * 16) b8 = 148 * 16;
+        RFX_LAUNCH(swiglu_bf16x8_kernel, b8, 256, 0, s, (const __nv_bfloat16*)gate_up,
+                   (__nv_bfloat16*)out, R, I, alternating);
+    } else if (dt == RFX_DT_BF16)
         RFX_LAUNCH(swiglu_kernel<__nv_bfloat16>, blocks, 256, 0, s, (const __nv_bfloat16*)gate_up,
                    (__nv_bfloat16*)out, R, I, alternating);
     else

@@ -20,15 +20,16 @@ using namespace rfx;
 
 constexpr int MAX_PER_LANE = 16;  // head_dim <= 512
 
-template <typename TI, typename TO>
-__global__ void __launch_bounds__(128)
+// PER: elements of a head vector per lane, head_dim <= 32 * PER
+template <typename TI, typename TO, int PER>
+__global__ void __launch_bounds__(256)
 qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restrict__ q_w,
                 const float* __restrict__ k_w, float eps, float w_offset,
                 const float* __restrict__ rope_denom, int rotary_dim,
                 const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                 TO* __restrict__ q_out, TO* __restrict__ k_pages, TO* __restrict__ v_pages,
                 PagedKV cache, int nq, int nkv_in) {
-    extern __shared__ float smem[];  // [warps][head_dim]
+    extern __shared__ float smem[];  // [warps][head_dim], then cos[half], sin[half]
     pdl_prologue();
     const int d = cache.head_dim;
     const int r = blockIdx.x;
@@ -38,6 +39,16 @@ qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restr
     float* buf = smem + warp * d;
     const int half = rotary_dim / 2;
     const int total = nq + 2 * nkv_in;
+    // the row's rotation, once for all heads of the block
+    float* cs_tab = smem + nwarps * d;
+    float* sn_tab = cs_tab + half;
+    if (rope_denom != nullptr) {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float theta = (float)pos / rope_denom[i];
+            sincosf(theta, &sn_tab[i], &cs_tab[i]);
+        }
+    }
+    __syncthreads();
 
     // one warp per (row, head): blockIdx.y walks the heads in groups of nwarps
     for (int hh = blockIdx.y * nwarps + warp; hh < total; hh += gridDim.y * nwarps) {
@@ -56,10 +67,10 @@ qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restr
             for (int e = lane; e < d; e += 32) st<TO>(dst, e, ld<TI>(src, e));
             continue;
         }
-        float v[MAX_PER_LANE];
+        float v[PER];
         float ss = 0.0f;
 #pragma unroll
-        for (int i = 0; i < MAX_PER_LANE; ++i) {
+        for (int i = 0; i < PER; ++i) {
             const int e = i * 32 + lane;
             v[i] = e < d ? ld<TI>(src, e) : 0.0f;
             ss = fmaf(v[i], v[i], ss);
@@ -68,14 +79,14 @@ qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restr
         if (w) {
             const float rinv = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);
 #pragma unroll
-            for (int i = 0; i < MAX_PER_LANE; ++i) {
+            for (int i = 0; i < PER; ++i) {
                 const int e = i * 32 + lane;
                 if (e < d) v[i] = (v[i] * rinv) * (w_offset + w[e]);
             }
         }
         if (rope_denom == nullptr || half == 0) {
 #pragma unroll
-            for (int i = 0; i < MAX_PER_LANE; ++i) {
+            for (int i = 0; i < PER; ++i) {
                 const int e = i * 32 + lane;
                 if (e < d) st<TO>(dst, e, v[i]);
             }
@@ -83,21 +94,19 @@ qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restr
         }
         __syncwarp();
 #pragma unroll
-        for (int i = 0; i < MAX_PER_LANE; ++i) {
+        for (int i = 0; i < PER; ++i) {
             const int e = i * 32 + lane;
             if (e < d) buf[e] = v[i];
         }
         __syncwarp();
 #pragma unroll
-        for (int i = 0; i < MAX_PER_LANE; ++i) {
+        for (int i = 0; i < PER; ++i) {
             const int e = i * 32 + lane;
             if (e >= d) break;
             float o = v[i];
             if (e < rotary_dim) {
                 const int fi = e < half ? e : e - half;
-                const float theta = (float)pos / rope_denom[fi];
-                float sn, cs;
-                sincosf(theta, &sn, &cs);
+                const float sn = sn_tab[fi], cs = cs_tab[fi];
                 if (e < half) o = v[i] * cs - buf[e + half] * sn;
                 else o = buf[e - half] * sn + v[i] * cs;
             }
@@ -119,19 +128,28 @@ extern "C" int rfx_qkv_post(const void* qkv, int in_dt, int row_stride, const fl
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return RFX_ERR_BAD_ARG;
     if (nkv_in != 0 && nkv_in != nkv) return RFX_ERR_BAD_ARG;
     PagedKV cache{page_table, max_pages, page_size, nkv, head_dim};
-    const int threads = 128;
-    const size_t smem = (size_t)(threads / 32) * head_dim * sizeof(float);
+    const int threads = 256;  // eight heads a block
+    const size_t smem = ((size_t)(threads / 32) * head_dim + rotary_dim) * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
     const int head_blocks = (nq + 2 * nkv_in + threads / 32 - 1) / (threads / 32);
     dim3 grid(R, head_blocks < 65535 ? head_blocks : 65535);
-#define RFX_POST(TI, TO)                                                                        \
-    RFX_LAUNCH((qkv_post_kernel<TI, TO>), grid, threads, smem, s, (const TI*)qkv, row_stride, q_w, \
-               k_w, eps, w_offset, rope_denom, rotary_dim, row_pos, row_slot, (TO*)q_out,          \
+#define RFX_POST_P(TI, TO, P)                                                                  \
+    RFX_LAUNCH((qkv_post_kernel<TI, TO, P>), grid, threads, smem, s, (const TI*)qkv, row_stride,   \
+               q_w, k_w, eps, w_offset, rope_denom, rotary_dim, row_pos, row_slot, (TO*)q_out,     \
                (TO*)k_pages, (TO*)v_pages, cache, nq, nkv_in)
+#define RFX_POST(TI, TO)                                  \
+    do {                                                  \
+        if (head_dim <= 32) RFX_POST_P(TI, TO, 1);        \
+        else if (head_dim <= 64) RFX_POST_P(TI, TO, 2);   \
+        else if (head_dim <= 128) RFX_POST_P(TI, TO, 4);  \
+        else if (head_dim <= 256) RFX_POST_P(TI, TO, 8);  \
+        else RFX_POST_P(TI, TO, 16);                      \
+    } while (0)
     if (in_dt == RFX_DT_F32 && out_dt == RFX_DT_F32) RFX_POST(float, float);
     else if (in_dt == RFX_DT_F32 && out_dt == RFX_DT_BF16) RFX_POST(float, __nv_bfloat16);
     else if (in_dt == RFX_DT_BF16 && out_dt == RFX_DT_BF16) RFX_POST(__nv_bfloat16, __nv_bfloat16);
     else return RFX_ERR_BAD_ARG;
 #undef RFX_POST
+#undef RFX_POST_P
     return 0;
 }

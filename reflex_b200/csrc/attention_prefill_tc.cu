@@ -1,0 +1,459 @@
+// Prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
+//
+// Same problem as attention_prefill.cu (causal, optionally windowed
+// grouped-query attention of a packed batch over the paged cache; a CTA =
+// one sequence, one kv head, 128 rows that are (position, head of the group)
+// pairs), for head sizes 64 and 128.  Per page of 64 keys:
+//   S = Q K^T      tcgen05.mma, Q [128 x D] and the K page [64 x D] in shared
+//                  memory (TMA, 128-byte swizzle), S [128 x 64] float32 in TMEM;
+//   softmax        four warps, one thread per row: tcgen05.ld its row of S,
+//                  mask, running max and sum in 32-bit, P as bfloat16 back into
+//                  TMEM over the columns S came from (tcgen05.st);
+//   O += P V       tcgen05.mma with P from TMEM and the V page as the MN-major
+//                  shared-memory operand, O [128 x D] accumulating in TMEM.
+// The running maximum is a reference, not the exact maximum: it is raised (and
+// the row of O rescaled through tcgen05.ld / tcgen05.st) only when a page's
+// maximum passes it by more than 2^8, so rescaling is rare; probabilities are
+// 2^(s - reference) <= 2^8 and the final division by the sum, taken with the
+// same reference, gives the exact softmax.  S and P are double-buffered so the
+// tensor core works on page j + 1 while the softmax warps are on page j.  Warp 0 issues TMA loads, warp 1 issues
+// MMAs, warps 2..5 are the softmax rows.  Every mbarrier wait is bounded; on a
+// timeout the kernel records it, stops, frees its tensor memory and returns.
+// The reference's tiled kernel is the CUDA-core ancestor
+// (src/kernels_cuda/attention_tiled.cuh:73-296).
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+#include "paged.cuh"
+#include "sm100.cuh"
+
+namespace {
+
+using namespace sm100;
+using rfx::PagedKV;
+
+constexpr int PAGE = 64;
+constexpr int ROWS = 128;
+constexpr int THREADS = 192;
+constexpr int KV_STAGES = 2;  // with 97 KB of shared memory two CTAs share an SM
+
+// 3-D tile load (x innermost)
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                            int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)),
+          "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+// 2^x, hardware approximation (about 2 ulp; the result is rounded to bfloat16)
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void fence_async_proxy() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// MN-major operand, 128-byte swizzle: 64 elements contiguous per k-row, k-rows
+// 128 bytes apart, groups of 8 k-rows `sbo` bytes apart, blocks of 64 elements
+// along MN `lbo` bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)(lbo >> 4) << 16;
+    d |= (uint64_t)(sbo >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// kind::f16, A bfloat16 K-major, B bfloat16 MN-major, D float32
+__host__ __device__ constexpr uint32_t idesc_b_mn(int M, int N) {
+    return umma_idesc_bf16(M, N) | (1u << 16);
+}
+
+struct Smem {
+    // all tiles 1024-byte aligned
+    static constexpr int q_bytes(int D) { return ROWS * D * 2; }
+    static constexpr int kv_bytes(int D) { return PAGE * D * 2; }
+    static constexpr int total(int D) { return q_bytes(D) + 2 * KV_STAGES * kv_bytes(D) + 1024; }
+};
+
+template <int D>
+__global__ void __launch_bounds__(THREADS)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+                            const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, PagedKV cache,
+                            const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
+                            const int* __restrict__ seq_new, const int* __restrict__ seq_row0,
+                            __nv_bfloat16* __restrict__ out, int nq, int bq, int window,
+                            float scale_log2, int* __restrict__ err) {
+    static_assert(D == 64 || D == 128, "head sizes 64 and 128");
+    constexpr int KB = D / 64;                 // 64-column blocks of a row
+    constexpr int KV_BYTES = PAGE * D * 2;
+    constexpr uint32_t TMEM_COLS = 256;
+    // S: 2 x 64 columns (P_b, 32 columns of packed bfloat16, overwrites the start
+    // of S_b once the row has read it), then O: D columns
+    constexpr uint32_t S_COL = 0, O_COL = 128;
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t q_full, k_full[KV_STAGES], k_empty[KV_STAGES], v_full[KV_STAGES],
+        v_empty[KV_STAGES], s_full[2], p_full[2], o_full;
+    __shared__ uint32_t tmem_base_smem;
+    __shared__ int abort_flag;
+
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_tile = base;
+    uint8_t* k_ring = q_tile + ROWS * D * 2;
+    uint8_t* v_ring = k_ring + KV_STAGES * KV_BYTES;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seq = blockIdx.y, kvh = blockIdx.z;
+    const int n_new = seq_new[seq];
+    const int q0 = (gridDim.x - 1 - blockIdx.x) * bq;  // the longest tiles first
+    const bool active = q0 < n_new;
+    const int g = nq / cache.n_kv_heads;
+    const int slot = seq_slot[seq], start = seq_start[seq], row0 = seq_row0[seq];
+    const int n_pos = active ? min(bq, n_new - q0) : 0;
+    const int n_rows = n_pos * g;
+    const int pos_first = start + q0, pos_last = pos_first + n_pos - 1;
+    const int lo_tile = (window > 0 && pos_first + 1 > window) ? pos_first + 1 - window : 0;
+    const int pg0 = lo_tile / PAGE, pg1 = active ? pos_last / PAGE + 1 : 0;
+    const int n_pages = active ? pg1 - pg0 : 0;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&q_full, 1);
+        for (int i = 0; i < KV_STAGES; ++i) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&k_empty[i], 1);
+            mbar_init(&v_full[i], 1);
+            mbar_init(&v_empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&s_full[i], 1);
+            mbar_init(&p_full[i], 4);
+        }
+        mbar_init(&o_full, 1);
+        abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(&tmem_base_smem, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = tmem_base_smem;
+    rfx::pdl_prologue();  // q and this step's keys and values come from the kernel before
+
+    if (!active) {
+        // nothing to do for this tile; fall through to the teardown
+    } else if (warp == 0) {
+        if (elect_one()) {
+            const int* table = cache.page_table + (size_t)slot * cache.max_pages;
+            mbar_expect_tx(&q_full, (uint32_t)(bq * g * 128 * KB));
+            for (int kb = 0; kb < KB; ++kb)
+                tma_load_3d(q_tile + kb * ROWS * 128, &map_q, &q_full, kb * 64, kvh * g, row0 + q0);
+            for (int j = 0; j < n_pages; ++j) {
+                const int s = j % KV_STAGES;
+                const uint32_t ph = (j / KV_STAGES) & 1;
+                const int page = table[pg0 + j];
+                const int y = (page * cache.n_kv_heads + kvh) * PAGE;
+                if (!mbar_wait(&k_empty[s], ph ^ 1)) { atomicExch(err, 11); abort_flag = 1; break; }
+                mbar_expect_tx(&k_full[s], KV_BYTES);
+                for (int kb = 0; kb < KB; ++kb)
+                    tma_load_2d(k_ring + s * KV_BYTES + kb * PAGE * 128, &map_k, &k_full[s], kb * 64, y);
+                if (!mbar_wait(&v_empty[s], ph ^ 1)) { atomicExch(err, 12); abort_flag = 1; break; }
+                mbar_expect_tx(&v_full[s], KV_BYTES);
+                for (int kb = 0; kb < KB; ++kb)
+                    tma_load_2d(v_ring + s * KV_BYTES + kb * PAGE * 128, &map_v, &v_full[s], kb * 64, y);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (elect_one()) {
+            constexpr uint32_t idesc_s = umma_idesc_bf16(ROWS, PAGE);  // S: N = 64 keys
+            constexpr uint32_t idesc_o = idesc_b_mn(ROWS, D);          // O: N = D, V is MN-major
+            bool ok = mbar_wait(&q_full, 0);
+            if (!ok) { atomicExch(err, 13); abort_flag = 1; }
+            auto pv = [&](int i) -> bool {
+                const int b = i & 1, s = i % KV_STAGES;
+                const uint32_t ph2 = (i >> 1) & 1, phs = (i / KV_STAGES) & 1;
+                // P_i is delivered after any rescaling of O that page i asked for
+                if (!mbar_wait(&p_full[b], ph2)) { atomicExch(err, 14); return false; }
+                if (!mbar_wait(&v_full[s], phs)) { atomicExch(err, 15); return false; }
+                tc_fence_after_sync();
+                const uint32_t va = smem_u32(v_ring + s * KV_BYTES);
+#pragma unroll
+                for (int k = 0; k < PAGE / 16; ++k) {  // 16 keys per MMA: 8 packed columns of P
+                    const uint64_t db = umma_desc_mn_sw128(va + k * 16 * 128, PAGE * 128, 1024);
+                    umma_bf16_ts(tmem + O_COL, tmem + S_COL + b * PAGE + k * 8, db, idesc_o,
+                                 (i > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&v_empty[s]);
+                umma_commit(&o_full);
+                return true;
+            };
+            for (int j = 0; j < n_pages && ok; ++j) {
+                const int b = j & 1, s = j % KV_STAGES;
+                const uint32_t phs = (j / KV_STAGES) & 1;
+                // S_j reuses the columns of S_{j-2} and P_{j-2}: PV_{j-2} was issued
+                // before this and the tensor core runs MMAs in issue order
+                if (!mbar_wait(&k_full[s], phs)) { atomicExch(err, 18); ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t qa = smem_u32(q_tile), ka = smem_u32(k_ring + s * KV_BYTES);
+#pragma unroll
+                for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint64_t da = umma_desc_k_sw128(qa + kb * ROWS * 128) + 2 * k;
+                        const uint64_t db = umma_desc_k_sw128(ka + kb * PAGE * 128) + 2 * k;
+                        umma_bf16(tmem + S_COL + b * PAGE, da, db, idesc_s, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                umma_commit(&k_empty[s]);
+                umma_commit(&s_full[b]);
+                if (j > 0) ok = pv(j - 1);
+            }
+            if (ok && n_pages > 0) ok = pv(n_pages - 1);
+            if (!ok) abort_flag = 1;
+        }
+        __syncwarp();
+    } else {
+        // softmax rows: this thread owns row t (TMEM lane t) of the tile
+        const int qd = warp & 3;
+        const int t = qd * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(qd * 32) << 16;
+        const bool row_valid = t < n_rows;
+        const int row_p = t / g, row_h = t % g;
+        const int row_pos = row_valid ? pos_first + row_p : -1;
+        const int row_lo = (window > 0 && row_pos + 1 > window) ? row_pos + 1 - window : 0;
+        const int lo_last = (window > 0 && pos_last + 1 > window) ? pos_last + 1 - window : 0;
+        constexpr float RAISE = 8.0f;  // raise the reference maximum only past 2^8
+        float m = -INFINITY, l = 0.0f;
+        bool ok = true;
+
+        for (int j = 0; j < n_pages && ok; ++j) {
+            const int b = j & 1;
+            const uint32_t ph2 = (j >> 1) & 1;
+            if (!mbar_wait(&s_full[b], ph2)) { atomicExch(err, 22); ok = false; break; }
+            tc_fence_after_sync();
+            uint32_t sr[PAGE];
+#pragma unroll
+            for (int c = 0; c < PAGE / 16; ++c)
+                tmem_ld_16_nowait(tmem + lane_addr + S_COL + b * PAGE + c * 16, sr + c * 16);
+            tmem_ld_wait();
+
+            const int basej = (pg0 + j) * PAGE;
+            // every key of the page visible to every valid row of the tile: no compares
+            const bool all_visible = basej + PAGE - 1 <= pos_first && basej >= lo_last && n_rows == ROWS;
+            // four independent chains each for the maximum and the sum: one warp per
+            // scheduler has nothing else to hide a dependent chain's latency with
+            float s[PAGE];
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (all_visible) {
+#pragma unroll
+                for (int c = 0; c < PAGE; ++c) {
+                    s[c] = __uint_as_float(sr[c]) * scale_log2;
+                    mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < PAGE; ++c) {
+                    const int key = basej + c;
+                    s[c] = (key <= row_pos && key >= row_lo) ? __uint_as_float(sr[c]) * scale_log2 : -INFINITY;
+                    mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+                }
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // the reference maximum moves only when it must
+            float corr = 1.0f;
+            const bool raise = mx > m + RAISE || (m == -INFINITY && mx != -INFINITY);
+            if (raise) {
+                corr = (m == -INFINITY) ? 0.0f : ex2(m - mx);
+                m = mx;
+                l *= corr;
+            }
+            // rows that have seen no key yet: every s is -inf, shift by 0 gives p = 0
+            const float shift = (m == -INFINITY) ? 0.0f : m;
+            float rs4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            uint32_t packed[PAGE / 2];
+#pragma unroll
+            for (int c = 0; c < PAGE; c += 2) {
+                const float e0 = ex2(s[c] - shift);
+                const float e1 = ex2(s[c + 1] - shift);
+                rs4[(c >> 1) & 3] += e0 + e1;
+                __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+                packed[c / 2] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+
+            // rescale this row of O if its reference moved (whole warp together:
+            // the TMEM accesses are warp-wide; lanes that did not move scale by 1)
+            if (j > 0 && __any_sync(0xffffffffu, raise)) {
+                if (!mbar_wait(&o_full, (uint32_t)((j - 1) & 1))) { atomicExch(err, 21); ok = false; break; }
+                tc_fence_after_sync();
+#pragma unroll
+                for (int c = 0; c < D / 16; ++c) {
+                    uint32_t o[16];
+                    tmem_ld_16_nowait(tmem + lane_addr + O_COL + c * 16, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * corr);
+                    tmem_st_16(tmem + lane_addr + O_COL + c * 16, o);
+                }
+                tmem_st_wait();
+                tc_fence_before_sync();
+            }
+
+            // row t of P into TMEM, over the columns its S came from
+            tmem_st_16(tmem + lane_addr + S_COL + b * PAGE, packed);
+            tmem_st_16(tmem + lane_addr + S_COL + b * PAGE + 16, packed + 16);
+            tmem_st_wait();
+            // the last page may hold keys past this tile's last position whose
+            // value rows were never written: zero them, 0 * NaN would not be 0
+            const int valid_keys = pos_last + 1 - basej;
+            if (valid_keys < PAGE) {
+                const int sidx = j % KV_STAGES;
+                if (!mbar_wait(&v_full[sidx], (j / KV_STAGES) & 1)) { atomicExch(err, 24); ok = false; break; }
+                uint8_t* vt = v_ring + sidx * KV_BYTES;
+                for (int i = t; i < (PAGE - valid_keys) * KB * 8; i += ROWS) {
+                    const int rrow = valid_keys + i / (KB * 8), rem = i % (KB * 8);
+                    *reinterpret_cast<uint4*>(vt + (rem / 8) * PAGE * 128 + rrow * 128 + (rem % 8) * 16) =
+                        make_uint4(0, 0, 0, 0);
+                }
+            }
+            if (valid_keys < PAGE) fence_async_proxy();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[b]);
+        }
+        if (ok && n_pages > 0) {
+            if (!mbar_wait(&o_full, (uint32_t)((n_pages - 1) & 1))) { atomicExch(err, 25); ok = false; }
+        }
+        if (ok && n_pages > 0) {
+            tc_fence_after_sync();
+            const float inv = 1.0f / l;
+            __nv_bfloat16* o = out + ((size_t)(row0 + q0 + row_p) * nq + kvh * g + row_h) * D;
+#pragma unroll
+            for (int c = 0; c < D / 16; ++c) {
+                uint32_t r[16];
+                tmem_ld_16_nowait(tmem + lane_addr + O_COL + c * 16, r);
+                tmem_ld_wait();
+                if (row_valid) {
+                    uint4 v[2];
+                    __nv_bfloat162* pv2 = reinterpret_cast<__nv_bfloat162*>(v);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        pv2[e] = __floats2bfloat162_rn(__uint_as_float(r[2 * e]) * inv, __uint_as_float(r[2 * e + 1]) * inv);
+                    *reinterpret_cast<uint4*>(o + c * 16) = v[0];
+                    *reinterpret_cast<uint4*>(o + c * 16 + 8) = v[1];
+                }
+            }
+        }
+        tc_fence_before_sync();
+    }
+
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+// ---- host ---------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+bool make_map_2d(CUtensorMap* map, const void* base, long long rows, int cols, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// q [R, nq, D]: dims (D, nq, R), a box of 64 columns x g heads x bq positions
+bool make_map_q(CUtensorMap* map, const void* base, int R, int nq, int D, int g, int bq) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)nq, (cuuint64_t)R};
+    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)nq * D * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)g, (cuuint32_t)bq};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int D>
+int launch_tc(const void* q, const void* k_pages, const void* v_pages, long long n_pages_total,
+              const PagedKV& cache, const int* seq_slot, const int* seq_start, const int* seq_new,
+              const int* seq_row0, void* out, int S, int max_new, int R, int nq, int window, float scale,
+              int* err, cudaStream_t s) {
+    const int g = nq / cache.n_kv_heads;
+    if (g > ROWS) return RFX_ERR_UNSUPPORTED;
+    const int bq = ROWS / g;
+    CUtensorMap mq, mk, mv;
+    const long long kv_rows = n_pages_total * cache.n_kv_heads * PAGE;
+    if (!make_map_q(&mq, q, R, nq, D, g, bq) || !make_map_2d(&mk, k_pages, kv_rows, D, PAGE) ||
+        !make_map_2d(&mv, v_pages, kv_rows, D, PAGE))
+        return RFX_ERR_UNSUPPORTED;
+    const size_t smem = Smem::total(D);
+    auto kernel = attention_prefill_tc_kernel<D>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid((max_new + bq - 1) / bq, S, cache.n_kv_heads);
+    if (grid.y > 65535 || grid.z > 65535) return RFX_ERR_UNSUPPORTED;
+    RFX_LAUNCH(kernel, grid, THREADS, smem, s, mq, mk, mv, cache, seq_slot, seq_start, seq_new, seq_row0,
+               (__nv_bfloat16*)out, nq, bq, window, scale * 1.4426950408889634f, err);
+    return 0;
+}
+
+}  // namespace
+
+// As rfx_attention_prefill, for head_dim 64 or 128.  `n_pages_total` is the
+// number of pages of the K/V store (for the TMA maps), R the number of rows of
+// q.  `err` is a device word that receives a code if a bounded wait ran out.
+extern "C" int rfx_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages,
+                                        long long n_pages_total, const int* page_table, int max_pages,
+                                        int page_size, const int* seq_slot, const int* seq_start,
+                                        const int* seq_new, const int* seq_row0, void* out, int S,
+                                        int max_new, int R, int nq, int nkv, int head_dim, int window,
+                                        float scale, int* err, void* stream) {
+    if (S <= 0 || max_new <= 0 || R <= 0) return 0;
+    if (page_size != PAGE || nkv <= 0 || nq % nkv != 0) return RFX_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_pages) |
+         reinterpret_cast<uintptr_t>(v_pages)) & 15)
+        return RFX_ERR_BAD_ARG;
+    PagedKV cache{page_table, max_pages, page_size, nkv, head_dim};
+    cudaStream_t s = (cudaStream_t)stream;
+    if (head_dim == 64)
+        return launch_tc<64>(q, k_pages, v_pages, n_pages_total, cache, seq_slot, seq_start, seq_new,
+                             seq_row0, out, S, max_new, R, nq, window, scale, err, s);
+    if (head_dim == 128)
+        return launch_tc<128>(q, k_pages, v_pages, n_pages_total, cache, seq_slot, seq_start, seq_new,
+                              seq_row0, out, S, max_new, R, nq, window, scale, err, s);
+    return RFX_ERR_UNSUPPORTED;
+}

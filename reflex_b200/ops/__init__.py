@@ -290,6 +290,26 @@ def attention_prefill(q, k_pages, v_pages, page_table, page_size, seq_slot, seq_
     return out
 
 
+def attention_prefill_tc(q, k_pages, v_pages, page_table, page_size, seq_slot, seq_start, seq_new,
+                         seq_row0, max_new: int, nq, nkv, head_dim, window, scale) -> torch.Tensor:
+    """The tcgen05/TMEM form of `attention_prefill`, for head sizes 64 and 128."""
+    _chk(q, "q", torch.bfloat16)
+    if head_dim not in (64, 128):
+        raise InvalidInput(f"attention_prefill_tc takes head_dim 64 or 128, got {head_dim}")
+    if nq // nkv > 128:
+        raise InvalidInput(f"attention_prefill_tc takes up to 128 query heads per kv head, got {nq // nkv}")
+    out = torch.empty_like(q)
+    st = native.lib().rfx_attention_prefill_tc(
+        q.data_ptr(), _chk(k_pages, "k_pages", torch.bfloat16), _chk(v_pages, "v_pages", torch.bfloat16),
+        k_pages.shape[0], _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
+        _chk(seq_slot, "seq_slot", torch.int32), _chk(seq_start, "seq_start", torch.int32),
+        _chk(seq_new, "seq_new", torch.int32), _chk(seq_row0, "seq_row0", torch.int32), out.data_ptr(),
+        seq_slot.numel(), int(max_new), q.shape[0], nq, nkv, head_dim, int(window or 0), float(scale),
+        device_error_word(q.device).data_ptr(), _stream())
+    native.check(st, f"attention_prefill_tc (head_dim={head_dim})")
+    return out
+
+
 def attention(q, k_pages, v_pages, page_table, page_size, batch, nq, nkv, head_dim, window, scale):
     """Attention of the step's rows over their sequences' cached keys and
     values; picks the kernel for the dtype and the kind of step."""
@@ -297,6 +317,10 @@ def attention(q, k_pages, v_pages, page_table, page_size, batch, nq, nkv, head_d
     if fast and batch.is_decode:
         return attention_decode(q, k_pages, v_pages, page_table, page_size, batch.row_pos,
                                 batch.row_slot, nq, nkv, head_dim, window, scale)
+    if fast and nq // nkv <= 128 and head_dim in (64, 128):
+        return attention_prefill_tc(q, k_pages, v_pages, page_table, page_size, batch.seq_slot,
+                                    batch.seq_start, batch.seq_new, batch.seq_row0, batch.max_new, nq,
+                                    nkv, head_dim, window, scale)
     if fast and nq // nkv <= 128:
         return attention_prefill(q, k_pages, v_pages, page_table, page_size, batch.seq_slot,
                                  batch.seq_start, batch.seq_new, batch.seq_row0, batch.max_new, nq,

@@ -241,12 +241,17 @@ ATT_CASES = [
     (32, 8, 128, [(1489, 41), (0, 1), (63, 2)], None),
     (7, 7, 80, [(0, 255), (5, 251)], 64),
     (16, 1, 64, [(31, 34)], None),
+    (6, 2, 64, [(0, 1), (0, 7), (0, 64), (0, 100), (0, 129)], None),
+    (5, 1, 128, [(100, 37), (700, 300)], 37),
+    (8, 8, 128, [(0, 200), (60, 9)], None),
 ]
 
 
 @pytest.mark.parametrize("nq,nkv,d,seqs,window", ATT_CASES)
-@pytest.mark.parametrize("kernel", ["plain_f32", "plain_bf16", "prefill_bf16"])
+@pytest.mark.parametrize("kernel", ["plain_f32", "plain_bf16", "prefill_bf16", "prefill_tc_bf16"])
 def test_attention_over_the_paged_cache(nq, nkv, d, seqs, window, kernel):
+    if kernel == "prefill_tc_bf16" and d not in (64, 128):
+        pytest.skip("the tcgen05 kernel takes head sizes 64 and 128")
     g = torch.Generator().manual_seed(nq * 31 + d)
     dtype = torch.float32 if kernel == "plain_f32" else torch.bfloat16
     slots, table, kp, vp, ks, vs = _paged([a + b for a, b in seqs], nkv, d, dtype, g)
@@ -265,9 +270,11 @@ def test_attention_over_the_paged_cache(nq, nkv, d, seqs, window, kernel):
         row0 = [0]
         for _, b in seqs:
             row0.append(row0[-1] + b)
-        out = ops().attention_prefill(qd, kp.to(DEV), vp.to(DEV), table.to(DEV), 64, i32(slots),
-                                      i32([a for a, _ in seqs]), i32([b for _, b in seqs]), i32(row0),
-                                      max(b for _, b in seqs), nq, nkv, d, window, scale)
+        fn = ops().attention_prefill_tc if kernel == "prefill_tc_bf16" else ops().attention_prefill
+        out = fn(qd, kp.to(DEV), vp.to(DEV), table.to(DEV), 64, i32(slots),
+                 i32([a for a, _ in seqs]), i32([b for _, b in seqs]), i32(row0),
+                 max(b for _, b in seqs), nq, nkv, d, window, scale)
+        ops().check_device_errors(DEV)
     assert not bool(torch.isnan(out.float()).any()), "read a cache row that was never written"
     assert relerr(out.reshape(R, nq, d), ref) < (2e-6 if dtype == torch.float32 else 8e-3)
 
@@ -290,7 +297,7 @@ def test_attention_decode_splits(nq, nkv, d, ctxs, window, splits):
     assert relerr(out.reshape(R, nq, d), ref) < 8e-3
 
 
-@pytest.mark.parametrize("kernel", ["plain_f32", "plain_bf16", "prefill_bf16", "decode_bf16"])
+@pytest.mark.parametrize("kernel", ["plain_f32", "plain_bf16", "prefill_bf16", "prefill_tc_bf16", "decode_bf16"])
 def test_a_far_key_among_hundreds_and_the_windows_edge(kernel):
     """One key gets a score far above the rest, so the output must be its value
     row; the key sits far back (position 3 of 900), and then exactly at the
@@ -315,8 +322,8 @@ def test_a_far_key_among_hundreds_and_the_windows_edge(kernel):
         elif kernel == "decode_bf16":
             out = ops().attention_decode(qd, *args, i32([n - 1]), i32(slots), nq, nkv, d, window, d ** -0.5, n_splits=4)
         else:
-            out = ops().attention_prefill(qd, *args, i32(slots), i32([n - 1]), i32([1]), i32([0, 1]), 1,
-                                          nq, nkv, d, window, d ** -0.5)
+            fn = ops().attention_prefill_tc if kernel == "prefill_tc_bf16" else ops().attention_prefill
+            out = fn(qd, *args, i32(slots), i32([n - 1]), i32([1]), i32([0, 1]), 1, nq, nkv, d, window, d ** -0.5)
         out = out.float().cpu().reshape(nq, d)
         for kvh, h in ((0, 0), (1, 2)):
             target = vp[page, kvh, tok].to(dtype).float()

@@ -37,11 +37,50 @@ constexpr int MAX_STAGES = 12;
 constexpr int THREADS = 192;   // warp 0: TMA, warp 1: MMA, warps 2..5: epilogue
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 
+// Optional timeline for tuning: when a buffer is set (rfx_gemm_trace), thread 0 of
+// every CTA stores %globaltimer at entry, after the dependency wait, when the
+// accumulator is complete and at exit, in the record of its launch.
+struct TraceRec {
+    unsigned long long t[4];
+};
+static __device__ TraceRec* g_trace = nullptr;
+static __device__ int g_trace_ctas = 0;   // records per launch
+static __device__ int g_trace_launches = 0;
+__device__ __forceinline__ void trace_mark(int launch, int which) {
+    if (g_trace == nullptr || launch >= g_trace_launches) return;
+    const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    if (cta >= g_trace_ctas) return;
+    g_trace[(size_t)launch * g_trace_ctas + cta].t[which] = global_timer_ns();
+}
+
 template <int BN>
 struct Shape {
     static constexpr int B_STAGE_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
     static constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+};
+
+// What the epilogue does besides storing, for the fused decode path:
+//  * scale_rows (PRO): the activation rows came in unnormalised (x = h * w_norm,
+//    rounded to bfloat16); row r of the result is multiplied by
+//    1 / sqrt(sum_p ssq_in[p][r] / H + eps), the RMSNorm factor, which commutes
+//    with the product.  The partial sums of squares come from the product that
+//    made h (below).
+//  * EPI 2: the result is a delta of the residual stream: h[r, n] += acc (32-bit,
+//    each element by one thread), hb[r, n] = bfloat16(h * (nw_offset + nw[n])) is
+//    the next product's unnormalised input, and ssq_out[p][r] = sum of h^2 over
+//    this CTA's rows n is one partial of the next norm's statistic.
+// Together they replace the separate add + RMSNorm launch between two products
+// (src/kernels_cuda/decode_ops.cu:10-35 is the reference's fused add + norm).
+struct Fuse {
+    const float* ssq_in;   // [n_part_in][R]
+    int n_part_in;
+    float inv_h, eps;
+    float* h;              // [R, N] residual stream, updated in place
+    const float* nw;       // [N] weight of the norm that follows
+    float nw_offset;
+    __nv_bfloat16* hb;     // [R, N]
+    float* ssq_out;        // [tiles * ksplit][R]
 };
 
 // EPI 0: y = x W^T.  EPI 1: W's rows alternate gate, up (row 2j gate_j, row 2j+1
@@ -50,12 +89,14 @@ struct Shape {
 // (src/kernels_cuda/silu_and_mul.cu:7-23 is the reference's separate kernel).
 __device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
 
-template <int BN, typename TO, int EPI>
+template <int BN, typename TO, int EPI, bool PRO>
 __global__ void __launch_bounds__(THREADS)
 gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                TO* __restrict__ y, int R, int N, int K, int ksplit, int stages, int bm,
-               int l2_ahead, int* __restrict__ err) {
+               int l2_ahead, int trace_id, Fuse fuse, int* __restrict__ err) {
     extern __shared__ uint8_t smem_raw[];
+    __shared__ float red_s[128];
+    __shared__ float rstd_s[BN];
     __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
     __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
     __shared__ __align__(8) uint64_t tmem_full_bar;
@@ -66,6 +107,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                 ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) trace_mark(trace_id, 0);
     // a tile is `bm` <= 128 weight rows: the MMA always spans 128 rows of shared
     // memory, rows past bm hold whatever was there and give output rows nobody reads
     const int n0 = blockIdx.x * bm, r0 = blockIdx.y * BN, z = blockIdx.z;
@@ -115,6 +157,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const int ahead = min(nkb, pre + l2_ahead);
             for (int i = pre; i < ahead; ++i) tma_prefetch_l2_2d(&map_w, (kb0 + i) * BK, n0);
             rfx::pdl_wait();
+            trace_mark(trace_id, 1);
             for (int i = 0; i < pre; ++i)
                 tma_load_2d(tiles + (size_t)i * S::STAGE_BYTES + A_STAGE_BYTES, &map_x, &full_bar[i],
                             (kb0 + i) * BK, r0);
@@ -163,12 +206,30 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         rfx::pdl_wait();         // y may still be read by an earlier kernel
         const int q = warp & 3;  // this warp may read TMEM lanes [32 q, 32 q + 32)
         const int m = q * 32 + lane;
+        if (PRO) {
+            // the rows' norm factors, while the main loop runs: 128 / BN threads
+            // share a row's partials, then one thread adds their sums in order
+            const int t = m, rl = t % BN, grp = t / BN;
+            constexpr int G = 128 / BN;
+            float sum = 0.0f;
+            if (r0 + rl < R)
+                for (int p = grp; p < fuse.n_part_in; p += G) sum += fuse.ssq_in[(size_t)p * R + r0 + rl];
+            red_s[t] = sum;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (t < BN) {
+                float total = 0.0f;
+#pragma unroll
+                for (int gi = 0; gi < G; ++gi) total += red_s[gi * BN + t];
+                rstd_s[t] = 1.0f / sqrtf(total * fuse.inv_h + fuse.eps);
+            }
+        }
         bool have = nkb > 0;
         if (have && !mbar_wait(&tmem_full_bar, 0)) {
             if (lane == 0) atomicExch(err, 3);
             have = false;
         }
         tc_fence_after_sync();
+        if (warp == 2 && lane == 0) trace_mark(trace_id, 2);
         float* partial = reinterpret_cast<float*>(tiles);  // [BN][BM], reuses the drained stages
 #pragma unroll 1
         for (int c = 0; c < BN / 16; ++c) {
@@ -179,35 +240,22 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] = 0.0f;
             }
-            if (ksplit == 1 && EPI == 0) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int r = r0 + c * 16 + j;
-                    if (r < R && m < bm && n0 + m < N) rfx::st<TO>(y, (size_t)r * N + n0 + m, v[j]);
-                }
-            } else if (ksplit == 1) {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const float up = __shfl_down_sync(0xffffffffu, v[j], 1);  // the odd row above
-                    const int r = r0 + c * 16 + j;
-                    if ((m & 1) == 0 && r < R && m + 1 < bm && n0 + m + 1 < N)
-                        rfx::st<TO>(y, (size_t)r * (N / 2) + (n0 + m) / 2, silu_mul(v[j], up));
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) partial[(c * 16 + j) * BM + m] = v[j];
-            }
+            for (int j = 0; j < 16; ++j) partial[(c * 16 + j) * BM + m] = v[j];
         }
         tc_fence_before_sync();
     }
 
-    if (ksplit > 1) {
-        // every CTA of the cluster has its partial tile in shared memory; rank z
-        // sums its share of the tile's rows over the ranks in rank order
+    // Every CTA of the cluster (or just this one) has its partial tile in shared
+    // memory; rank z finishes its share of the tile's rows: the sum over the ranks
+    // in rank order, then the epilogue.
+    {
         cg::cluster_group cluster = cg::this_cluster();
         rfx::pdl_wait();
-        cluster.sync();
+        if (ksplit > 1) cluster.sync();
+        else __syncthreads();
         float* partial = reinterpret_cast<float*>(tiles);
+        float* sq = partial + BN * BM;  // [BN][mw] squares of the new residual (EPI 2)
         int mw = (bm + ksplit - 1) / ksplit;
         if (EPI == 1) mw = (mw + 1) & ~1;  // gate and up of a pair stay with one rank
         if (EPI == 0) {
@@ -215,14 +263,12 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const int rr = e / mw, mm = z * mw + e % mw;
                 if (mm >= bm) continue;
                 float acc = 0.0f;
-                for (int p = 0; p < ksplit; ++p) {
-                    const float* remote = cluster.map_shared_rank(partial, p);
-                    acc += remote[rr * BM + mm];
-                }
+                for (int p = 0; p < ksplit; ++p) acc += cluster.map_shared_rank(partial, p)[rr * BM + mm];
+                if (PRO) acc *= rstd_s[rr];
                 const int r = r0 + rr;
                 if (r < R && n0 + mm < N) rfx::st<TO>(y, (size_t)r * N + n0 + mm, acc);
             }
-        } else {
+        } else if (EPI == 1) {
             const int pw = mw / 2;
             for (int e = threadIdx.x; e < BN * pw; e += THREADS) {
                 const int rr = e / pw, mm = z * mw + 2 * (e % pw);
@@ -233,15 +279,43 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     g += remote[rr * BM + mm];
                     u += remote[rr * BM + mm + 1];
                 }
+                if (PRO) {
+                    g *= rstd_s[rr];
+                    u *= rstd_s[rr];
+                }
                 const int r = r0 + rr;
                 if (r < R && n0 + mm + 1 < N)
                     rfx::st<TO>(y, (size_t)r * (N / 2) + (n0 + mm) / 2, silu_mul(g, u));
             }
+        } else {
+            for (int e = threadIdx.x; e < BN * mw; e += THREADS) {
+                const int rr = e / mw, ml = e % mw, mm = z * mw + ml;
+                const int r = r0 + rr, n = n0 + mm;
+                float hv = 0.0f;
+                if (mm < bm && r < R && n < N) {
+                    float acc = 0.0f;
+                    for (int p = 0; p < ksplit; ++p) acc += cluster.map_shared_rank(partial, p)[rr * BM + mm];
+                    const size_t idx = (size_t)r * N + n;
+                    hv = fuse.h[idx] + acc;
+                    fuse.h[idx] = hv;
+                    fuse.hb[idx] = __float2bfloat16_rn(hv * (fuse.nw_offset + fuse.nw[n]));
+                }
+                sq[rr * mw + ml] = hv * hv;
+            }
+            __syncthreads();
+            // this CTA's partial of each row's sum of squares, added in index order
+            if ((int)threadIdx.x < BN && r0 + (int)threadIdx.x < R) {
+                float tot = 0.0f;
+                for (int i = 0; i < mw; ++i) tot += sq[threadIdx.x * mw + i];
+                const int part = blockIdx.x * ksplit + z;
+                fuse.ssq_out[(size_t)part * R + r0 + threadIdx.x] = tot;
+            }
         }
-        cluster.sync();  // nobody leaves while its shared memory is still read
+        if (ksplit > 1) cluster.sync();  // nobody leaves while its shared memory is still read
     }
 
     __syncthreads();
+    if (threadIdx.x == 0) trace_mark(trace_id, 3);
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_d, S::TMEM_COLS);
@@ -314,6 +388,8 @@ int sm_count() {
     return n;
 }
 
+int g_trace_next = 0;  // launch counter: the trace record a launch writes
+
 int env_int(const char* name, int dflt) {
     const char* e = getenv(name);
     return e ? atoi(e) : dflt;
@@ -358,9 +434,9 @@ Cut choose_cut(int N, int r_tiles, int num_kb, int ks_req) {
     return Cut{BM, tiles, ks};
 }
 
-template <int BN, typename TO, int EPI>
-int launch(const void* x, const void* W, void* y, int R, int N, int K, int ksplit_req, int* err,
-           cudaStream_t s) {
+template <int BN, typename TO, int EPI, bool PRO>
+int launch(const void* x, const void* W, void* y, int R, int N, int K, int ksplit_req, const Fuse& fuse_in,
+           int* n_part_out, int* err, cudaStream_t s) {
     using S = Shape<BN>;
     const int r_tiles = (R + BN - 1) / BN;
     const int num_kb = (K + BK - 1) / BK;
@@ -384,9 +460,12 @@ int launch(const void* x, const void* W, void* y, int R, int N, int K, int kspli
     if (st_env >= 2) stages = st_env;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 2) stages = 2;
-    if (ks > 1 && stages * S::STAGE_BYTES < BN * BM * 4) return RFX_ERR_UNSUPPORTED;
+    // the drained stages hold the partial tile (and the squares of EPI 2) afterwards
+    if (stages * S::STAGE_BYTES < BN * BM * 4 * (EPI == 2 ? 2 : 1)) return RFX_ERR_UNSUPPORTED;
+    if (n_part_out) *n_part_out = cut.tiles * ks;
+    if (EPI == 2 && r_tiles != 1) return RFX_ERR_UNSUPPORTED;
     const size_t smem = (size_t)stages * S::STAGE_BYTES + 1024;
-    auto kernel = gemm_wt_kernel<BN, TO, EPI>;
+    auto kernel = gemm_wt_kernel<BN, TO, EPI, PRO>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     // L2 prefetch before the dependency wait: up to a budget for the whole grid
@@ -395,18 +474,26 @@ int launch(const void* x, const void* W, void* y, int R, int N, int K, int kspli
     int l2_ahead = (int)(budget / (ctas * cut.bm * BK * 2));
     if (r_tiles > 1) l2_ahead = 0;  // prefill-sized calls are not bandwidth-bound
     e = rfx::launch(kernel, dim3(cut.tiles, r_tiles, ks), dim3(THREADS), smem, s, ks, *mw, mx, (TO*)y, R,
-                    N, K, ks, stages, cut.bm, l2_ahead, err);
+                    N, K, ks, stages, cut.bm, l2_ahead, g_trace_next++, fuse_in, err);
     if (e != cudaSuccess) return (int)e;
     return 0;
 }
 
-template <typename TO, int EPI>
-int dispatch(const void* x, const void* W, void* y, int R, int N, int K, int ksplit, int* err,
-             cudaStream_t s) {
-    if (R <= 16) return launch<16, TO, EPI>(x, W, y, R, N, K, ksplit, err, s);
-    if (R <= 32) return launch<32, TO, EPI>(x, W, y, R, N, K, ksplit, err, s);
-    if (R <= 64) return launch<64, TO, EPI>(x, W, y, R, N, K, ksplit, err, s);
-    return launch<128, TO, EPI>(x, W, y, R, N, K, ksplit, err, s);
+template <typename TO, int EPI, bool PRO>
+int dispatch(const void* x, const void* W, void* y, int R, int N, int K, int ksplit, const Fuse& fuse,
+             int* n_part_out, int* err, cudaStream_t s) {
+    if (R <= 16) return launch<16, TO, EPI, PRO>(x, W, y, R, N, K, ksplit, fuse, n_part_out, err, s);
+    if (R <= 32) return launch<32, TO, EPI, PRO>(x, W, y, R, N, K, ksplit, fuse, n_part_out, err, s);
+    if (R <= 64) return launch<64, TO, EPI, PRO>(x, W, y, R, N, K, ksplit, fuse, n_part_out, err, s);
+    if (EPI == 2 || PRO) return RFX_ERR_UNSUPPORTED;  // the fused forms are for decode-sized batches
+    return launch<128, TO, EPI, PRO>(x, W, y, R, N, K, ksplit, fuse, n_part_out, err, s);
+}
+
+int check_common(const void* x, const void* W, int R, int N, int K) {
+    if (K <= 0 || K % 8 != 0) return RFX_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(W)) & 15) return RFX_ERR_BAD_ARG;
+    if ((N + BM - 1) / BM > 2147483647 || (R + 127) / 128 > 65535) return RFX_ERR_UNSUPPORTED;
+    return 0;
 }
 
 }  // namespace
@@ -417,21 +504,67 @@ int dispatch(const void* x, const void* W, void* y, int R, int N, int K, int ksp
 // word that receives a non-zero code if a bounded wait ran out.
 // epilogue 1: W's rows alternate gate/up, N is even, y is [R, N / 2] =
 // silu(gate) * up.
+// ssq_in (optional, R <= 64): x is unnormalised; row r of the result is scaled by
+// 1 / sqrt(sum_p ssq_in[p][r] / norm_h + eps), p < n_part_in.
 extern "C" int rfx_gemm_bf16_tc(const void* x, const void* W, void* y, int y_dt, int R, int N,
-                                int K, int ksplit, int epilogue, int* err, void* stream) {
+                                int K, int ksplit, int epilogue, const float* ssq_in, int n_part_in,
+                                int norm_h, float eps, int* err, void* stream) {
     if (R <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8 != 0) return RFX_ERR_UNSUPPORTED;
+    if (int c = check_common(x, W, R, N, K)) return c;
     if (epilogue != 0 && epilogue != 1) return RFX_ERR_BAD_ARG;
     if (epilogue == 1 && (N & 1)) return RFX_ERR_BAD_ARG;
-    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(W)) & 15) return RFX_ERR_BAD_ARG;
-    if ((N + BM - 1) / BM > 2147483647 || (R + 127) / 128 > 65535) return RFX_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    if (epilogue == 0) {
-        if (y_dt == RFX_DT_F32) return dispatch<float, 0>(x, W, y, R, N, K, ksplit, err, s);
-        if (y_dt == RFX_DT_BF16) return dispatch<__nv_bfloat16, 0>(x, W, y, R, N, K, ksplit, err, s);
-    } else {
-        if (y_dt == RFX_DT_F32) return dispatch<float, 1>(x, W, y, R, N, K, ksplit, err, s);
-        if (y_dt == RFX_DT_BF16) return dispatch<__nv_bfloat16, 1>(x, W, y, R, N, K, ksplit, err, s);
+    Fuse f{};
+    const bool pro = ssq_in != nullptr;
+    if (pro) {
+        if (n_part_in <= 0 || norm_h <= 0) return RFX_ERR_BAD_ARG;
+        f.ssq_in = ssq_in;
+        f.n_part_in = n_part_in;
+        f.inv_h = 1.0f / (float)norm_h;
+        f.eps = eps;
     }
+#define RFX_GO(TO, E, P) return dispatch<TO, E, P>(x, W, y, R, N, K, ksplit, f, nullptr, err, s)
+    if (y_dt == RFX_DT_F32) {
+        if (epilogue == 0) { if (pro) RFX_GO(float, 0, true); else RFX_GO(float, 0, false); }
+        else { if (pro) RFX_GO(float, 1, true); else RFX_GO(float, 1, false); }
+    } else if (y_dt == RFX_DT_BF16) {
+        if (epilogue == 0) { if (pro) RFX_GO(__nv_bfloat16, 0, true); else RFX_GO(__nv_bfloat16, 0, false); }
+        else { if (pro) RFX_GO(__nv_bfloat16, 1, true); else RFX_GO(__nv_bfloat16, 1, false); }
+    }
+#undef RFX_GO
     return RFX_ERR_BAD_ARG;
+}
+
+// The product as a delta of the residual stream, for R <= 64:
+//   h [R, N] (float32) += x . W^T;   hb [R, N] = bfloat16(h * (nw_offset + nw[n]));
+//   ssq_out[p][r] = this CTA's share of sum_n h[r, n]^2, p < *n_part_out
+// (ssq_out must hold at least rfx_gemm_bf16_tc_max_parts(N) * R floats).
+extern "C" int rfx_gemm_bf16_tc_residual(const void* x, const void* W, float* h, const float* nw,
+                                         float nw_offset, void* hb, float* ssq_out, int* n_part_out,
+                                         int R, int N, int K, int ksplit, int* err, void* stream) {
+    if (R <= 0 || N <= 0) return 0;
+    if (R > 64) return RFX_ERR_UNSUPPORTED;
+    if (int c = check_common(x, W, R, N, K)) return c;
+    if (!h || !nw || !hb || !ssq_out || !n_part_out) return RFX_ERR_BAD_ARG;
+    Fuse f{};
+    f.h = h;
+    f.nw = nw;
+    f.nw_offset = nw_offset;
+    f.hb = (__nv_bfloat16*)hb;
+    f.ssq_out = ssq_out;
+    return dispatch<float, 2, false>(x, W, nullptr, R, N, K, ksplit, f, n_part_out, err, (cudaStream_t)stream);
+}
+
+// An upper bound of the partials a residual product of N weight rows writes per row.
+extern "C" int rfx_gemm_bf16_tc_max_parts(int N) { return ((N + 31) / 32) * 8 + 8 * 148 * 2; }
+
+// Tuning aid: give the product kernel a device buffer of launches * ctas records of
+// four 64-bit timestamps; the next launch writes record 0.  Null turns it off.
+extern "C" int rfx_gemm_trace(void* buffer, int launches, int ctas) {
+    g_trace_next = 0;
+    TraceRec* p = (TraceRec*)buffer;
+    cudaError_t e = cudaMemcpyToSymbol(g_trace, &p, sizeof(p));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_trace_ctas, &ctas, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_trace_launches, &launches, sizeof(int));
+    return (int)e;
 }

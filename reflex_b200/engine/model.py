@@ -89,19 +89,34 @@ class CausalLM:
     def hidden_states(self, batch, cache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         h = ops.embed(self.embedding, batch.tokens, self.spec.embedding_scale, self.err_flag)
         pending = None
-        for run in self.spec.run_order:
+        order = self.spec.run_order
+        for i, run in enumerate(order):
+            # the norm that will consume this run's result: the next run's first norm, or the final one
+            next_norm = (getattr(self.layers[order[i + 1].layer], "mixer_norm", None)
+                         if i + 1 < len(order) else self.final_norm)
             ctx = RunContext(batch=batch, writes_cache=run.writes_cache, entry=run.cache)
             kind = cache.has(run.cache)
             if kind == "kv":
                 ctx.kv = cache.kv(run.cache)
             elif kind == "state":
                 ctx.state = cache.state(run.cache)
-            h, pending = self.layers[run.layer].forward(h, pending, ctx)
+            layer = self.layers[run.layer]
+            if hasattr(layer, "mixer_norm"):
+                h, pending = layer.forward(h, pending, ctx, next_norm=next_norm)
+            else:
+                h, pending = layer.forward(h, pending, ctx)
         return h, pending
 
-    def logits(self, hidden: torch.Tensor, pending: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
+    def logits(self, hidden: torch.Tensor, pending, rows: torch.Tensor, rows_host=None) -> torch.Tensor:
         """Final norm and head on the wanted rows only; float32 [len(rows), V]."""
-        normed = self.final_norm(hidden, delta=pending, rows=rows)
+        if isinstance(pending, ops.NormedInput):
+            # fused decode path: hidden already holds the last delta
+            if rows_host is not None and list(rows_host) == list(range(hidden.shape[0])):
+                normed = pending  # every row wanted, in order: the head product takes them as they are
+            else:
+                normed = self.final_norm(hidden, rows=rows)
+        else:
+            normed = self.final_norm(hidden, delta=pending, rows=rows)
         out = ops.linear(normed, self.head, out_dtype=torch.float32)
         if self.spec.logit_scale != 1.0:
             out = out * self.spec.logit_scale
@@ -109,4 +124,4 @@ class CausalLM:
 
     def forward(self, batch, cache) -> torch.Tensor:
         h, pending = self.hidden_states(batch, cache)
-        return self.logits(h, pending, batch.want_rows)
+        return self.logits(h, pending, batch.want_rows, batch.want_rows_host)

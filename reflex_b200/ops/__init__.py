@@ -128,19 +128,42 @@ def check_device_errors(device="cuda:0") -> None:
         raise CudaError(f"a kernel gave up a bounded wait (code {code}); its results are not valid")
 
 
-def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.float32,
+class NormedInput:
+    """Rows that still await their RMSNorm factor: `hb` = bfloat16(h * norm
+    weight) and `ssq[p][r]`, partial sums of squares of h's row r.  The product
+    that consumes them multiplies its row r by 1 / sqrt(sum_p ssq[p][r] / size +
+    eps), which is the same as normalising first.  Made by `gemm_tc_residual`."""
+
+    def __init__(self, hb: torch.Tensor, ssq: torch.Tensor, n_part: int, size: int, eps: float):
+        self.hb, self.ssq, self.n_part, self.size, self.eps = hb, ssq, n_part, size, eps
+
+    @property
+    def shape(self):
+        return self.hb.shape
+
+    @property
+    def dtype(self):
+        return self.hb.dtype
+
+
+def gemm_tc(x, weight: torch.Tensor, out_dtype: torch.dtype = torch.float32,
             ksplit: int = 0, swiglu_pairs: bool = False) -> torch.Tensor:
     """The tcgen05/TMA product y = x @ weight.T (bfloat16 in, float32 accumulate).
     With `swiglu_pairs` the weight's rows alternate gate, up and the result is
-    silu(gate) * up, [R, N / 2]."""
+    silu(gate) * up, [R, N / 2].  `x` may be a `NormedInput`."""
+    normed = x if isinstance(x, NormedInput) else None
+    if normed is not None:
+        x = normed.hb
     R, K = x.shape
     N = weight.shape[0]
     _chk(x, "x", torch.bfloat16)
     _chk(weight, "weight", torch.bfloat16)
     y = torch.empty((R, N // 2 if swiglu_pairs else N), dtype=out_dtype, device=x.device)
-    st = native.lib().rfx_gemm_bf16_tc(x.data_ptr(), weight.data_ptr(), y.data_ptr(), dt_code(out_dtype),
-                                       R, N, K, ksplit, 1 if swiglu_pairs else 0,
-                                       device_error_word(x.device).data_ptr(), _stream())
+    st = native.lib().rfx_gemm_bf16_tc(
+        x.data_ptr(), weight.data_ptr(), y.data_ptr(), dt_code(out_dtype), R, N, K, ksplit,
+        1 if swiglu_pairs else 0, normed.ssq.data_ptr() if normed is not None else 0,
+        normed.n_part if normed is not None else 0, normed.size if normed is not None else 0,
+        float(normed.eps) if normed is not None else 0.0, device_error_word(x.device).data_ptr(), _stream())
     native.check(st, f"gemm_bf16_tc (R={R}, N={N}, K={K})")
     return y
 
@@ -160,6 +183,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
         raise InvalidInput(f"linear: x has {K} columns, weight has {K2}")
     if x.dtype != weight.dtype:
         raise InvalidInput(f"linear: x is {x.dtype}, weight is {weight.dtype}")
+    if isinstance(x, NormedInput):
+        return gemm_tc(x, weight, out_dtype or torch.bfloat16)
     _chk(x, "x")
     _chk(weight, "weight")
     if x.dtype == torch.float32:
@@ -175,6 +200,51 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     return torch.mm(x, weight.t())
 
 
+def gemm_tc_residual(x: torch.Tensor, weight: torch.Tensor, hidden: torch.Tensor,
+                     norm_weight: torch.Tensor, norm_offset: float, eps: float, ksplit: int = 0) -> NormedInput:
+    """hidden += x @ weight.T in place (float32), and the rows of the new hidden
+    as a `NormedInput` for the product after the norm whose weight is given: the
+    residual add and the RMSNorm between two products without a launch."""
+    import ctypes
+
+    R, K = x.shape
+    N = weight.shape[0]
+    _chk(x, "x", torch.bfloat16)
+    _chk(weight, "weight", torch.bfloat16)
+    _chk(hidden, "hidden", torch.float32)
+    _chk(norm_weight, "norm_weight", torch.float32)
+    if tuple(hidden.shape) != (R, N) or norm_weight.numel() != N:
+        raise InvalidInput("gemm_tc_residual: hidden must be [rows, out] and the norm weight [out]")
+    hb = torch.empty((R, N), dtype=torch.bfloat16, device=x.device)
+    ssq = torch.empty((native.lib().rfx_gemm_bf16_tc_max_parts(N), R), dtype=torch.float32, device=x.device)
+    n_part = ctypes.c_int(0)
+    st = native.lib().rfx_gemm_bf16_tc_residual(
+        x.data_ptr(), weight.data_ptr(), hidden.data_ptr(), norm_weight.data_ptr(), float(norm_offset),
+        hb.data_ptr(), ssq.data_ptr(), ctypes.addressof(n_part), R, N, K, ksplit,
+        device_error_word(x.device).data_ptr(), _stream())
+    native.check(st, f"gemm_bf16_tc_residual (R={R}, N={N}, K={K})")
+    return NormedInput(hb, ssq, n_part.value, N, eps)
+
+
+def linear_residual(x: torch.Tensor, weight: torch.Tensor, hidden: torch.Tensor, next_norm) -> Optional[NormedInput]:
+    """The fused form of `hidden += linear(x, weight)` followed by `next_norm`,
+    when the sizes and the norm allow it (a few bfloat16 rows, an RMSNorm with a
+    plain weight); None otherwise, and the caller takes the two-launch way."""
+    if (x.dtype != torch.bfloat16 or x.shape[0] > GEMV_MAX_ROWS or x.shape[1] % 8 or next_norm is None
+            or not FUSE_NORM):
+        return None
+    w = getattr(next_norm, "weight", None)
+    spec = getattr(next_norm, "spec", None)
+    if w is None or spec is None or getattr(spec, "kind", None) != "rmsnorm" or w.numel() != weight.shape[0]:
+        return None
+    return gemm_tc_residual(x, weight, hidden, w, spec.weight_offset, spec.eps)
+
+
+import os as _os
+
+FUSE_NORM = _os.environ.get("REFLEX_B200_FUSE_NORM", "1") != "0"
+
+
 def linear_swiglu(x: torch.Tensor, weight_pairs: torch.Tensor) -> torch.Tensor:
     """silu(x @ gate.T) * (x @ up.T) for a weight whose rows alternate gate_j,
     up_j; [R, I] in x's dtype.  For a few bfloat16 rows the activation is the
@@ -182,6 +252,8 @@ def linear_swiglu(x: torch.Tensor, weight_pairs: torch.Tensor) -> torch.Tensor:
     R, K = x.shape
     if x.dtype == torch.bfloat16 and R <= GEMV_MAX_ROWS and K % 8 == 0:
         return gemm_tc(x, weight_pairs, torch.bfloat16, swiglu_pairs=True)
+    if isinstance(x, NormedInput):
+        raise InvalidInput("a NormedInput is only made for sizes the fused product takes")
     return swiglu(linear(x, weight_pairs), alternating=True)
 
 

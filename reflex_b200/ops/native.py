@@ -28,7 +28,9 @@ _SIGNATURES = {
     "rfx_add": [c_void_p, c_void_p, c_int, c_longlong, c_void_p],
     "rfx_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "rfx_gemm_bf16_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                         c_void_p],
+                         c_int, c_int, c_float, c_void_p, c_void_p],
+    "rfx_gemm_bf16_tc_residual": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                                  c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "rfx_gemv_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "rfx_qkv_post": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p, c_int,
                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
@@ -70,6 +72,8 @@ def lib() -> ctypes.CDLL:
                 raise CudaError(f"native library {path} lacks symbol {name}") from e
             fn.argtypes = argtypes
             fn.restype = c_int
+        handle.rfx_gemm_bf16_tc_max_parts.argtypes = [c_int]
+        handle.rfx_gemm_bf16_tc_max_parts.restype = c_int
         handle.rfx_error_string.argtypes = [c_int]
         handle.rfx_error_string.restype = ctypes.c_char_p
         _lib = handle

@@ -76,7 +76,13 @@ class GQAttention:
             self.q_norm = tensors["q_norm"].to(device=self.device, dtype=torch.float32).contiguous()
             self.k_norm = tensors["k_norm"].to(device=self.device, dtype=torch.float32).contiguous()
 
-    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+    supports_fused_residual = True
+
+    def forward(self, x, ctx, residual=None):
+        """x: normed rows (or rows awaiting their norm factor, `ops.NormedInput`).
+        With `residual` = (hidden, next norm) the output projection may add
+        itself to `hidden` and hand on the rows for the product after that norm
+        (an `ops.NormedInput`); otherwise the delta [rows, hidden] is returned."""
         s = self.spec
         kv = ctx.kv  # the cache entry's view
         batch = ctx.batch
@@ -91,4 +97,8 @@ class GQAttention:
             s.head_dim, ctx.writes_cache, self.dtype)
         attn = ops.attention(q, kv.k_pages, kv.v_pages, kv.page_table, kv.page_size, batch,
                              s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale)
+        if residual is not None:
+            fused = ops.linear_residual(attn, self.o, residual[0], residual[1])
+            if fused is not None:
+                return fused
         return ops.linear(attn, self.o, out_dtype=torch.float32)

@@ -54,9 +54,25 @@ class PreNormBlock:
         self.mixer.bind(by_part.get("mixer", {}))
         self.feed_forward.bind(by_part.get("feed_forward", {}))
 
-    def forward(self, hidden: torch.Tensor, pending: Optional[torch.Tensor], ctx):
-        x = self.mixer_norm(hidden, delta=pending)
-        a = self.mixer.forward(x, ctx)
-        x = self.feed_forward_norm(hidden, delta=a)
-        f = self.feed_forward.forward(x)
+    def forward(self, hidden: torch.Tensor, pending, ctx, next_norm=None):
+        """`pending` is what the block before left: a delta still to be added to
+        `hidden`, or (fused decode path) an `ops.NormedInput`: `hidden` already
+        holds the sum and the rows only await this block's first norm factor.
+        `next_norm` is the norm that will consume this block's result; parts that
+        can fuse the residual add and that norm into their last product do so."""
+        from .. import ops
+
+        if isinstance(pending, ops.NormedInput):
+            x = pending
+        else:
+            x = self.mixer_norm(hidden, delta=pending)
+        if getattr(self.mixer, "supports_fused_residual", False):
+            a = self.mixer.forward(x, ctx, residual=(hidden, self.feed_forward_norm))
+        else:
+            a = self.mixer.forward(x, ctx)
+        x = a if isinstance(a, ops.NormedInput) else self.feed_forward_norm(hidden, delta=a)
+        if getattr(self.feed_forward, "supports_fused_residual", False):
+            f = self.feed_forward.forward(x, residual=(hidden, next_norm))
+        else:
+            f = self.feed_forward.forward(x)
         return hidden, f

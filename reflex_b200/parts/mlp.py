@@ -45,6 +45,15 @@ class SwiGLU:
         self.gate_up = torch.stack([g, u], dim=1).reshape(2 * g.shape[0], g.shape[1]).contiguous()
         self.down = dev(tensors["down_proj"]).contiguous()
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    supports_fused_residual = True
+
+    def forward(self, x, residual=None):
+        """With `residual` = (hidden, next norm) the down projection may add itself
+        to `hidden` and return the rows for the product after that norm
+        (`ops.NormedInput`); otherwise it returns the delta."""
         act = ops.linear_swiglu(x, self.gate_up)
+        if residual is not None:
+            fused = ops.linear_residual(act, self.down, residual[0], residual[1])
+            if fused is not None:
+                return fused
         return ops.linear(act, self.down, out_dtype=torch.float32)

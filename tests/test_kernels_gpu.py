@@ -132,6 +132,39 @@ def test_gemm_tc_with_the_swiglu_epilogue(R, I, K):
     ops().check_device_errors(DEV)
 
 
+@pytest.mark.parametrize("R,N,K", [(1, 64, 64), (5, 96, 320), (8, 4096, 4096), (64, 4096, 12288), (17, 1000, 96)])
+def test_gemm_tc_residual_add_with_the_norm_folded_into_the_next_product(R, N, K):
+    """hidden += x W^T in the product's epilogue, the rows handed on unnormalised
+    with partial sums of squares, and the next product scaling its rows by the
+    norm factor: against add, RMSNorm, product done one after the other in
+    double precision."""
+    g = torch.Generator().manual_seed(R + N + K)
+    x = torch.randn(R, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    h = torch.randn(R, N, generator=g) * 2
+    nw = 1 + 0.1 * torch.randn(N, generator=g)
+    w2 = (torch.randn(2 * 24, N, generator=g) * 0.05).bfloat16()
+    eps = 1e-5
+    for ks in (0, 1, 2, 4, 8):
+        if ks > 1 and (K + 63) // 64 < ks:
+            continue
+        hd = h.to(DEV).clone()
+        ni = ops().gemm_tc_residual(x.to(DEV), w.to(DEV), hd, nw.to(DEV), 0.0, eps, ksplit=ks)
+        h_ref = h.double().numpy() + x.double().numpy() @ w.double().numpy().T
+        assert relerr(hd, h_ref) < 3e-6 * math.sqrt(K)
+        assert relerr(ni.hb, h_ref * nw.double().numpy()) < 5e-3
+        ssq = ni.ssq[: ni.n_part].sum(dim=0)
+        assert relerr(ssq, (h_ref * h_ref).sum(axis=1)) < 1e-4  # 32-bit h, K products each
+        normed = pm.rms_norm(h_ref, nw.double().numpy(), eps)
+        y = ops().linear(ni, w2.to(DEV), out_dtype=torch.float32)
+        assert relerr(y, normed @ w2.double().numpy().T) < 8e-3, ks
+        act = ops().linear_swiglu(ni, w2.to(DEV))
+        full = normed @ w2.double().numpy().T
+        gt, up = full[:, 0::2], full[:, 1::2]
+        assert relerr(act, gt / (1 + np.exp(-gt)) * up) < 1.2e-2, ks
+    ops().check_device_errors(DEV)
+
+
 def test_gemm_tc_refuses_what_it_cannot_do():
     from reflex_b200 import CudaError
 

@@ -41,7 +41,7 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;
 // every CTA stores %globaltimer at entry, after the dependency wait, when the
 // accumulator is complete and at exit, in the record of its launch.
 struct TraceRec {
-    unsigned long long t[4];
+    unsigned long long t[8];
 };
 static __device__ TraceRec* g_trace = nullptr;
 static __device__ int g_trace_ctas = 0;   // records per launch
@@ -116,6 +116,8 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int per = (num_kb + ksplit - 1) / ksplit;
     const int kb0 = z * per;
     const int nkb = max(0, min(num_kb, kb0 + per) - kb0);
+    // rows of the tile that each rank of a K-split cluster finishes
+    const int mw = (EPI == 1) ? ((((bm + ksplit - 1) / ksplit) + 1) & ~1) : (bm + ksplit - 1) / ksplit;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
@@ -230,40 +232,97 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         tc_fence_after_sync();
         if (warp == 2 && lane == 0) trace_mark(trace_id, 2);
-        float* partial = reinterpret_cast<float*>(tiles);  // [BN][BM], reuses the drained stages
+        // after the stages: a tile of [BN][BM] floats that receives partial rows from
+        // the cluster's ranks (it must not alias the stages: a rank that is done
+        // early sends while this CTA may still be streaming)
+        float* stage0 = reinterpret_cast<float*>(tiles + (size_t)stages * S::STAGE_BYTES);
+        if (ksplit > 1) {
+            // Split K: this CTA's tile is a partial sum.  Row m of the tile belongs to
+            // rank m / mw of the cluster; send it there (remote shared-memory stores,
+            // nothing waits on them) into slot [this rank][column][m % mw].
+            cg::cluster_group cluster = cg::this_cluster();
+            const int owner = m / mw, ml = m % mw;
+            float* dst = cluster.map_shared_rank(stage0, owner < ksplit ? owner : 0) + (size_t)z * BN * mw + ml;
 #pragma unroll 1
-        for (int c = 0; c < BN / 16; ++c) {
-            float v[16];
-            if (have) {
-                tmem_ld_16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 16), v);
-            } else {
+            for (int c = 0; c < BN / 16; ++c) {
+                float v[16];
+                if (have) {
+                    tmem_ld_16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 16), v);
+                } else {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                    for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                }
+                if (m < bm) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) dst[(c * 16 + j) * mw] = v[j];
+                }
             }
+        } else {
+            // One CTA has the whole sum: finish straight from the registers.
+            float* sq = stage0;  // [BN][BM] squares of the new residual (EPI 2)
+#pragma unroll 1
+            for (int c = 0; c < BN / 16; ++c) {
+                float v[16];
+                if (have) {
+                    tmem_ld_16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 16), v);
+                } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) partial[(c * 16 + j) * BM + m] = v[j];
+                    for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int rr = c * 16 + j, r = r0 + rr, n = n0 + m;
+                    float a = v[j];
+                    if (PRO) a *= rstd_s[rr];
+                    if (EPI == 0) {
+                        if (r < R && m < bm && n < N) rfx::st<TO>(y, (size_t)r * N + n, a);
+                    } else if (EPI == 1) {
+                        const float up = __shfl_down_sync(0xffffffffu, a, 1);  // the odd row above
+                        if ((m & 1) == 0 && r < R && m + 1 < bm && n + 1 < N)
+                            rfx::st<TO>(y, (size_t)r * (N / 2) + n / 2, silu_mul(a, up));
+                    } else {
+                        float hv = 0.0f;
+                        if (r < R && m < bm && n < N) {
+                            const size_t idx = (size_t)r * N + n;
+                            hv = fuse.h[idx] + a;
+                            fuse.h[idx] = hv;
+                            fuse.hb[idx] = __float2bfloat16_rn(hv * (fuse.nw_offset + fuse.nw[n]));
+                        }
+                        sq[rr * BM + m] = hv * hv;
+                    }
+                }
+            }
+            if (EPI == 2) {
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                // this CTA's partial of each row's sum of squares, added in index order
+                if (m < BN && r0 + m < R) {
+                    float tot = 0.0f;
+                    for (int i = 0; i < bm; ++i) tot += sq[m * BM + i];
+                    fuse.ssq_out[(size_t)blockIdx.x * R + r0 + m] = tot;
+                }
+            }
         }
         tc_fence_before_sync();
     }
 
-    // Every CTA of the cluster (or just this one) has its partial tile in shared
-    // memory; rank z finishes its share of the tile's rows: the sum over the ranks
-    // in rank order, then the epilogue.
-    {
+    if (ksplit > 1) {
+        // After one cluster barrier every rank holds all ranks' partial rows of its
+        // share of the tile in its own shared memory: [rank][column][row].  Sum in
+        // rank order, then the epilogue.  Nobody reads remote memory after the
+        // barrier, so CTAs may leave as they finish.
         cg::cluster_group cluster = cg::this_cluster();
         rfx::pdl_wait();
-        if (ksplit > 1) cluster.sync();
-        else __syncthreads();
-        float* partial = reinterpret_cast<float*>(tiles);
-        float* sq = partial + BN * BM;  // [BN][mw] squares of the new residual (EPI 2)
-        int mw = (bm + ksplit - 1) / ksplit;
-        if (EPI == 1) mw = (mw + 1) & ~1;  // gate and up of a pair stay with one rank
+        if (threadIdx.x == 64) trace_mark(trace_id, 4);
+        cluster.sync();
+        if (threadIdx.x == 64) trace_mark(trace_id, 5);
+        const float* recv = reinterpret_cast<const float*>(tiles + (size_t)stages * S::STAGE_BYTES);
+        float* sq = reinterpret_cast<float*>(tiles);  // [BN][mw]; this CTA's stages are drained
         if (EPI == 0) {
             for (int e = threadIdx.x; e < BN * mw; e += THREADS) {
-                const int rr = e / mw, mm = z * mw + e % mw;
+                const int rr = e / mw, ml = e % mw, mm = z * mw + ml;
                 if (mm >= bm) continue;
                 float acc = 0.0f;
-                for (int p = 0; p < ksplit; ++p) acc += cluster.map_shared_rank(partial, p)[rr * BM + mm];
+                for (int p = 0; p < ksplit; ++p) acc += recv[((size_t)p * BN + rr) * mw + ml];
                 if (PRO) acc *= rstd_s[rr];
                 const int r = r0 + rr;
                 if (r < R && n0 + mm < N) rfx::st<TO>(y, (size_t)r * N + n0 + mm, acc);
@@ -271,13 +330,12 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         } else if (EPI == 1) {
             const int pw = mw / 2;
             for (int e = threadIdx.x; e < BN * pw; e += THREADS) {
-                const int rr = e / pw, mm = z * mw + 2 * (e % pw);
+                const int rr = e / pw, ml = 2 * (e % pw), mm = z * mw + ml;
                 if (mm + 1 >= bm) continue;
                 float g = 0.0f, u = 0.0f;
                 for (int p = 0; p < ksplit; ++p) {
-                    const float* remote = cluster.map_shared_rank(partial, p);
-                    g += remote[rr * BM + mm];
-                    u += remote[rr * BM + mm + 1];
+                    g += recv[((size_t)p * BN + rr) * mw + ml];
+                    u += recv[((size_t)p * BN + rr) * mw + ml + 1];
                 }
                 if (PRO) {
                     g *= rstd_s[rr];
@@ -294,7 +352,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 float hv = 0.0f;
                 if (mm < bm && r < R && n < N) {
                     float acc = 0.0f;
-                    for (int p = 0; p < ksplit; ++p) acc += cluster.map_shared_rank(partial, p)[rr * BM + mm];
+                    for (int p = 0; p < ksplit; ++p) acc += recv[((size_t)p * BN + rr) * mw + ml];
                     const size_t idx = (size_t)r * N + n;
                     hv = fuse.h[idx] + acc;
                     fuse.h[idx] = hv;
@@ -307,11 +365,10 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             if ((int)threadIdx.x < BN && r0 + (int)threadIdx.x < R) {
                 float tot = 0.0f;
                 for (int i = 0; i < mw; ++i) tot += sq[threadIdx.x * mw + i];
-                const int part = blockIdx.x * ksplit + z;
-                fuse.ssq_out[(size_t)part * R + r0 + threadIdx.x] = tot;
+                fuse.ssq_out[((size_t)blockIdx.x * ksplit + z) * R + r0 + threadIdx.x] = tot;
             }
         }
-        if (ksplit > 1) cluster.sync();  // nobody leaves while its shared memory is still read
+        if (threadIdx.x == 64) trace_mark(trace_id, 6);
     }
 
     __syncthreads();
@@ -429,6 +486,13 @@ Cut choose_cut(int N, int r_tiles, int num_kb, int ks_req) {
         if (best_ks) return Cut{best_bm, best_tiles, best_ks};
     }
     const int tiles = (N + BM - 1) / BM;
+    // Between one and two 128-row tiles per SM the SMs that get two CTAs finish
+    // late while the rest idle: cut lower tiles instead, two per SM, equal work.
+    if (r_tiles == 1 && tiles > sms && tiles < 2 * sms && env_int("REFLEX_B200_GEMM_EVEN", 1)) {
+        int bm = (N + 2 * sms - 1) / (2 * sms);
+        bm = (bm + 1) & ~1;
+        if (bm >= 32 && bm <= BM) return Cut{bm, (N + bm - 1) / bm, 1};
+    }
     int ks = 1;
     while (ks < 8 && tiles * r_tiles * ks * 2 <= 2 * sms && num_kb >= ks * 4) ks *= 2;
     return Cut{BM, tiles, ks};
@@ -460,11 +524,13 @@ int launch(const void* x, const void* W, void* y, int R, int N, int K, int kspli
     if (st_env >= 2) stages = st_env;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 2) stages = 2;
-    // the drained stages hold the partial tile (and the squares of EPI 2) afterwards
-    if (stages * S::STAGE_BYTES < BN * BM * 4 * (EPI == 2 ? 2 : 1)) return RFX_ERR_UNSUPPORTED;
+    // after the stages, the tile that receives the cluster's partial rows
+    constexpr int RECV_BYTES = BN * BM * 4;
+    while (stages > 3 && stages * S::STAGE_BYTES + RECV_BYTES > 112 * 1024) --stages;
+    if (stages * S::STAGE_BYTES < BN * BM * 4) return RFX_ERR_UNSUPPORTED;  // the squares of EPI 2
     if (n_part_out) *n_part_out = cut.tiles * ks;
     if (EPI == 2 && r_tiles != 1) return RFX_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)stages * S::STAGE_BYTES + 1024;
+    const size_t smem = (size_t)stages * S::STAGE_BYTES + RECV_BYTES + 1024;
     auto kernel = gemm_wt_kernel<BN, TO, EPI, PRO>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;

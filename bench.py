@@ -120,7 +120,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0 = all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 decode points")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -234,7 +235,7 @@ def main() -> int:
                      "frac": achieved / pk["hbm_gbs"], "of": pk["source"]},
     }
 
-    if not args.no_points:
+    if not args.no_prefill:
         # prefill of one 2,048-token prompt
         prompt = torch.randint(0, V, (PREFILL_TOKENS,), generator=g).tolist()
         times = []
@@ -254,6 +255,7 @@ def main() -> int:
         out["prefill"] = {"value": PREFILL_TOKENS * 1000.0 / pms, "tokens": PREFILL_TOKENS, "ms": pms,
                           "frac": fl / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), "flops": fl,
                           "peak_tflops": pk["bf16_tflops"], "of": pk["source"]}
+    if not args.no_points:
         points = {}
         for b in (1, 64):
             st = min(args.steps, 64)

@@ -32,6 +32,9 @@ class StepBatch:
     seq_new: torch.Tensor      # [S]
     seq_row0: torch.Tensor     # [S + 1]
     want_rows: torch.Tensor    # [n_want]
+    # set by a captured decode step: an upper bound of the longest context for
+    # every step that replays the capture (kernels size their launches by it)
+    context_hint: Optional[int] = None
 
     @property
     def n_rows(self) -> int:
@@ -51,6 +54,8 @@ class StepBatch:
 
     @property
     def max_context(self) -> int:
+        if self.context_hint is not None:
+            return self.context_hint
         return max(s + n for s, n in zip(self.starts, self.new_counts))
 
 

@@ -18,9 +18,12 @@ from .batch import layout, make_batch
 class DecodeGraph:
     WARMUP = 2
 
-    def __init__(self, engine, n_seqs: int):
+    def __init__(self, engine, n_seqs: int, context_hint: int):
         self.engine = engine
         self.n = n_seqs
+        # kernels that size themselves by the longest context see this bucket's
+        # upper end, so that the captured launches fit every step that uses it
+        self.context_hint = context_hint
         _, total = layout(n_seqs, n_seqs, n_seqs)
         self.buffer = torch.zeros((total,), dtype=torch.int32, device=engine.device)
         self.graph = None
@@ -31,9 +34,14 @@ class DecodeGraph:
     def run(self, tokens, slots, starts, want) -> torch.Tensor:
         eng = self.engine
         batch = make_batch(tokens, slots, starts, want, eng.device, buffer=self.buffer)
+        batch.context_hint = self.context_hint
         if self.graph is None:
-            self.calls += 1
-            if self.calls <= self.WARMUP:
+            # the first decode steps of a batch size run eagerly: they size every
+            # lazily allocated buffer; later graphs of that size capture at once
+            done = eng._eager_decodes.get(self.n, 0)
+            if done < self.WARMUP:
+                eng._eager_decodes[self.n] = done + 1
+                batch.context_hint = None
                 return eng.model.forward(batch, eng.cache)
             # capture: the eager call above has already sized every lazy buffer
             torch.cuda.synchronize()

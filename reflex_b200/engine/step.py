@@ -34,7 +34,8 @@ class Engine:
                            model.dtype, model.device, max_slots=max_slots)
         self.vocab_size = model.spec.vocab_size
         self.use_graphs = use_graphs and model.dtype == torch.bfloat16
-        self._graphs: Dict[int, "object"] = {}
+        self._graphs: Dict[Tuple[int, int], "object"] = {}
+        self._eager_decodes: Dict[int, int] = {}  # eager decode steps run so far, per batch size
         self.steps_run = 0
 
     # --- sequences ----------------------------------------------------------
@@ -104,14 +105,23 @@ class Engine:
         from .graphs import DecodeGraph
 
         n = len(tokens)
-        g = self._graphs.get(n)
+        # the launch set depends on the batch size and, through the attention
+        # kernel's key splits, on how long the longest context is: one graph per
+        # (batch size, bucket of its pages: steps of 4 pages up to 32, then powers of two)
+        pages = -(-(max(starts) + 1) // PAGE_TOKENS)
+        bucket = -(-pages // 4) * 4 if pages <= 32 else 1 << (pages - 1).bit_length()
+        key = (n, bucket)
+        g = self._graphs.get(key)
         if g is None:
-            g = DecodeGraph(self, n)
-            self._graphs[n] = g
+            g = DecodeGraph(self, n, bucket * PAGE_TOKENS)
+            self._graphs[key] = g
         return g.run(tokens, slots, starts, want)
 
     def launches_per_decode_step(self, n_seqs: int) -> int:
         """This library's kernels in one decode step of `n_seqs` sequences
         (counted when the step's graph was captured; 0 if it never ran)."""
-        g = self._graphs.get(n_seqs)
-        return g.kernels if g is not None else 0
+        best = 0
+        for (n, _bucket), g in self._graphs.items():
+            if n == n_seqs:
+                best = max(best, g.kernels)
+        return best

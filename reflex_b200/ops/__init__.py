@@ -13,6 +13,8 @@ from typing import Optional
 import torch
 
 from ..errors import CudaError, InvalidInput
+import os as _os
+
 from . import native
 
 F32, BF16 = 0, 1
@@ -240,8 +242,6 @@ def linear_residual(x: torch.Tensor, weight: torch.Tensor, hidden: torch.Tensor,
     return gemm_tc_residual(x, weight, hidden, w, spec.weight_offset, spec.eps)
 
 
-import os as _os
-
 FUSE_NORM = _os.environ.get("REFLEX_B200_FUSE_NORM", "1") != "0"
 
 
@@ -308,15 +308,27 @@ def gemv_simple(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = 
 
 
 SM_COUNT = 148
-DECODE_MAX_SPLITS = 16
 
 
-def decode_splits(n_rows: int, nq: int, nkv: int) -> int:
-    """Key-range splits of the decode kernel: enough CTAs for two per SM.  It
-    depends on the batch size only, so a captured decode step stays valid while
-    contexts grow."""
+def decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int = 64) -> int:
+    """Key-range splits of the decode kernel for rows whose longest context has
+    `max_pages` pages.  A split costs a second kernel (the combine) and buys
+    parallelism; fitted to step times on a B200 at batches of 1, 8 and 64: about
+    4 us fixed per launch, 0.8 us per page a CTA walks, 4 us for the partials,
+    the combine and its hand-off.  The smallest estimate wins."""
+    forced = int(_os.environ.get("REFLEX_B200_DECODE_SPLITS", "0"))  # tuning aid
+    if forced > 0:
+        return forced
     ctas = n_rows * nkv * ((nq // nkv + 15) // 16)
-    return max(1, min(DECODE_MAX_SPLITS, -(-2 * SM_COUNT // ctas)))
+    best, best_cost = 1, None
+    for s in (1, 2, 4, 8, 16):
+        if s > max(1, max_pages):
+            break
+        waves = max(1.0, ctas * s / (2.0 * SM_COUNT))
+        cost = 4.0 + -(-max_pages // s) * 0.8 * waves + (4.0 if s > 1 else 0.0)
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
 
 
 def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_slot, nq, nkv,
@@ -387,8 +399,10 @@ def attention(q, k_pages, v_pages, page_table, page_size, batch, nq, nkv, head_d
     values; picks the kernel for the dtype and the kind of step."""
     fast = q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256
     if fast and batch.is_decode:
+        pages = -(-min(batch.max_context, window or batch.max_context) // page_size) + (1 if window else 0)
         return attention_decode(q, k_pages, v_pages, page_table, page_size, batch.row_pos,
-                                batch.row_slot, nq, nkv, head_dim, window, scale)
+                                batch.row_slot, nq, nkv, head_dim, window, scale,
+                                n_splits=decode_splits(q.shape[0], nq, nkv, pages))
     if fast and nq // nkv <= 128 and head_dim in (64, 128):
         return attention_prefill_tc(q, k_pages, v_pages, page_table, page_size, batch.seq_slot,
                                     batch.seq_start, batch.seq_new, batch.seq_row0, batch.max_new, nq,

@@ -158,7 +158,7 @@ def test_decode_graphs_equal_eager_steps():
     a = helpers.run_tail_one_by_one(helpers.make_engine(folder, "bfloat16", use_graphs=False), toks, 40)
     eng = helpers.make_engine(folder, "bfloat16", use_graphs=True)
     b = helpers.run_tail_one_by_one(eng, toks, 40)
-    assert eng._graphs and eng._graphs[1].graph is not None
+    assert eng._graphs and all(g.graph is not None for g in eng._graphs.values())
     assert np.array_equal(a, b)
 
 

@@ -1,0 +1,3 @@
+"""The C interface of the engine: `reflex_b200.h` declares it,
+`engine_abi.cpp` implements it over `bridge.py`, `build.py` compiles it into
+`libreflex_b200_engine.so`."""

@@ -112,7 +112,9 @@ class Model:
         """Float32 logits [len(prompt), vocab] of one whole prompt."""
         s = self.engine.open()
         try:
-            return self.engine.step([(s, list(prompt), list(range(len(prompt))))]).clone()
+            logits = self.engine.step([(s, list(prompt), list(range(len(prompt))))]).clone()
+            self.engine.check_errors()
+            return logits
         finally:
             self.engine.close(s)
 
@@ -143,6 +145,7 @@ class Model:
             logits = eng.step(entries)
             idx = torch.tensor([t for c in candidates for t in c], dtype=torch.int64, device=logits.device)
             picked = logits.gather(1, idx[:, None])[:, 0].tolist()
+            eng.check_errors()
         finally:
             for s in seqs:
                 eng.close(s)

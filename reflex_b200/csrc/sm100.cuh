@@ -59,15 +59,18 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // Wait with a time limit.  Returns false when the limit ran out; the caller
 // then records the place, stops issuing work and goes to its teardown.
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (global_timer_ns() - t0 > WAIT_LIMIT_NS) return false;
+        if (global_timer_ns() - t0 > limit_ns) return false;
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    return mbar_wait_for(bar, parity, WAIT_LIMIT_NS);
 }
 
 // ---- TMA --------------------------------------------------------------------

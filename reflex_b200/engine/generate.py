@@ -77,6 +77,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int,
     stats = stats if stats is not None else GenerationStats()
     outputs: List[List[int]] = [[] for _ in prompts]
     max_batch = max(1, min(max_batch, engine.cache.max_slots))
+    check_errors = getattr(engine, "check_errors", lambda: None)
     for batch in plan_batches([len(p) for p in prompts], max_new_tokens, engine.cache.max_tokens, max_batch):
         stats.batches += 1
         live = list(batch)
@@ -87,11 +88,13 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int,
             first = True
             while live:
                 logits = engine.step(entries)
+                ids = pick(logits, live, [len(outputs[i]) for i in live])
+                if first or stats.decode_steps % 64 == 0:
+                    check_errors()  # the picked ids are on the host: the device has been waited for
                 if not first:
                     stats.decode_steps += 1
                     stats.decode_tokens += len(live)
                 first = False
-                ids = pick(logits, live, [len(outputs[i]) for i in live])
                 still = []
                 for i, tok in zip(live, ids):
                     tok = int(tok)
@@ -104,6 +107,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int,
                         still.append(i)
                 live = still
                 entries = [(seqs[i], [outputs[i][-1]], [0]) for i in live]
+            check_errors()
         finally:
             for s in seqs.values():
                 engine.close(s)

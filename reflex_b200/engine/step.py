@@ -50,6 +50,14 @@ class Engine:
     def length(self, seq: int) -> int:
         return self.cache.length(seq)
 
+    def check_errors(self) -> None:
+        """Raises `CudaError` if a kernel of an earlier step gave up a bounded
+        wait (its results are then not valid).  Synchronises: callers use it
+        where they wait for the device anyway."""
+        from .. import ops
+
+        ops.check_device_errors(self.device)
+
     # --- the step -------------------------------------------------------------
     def _check(self, entries: Sequence[StepEntry]) -> None:
         if not entries:

@@ -52,6 +52,7 @@ class TraceRunner:
                     path = os.path.join(self.out_dir, f"{step}.f32")
                     with open(path, "wb") as f:
                         f.write(host.numpy().astype("<f4", copy=False).tobytes())
+                self.engine.check_errors()
         except Exception:
             for rid in opened:
                 self.engine.close(self.live.pop(rid))

@@ -130,6 +130,15 @@ def check_device_errors(device="cuda:0") -> None:
         raise CudaError(f"a kernel gave up a bounded wait (code {code}); its results are not valid")
 
 
+def wait_probe(limit_ns: int, device="cuda:0") -> None:
+    """Launches one block that waits, for at most `limit_ns` (clamped to a
+    second), on a barrier nothing signals: the bounded wait runs out and the
+    kernel records it in the device's error word, as the tensor-core kernels do
+    when a copy or a product never arrives."""
+    st = native.lib().rfx_wait_probe(int(limit_ns), device_error_word(device).data_ptr(), _stream())
+    native.check(st, "wait_probe")
+
+
 class NormedInput:
     """Rows that still await their RMSNorm factor: `hb` = bfloat16(h * norm
     weight) and `ssq[p][r]`, partial sums of squares of h's row r.  The product

@@ -45,6 +45,7 @@ _SIGNATURES = {
     "rfx_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p,
                                  c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_int, c_float, c_void_p, c_void_p],
+    "rfx_wait_probe": [c_longlong, c_void_p, c_void_p],
     "rfx_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "rfx_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                    c_void_p, c_void_p, c_void_p],

@@ -417,3 +417,31 @@ def test_sampling_distribution():
     p = np.exp(row.double().numpy() / 0.7)
     p /= p.sum()
     np.testing.assert_allclose(np.bincount(got, minlength=V) / n, p, atol=1.5e-3)
+
+
+# ------------------------------------------------------------------ bounded waits
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_device_stays_usable():
+    """One block waits a millisecond on a barrier that nothing signals.  The
+    wait gives up, the kernel records it and returns; the host reads the
+    device's error word as an exception, once, and later work is right."""
+    import helpers
+    from reflex_b200.errors import CudaError
+
+    o = ops()
+    o.check_device_errors(DEV)
+    o.wait_probe(1_000_000, DEV)
+    torch.cuda.synchronize()
+    with pytest.raises(CudaError, match="bounded wait"):
+        o.check_device_errors(DEV)
+    o.check_device_errors(DEV)  # reported once, then clear
+
+    engine = helpers.make_engine(helpers.model_folder("A", 7, "bfloat16"), "bfloat16")
+    o.wait_probe(1_000_000, DEV)
+    with pytest.raises(CudaError, match="bounded wait"):
+        engine.check_errors()
+    tokens = helpers.random_tokens(40, 512, 3)
+    got = helpers.run_whole(engine, tokens)
+    engine.check_errors()
+    assert helpers.rel_err(got, helpers.plain_logits(helpers.model_folder("A", 7, "bfloat16"), tokens)) < 1.5e-2

@@ -20,8 +20,18 @@ using namespace rfx;
 
 constexpr int MAX_PER_LANE = 16;  // head_dim <= 512
 
-// PER: elements of a head vector per lane, head_dim <= 32 * PER
-template <typename TI, typename TO, int PER>
+template <typename T, int N>
+struct alignas(sizeof(T) * N <= 16 ? sizeof(T) * N : 16) Pack {
+    T a[N];
+};
+
+// PER: elements of a head vector per lane, head_dim <= 32 * PER.
+// VEC: head_dim == 32 * PER and a lane holds PER neighbouring elements, moved
+// with one wide access; a rotary pair (e, e + rd/2) then lies in two lanes at
+// the same place of their packs and is exchanged by a shuffle (rd/2 a multiple
+// of PER).  Otherwise lane l holds elements l, l + 32, ... and the pair is
+// exchanged through shared memory.
+template <typename TI, typename TO, int PER, bool VEC>
 __global__ void __launch_bounds__(256)
 qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restrict__ q_w,
                 const float* __restrict__ k_w, float eps, float w_offset,
@@ -62,6 +72,44 @@ qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restr
             dst = k_pages + kv_offset(cache, slot, pos, hh - nq);
         } else {
             dst = v_pages + kv_offset(cache, slot, pos, hh - nq - nkv_in);
+        }
+        if constexpr (VEC) {
+            const Pack<TI, PER> in = *reinterpret_cast<const Pack<TI, PER>*>(src + lane * PER);
+            float v[PER];
+#pragma unroll
+            for (int i = 0; i < PER; ++i) v[i] = ld<TI>(in.a, i);
+            if (is_q || is_k) {
+                const float* w = is_q ? q_w : k_w;
+                if (w) {
+                    float ss = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < PER; ++i) ss = fmaf(v[i], v[i], ss);
+                    const float rinv = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);
+                    const Pack<float, PER> ww = *reinterpret_cast<const Pack<float, PER>*>(w + lane * PER);
+#pragma unroll
+                    for (int i = 0; i < PER; ++i) v[i] = (v[i] * rinv) * (w_offset + ww.a[i]);
+                }
+                if (rope_denom != nullptr && half > 0) {
+                    const int hl = half / PER;  // lanes in half a rotation
+                    const int e0 = lane * PER;
+                    const int partner = lane < hl ? lane + hl : lane - hl;
+#pragma unroll
+                    for (int i = 0; i < PER; ++i) {
+                        const float other = __shfl_sync(0xffffffffu, v[i], partner & 31);
+                        const int e = e0 + i;
+                        if (e < rotary_dim) {
+                            const int fi = e < half ? e : e - half;
+                            const float sn = sn_tab[fi], cs = cs_tab[fi];
+                            v[i] = e < half ? v[i] * cs - other * sn : other * sn + v[i] * cs;
+                        }
+                    }
+                }
+            }
+            Pack<TO, PER> o;
+#pragma unroll
+            for (int i = 0; i < PER; ++i) st<TO>(o.a, i, v[i]);
+            *reinterpret_cast<Pack<TO, PER>*>(dst + lane * PER) = o;
+            continue;
         }
         if (!is_q && !is_k) {  // v: stored as projected
             for (int e = lane; e < d; e += 32) st<TO>(dst, e, ld<TI>(src, e));
@@ -131,12 +179,30 @@ extern "C" int rfx_qkv_post(const void* qkv, int in_dt, int row_stride, const fl
     const int threads = 256;  // eight heads a block
     const size_t smem = ((size_t)(threads / 32) * head_dim + rotary_dim) * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
-    const int head_blocks = (nq + 2 * nkv_in + threads / 32 - 1) / (threads / 32);
+    // Few rows (decode): spread a row's heads over several blocks.  Many rows
+    // (prefill): one block a row, so the rotation table is made once per row.
+    int head_blocks = (nq + 2 * nkv_in + threads / 32 - 1) / (threads / 32);
+    if (R >= 512) head_blocks = 1;
     dim3 grid(R, head_blocks < 65535 ? head_blocks : 65535);
-#define RFX_POST_P(TI, TO, P)                                                                  \
-    RFX_LAUNCH((qkv_post_kernel<TI, TO, P>), grid, threads, smem, s, (const TI*)qkv, row_stride,   \
-               q_w, k_w, eps, w_offset, rope_denom, rotary_dim, row_pos, row_slot, (TO*)q_out,     \
-               (TO*)k_pages, (TO*)v_pages, cache, nq, nkv_in)
+    // the wide-access form: a whole head in 32 lanes' packs, pairs a whole number of lanes apart
+    const int per = head_dim / 32;
+    const uintptr_t ptrs = reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
+                           reinterpret_cast<uintptr_t>(k_pages) | reinterpret_cast<uintptr_t>(v_pages) |
+                           reinterpret_cast<uintptr_t>(q_w) | reinterpret_cast<uintptr_t>(k_w);
+    const bool vec = head_dim % 32 == 0 && (per == 1 || per == 2 || per == 4 || per == 8 || per == 16) &&
+                     (rope_denom == nullptr || rotary_dim == 0 || (rotary_dim / 2) % per == 0) &&
+                     row_stride % per == 0 && (ptrs & 15) == 0;
+#define RFX_POST_P(TI, TO, P)                                                                      \
+    do {                                                                                           \
+        if (vec)                                                                                   \
+            RFX_LAUNCH((qkv_post_kernel<TI, TO, P, true>), grid, threads, smem, s, (const TI*)qkv, \
+                       row_stride, q_w, k_w, eps, w_offset, rope_denom, rotary_dim, row_pos,       \
+                       row_slot, (TO*)q_out, (TO*)k_pages, (TO*)v_pages, cache, nq, nkv_in);       \
+        else                                                                                       \
+            RFX_LAUNCH((qkv_post_kernel<TI, TO, P, false>), grid, threads, smem, s, (const TI*)qkv, \
+                       row_stride, q_w, k_w, eps, w_offset, rope_denom, rotary_dim, row_pos,       \
+                       row_slot, (TO*)q_out, (TO*)k_pages, (TO*)v_pages, cache, nq, nkv_in);       \
+    } while (0)
 #define RFX_POST(TI, TO)                                  \
     do {                                                  \
         if (head_dim <= 32) RFX_POST_P(TI, TO, 1);        \

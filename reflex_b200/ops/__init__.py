@@ -237,12 +237,27 @@ def gemm_tc_residual(x: torch.Tensor, weight: torch.Tensor, hidden: torch.Tensor
     return NormedInput(hb, ssq, n_part.value, N, eps)
 
 
-def linear_residual(x: torch.Tensor, weight: torch.Tensor, hidden: torch.Tensor, next_norm) -> Optional[NormedInput]:
-    """The fused form of `hidden += linear(x, weight)` followed by `next_norm`,
-    when the sizes and the norm allow it (a few bfloat16 rows, an RMSNorm with a
-    plain weight); None otherwise, and the caller takes the two-launch way."""
-    if (x.dtype != torch.bfloat16 or x.shape[0] > GEMV_MAX_ROWS or x.shape[1] % 8 or next_norm is None
-            or not FUSE_NORM):
+ADDED = object()  # what `linear_residual` returns when it added into `hidden` and began no norm
+
+
+def linear_residual(x: torch.Tensor, weight: torch.Tensor, hidden: torch.Tensor, next_norm):
+    """The fused forms of `hidden += linear(x, weight)`.
+
+    A few bfloat16 rows and an RMSNorm with a plain weight next: the product
+    kernel's epilogue adds into `hidden` and begins `next_norm`; returns a
+    `NormedInput`.  More bfloat16 rows than that kernel takes: the library
+    product accumulates onto the 32-bit `hidden` in place (C = A B + C with
+    32-bit C, so the sum is never rounded to bfloat16); returns `ADDED`.
+    Otherwise None, and the caller takes the two-launch way."""
+    if x.dtype != torch.bfloat16 or not FUSE_NORM:
+        return None
+    if x.shape[0] > GEMV_MAX_ROWS or x.shape[1] % 8:
+        _chk(x, "x")
+        _chk(weight, "weight", torch.bfloat16)
+        _chk(hidden, "hidden", torch.float32)
+        torch.addmm(hidden, x, weight.t(), out_dtype=torch.float32, out=hidden)
+        return ADDED
+    if next_norm is None:
         return None
     w = getattr(next_norm, "weight", None)
     spec = getattr(next_norm, "spec", None)

@@ -81,8 +81,9 @@ class GQAttention:
     def forward(self, x, ctx, residual=None):
         """x: normed rows (or rows awaiting their norm factor, `ops.NormedInput`).
         With `residual` = (hidden, next norm) the output projection may add
-        itself to `hidden` and hand on the rows for the product after that norm
-        (an `ops.NormedInput`); otherwise the delta [rows, hidden] is returned."""
+        itself to `hidden`; it then returns the rows for the product after that
+        norm (an `ops.NormedInput`) or None (added, the norm not begun).
+        Otherwise the delta [rows, hidden] is returned."""
         s = self.spec
         kv = ctx.kv  # the cache entry's view
         batch = ctx.batch
@@ -99,6 +100,8 @@ class GQAttention:
                              s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale)
         if residual is not None:
             fused = ops.linear_residual(attn, self.o, residual[0], residual[1])
+            if fused is ops.ADDED:
+                return None  # nothing left to add
             if fused is not None:
                 return fused
         return ops.linear(attn, self.o, out_dtype=torch.float32)

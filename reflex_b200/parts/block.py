@@ -56,7 +56,7 @@ class PreNormBlock:
 
     def forward(self, hidden: torch.Tensor, pending, ctx, next_norm=None):
         """`pending` is what the block before left: a delta still to be added to
-        `hidden`, or (fused decode path) an `ops.NormedInput`: `hidden` already
+        `hidden`, None (nothing to add), or an `ops.NormedInput`: `hidden` already
         holds the sum and the rows only await this block's first norm factor.
         `next_norm` is the norm that will consume this block's result; parts that
         can fuse the residual add and that norm into their last product do so."""

@@ -49,11 +49,14 @@ class SwiGLU:
 
     def forward(self, x, residual=None):
         """With `residual` = (hidden, next norm) the down projection may add itself
-        to `hidden` and return the rows for the product after that norm
-        (`ops.NormedInput`); otherwise it returns the delta."""
+        to `hidden`; it then returns the rows for the product after that norm
+        (`ops.NormedInput`) or None (added, the norm not begun).  Otherwise it
+        returns the delta."""
         act = ops.linear_swiglu(x, self.gate_up)
         if residual is not None:
             fused = ops.linear_residual(act, self.down, residual[0], residual[1])
+            if fused is ops.ADDED:
+                return None  # nothing left to add
             if fused is not None:
                 return fused
         return ops.linear(act, self.down, out_dtype=torch.float32)

@@ -96,7 +96,8 @@ def test_attention_part_and_block_against_the_plain_layer(dtype):
         batch = make_batch([part], [s], [start], [[0]], DEV)
         h, pending = model.hidden_states(batch, cache)
         # the last delta is still pending, unless the fused path already added it
-        hs.append(h.clone() if isinstance(pending, ops.NormedInput) else ops.add_(h.clone(), pending))
+        hs.append(h.clone() if pending is None or isinstance(pending, ops.NormedInput)
+                  else ops.add_(h.clone(), pending))
         cache.commit([(s, len(part))])
     got = torch.cat(hs)
     h0 = w["model.embed_tokens.weight"][np.array(toks)]

@@ -63,24 +63,24 @@ struct Shape {
 // What the epilogue does besides storing, for the fused decode path:
 //  * scale_rows (PRO): the activation rows came in unnormalised (x = h * w_norm,
 //    rounded to bfloat16); row r of the result is multiplied by
-//    1 / sqrt(sum_p ssq_in[p][r] / H + eps), the RMSNorm factor, which commutes
+//    1 / sqrt(sum_p ssq_in[r][p] / H + eps), the RMSNorm factor, which commutes
 //    with the product.  The partial sums of squares come from the product that
 //    made h (below).
 //  * EPI 2: the result is a delta of the residual stream: h[r, n] += acc (32-bit,
 //    each element by one thread), hb[r, n] = bfloat16(h * (nw_offset + nw[n])) is
-//    the next product's unnormalised input, and ssq_out[p][r] = sum of h^2 over
+//    the next product's unnormalised input, and ssq_out[r][p] = sum of h^2 over
 //    this CTA's rows n is one partial of the next norm's statistic.
 // Together they replace the separate add + RMSNorm launch between two products
 // (src/kernels_cuda/decode_ops.cu:10-35 is the reference's fused add + norm).
 struct Fuse {
-    const float* ssq_in;   // [n_part_in][R]
+    const float* ssq_in;   // [R][n_part_in]
     int n_part_in;
     float inv_h, eps;
     float* h;              // [R, N] residual stream, updated in place
     const float* nw;       // [N] weight of the norm that follows
     float nw_offset;
     __nv_bfloat16* hb;     // [R, N]
-    float* ssq_out;        // [tiles * ksplit][R]
+    float* ssq_out;        // [R][tiles * ksplit]
 };
 
 // EPI 0: y = x W^T.  EPI 1: W's rows alternate gate, up (row 2j gate_j, row 2j+1
@@ -88,6 +88,23 @@ struct Fuse {
 // launch and no round trip of the [R, 2I] intermediate
 // (src/kernels_cuda/silu_and_mul.cu:7-23 is the reference's separate kernel).
 __device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+
+// four (two) neighbouring results in one access; the address is a multiple of
+// their size by the callers' conditions
+__device__ __forceinline__ void store4(float* p, const float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float4 v) {
+    uint2 u;
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    u.x = *reinterpret_cast<uint32_t*>(&lo);
+    u.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+__device__ __forceinline__ void store2(float* p, float a, float b) {
+    *reinterpret_cast<float2*>(p) = make_float2(a, b);
+}
+__device__ __forceinline__ void store2(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
 
 template <int BN, typename TO, int EPI, bool PRO>
 __global__ void __launch_bounds__(THREADS)
@@ -210,12 +227,31 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int m = q * 32 + lane;
         if (PRO) {
             // the rows' norm factors, while the main loop runs: 128 / BN threads
-            // share a row's partials, then one thread adds their sums in order
+            // share a row's partials (a contiguous run each, read four at a
+            // time), then one thread adds their sums in order
             const int t = m, rl = t % BN, grp = t / BN;
             constexpr int G = 128 / BN;
             float sum = 0.0f;
-            if (r0 + rl < R)
-                for (int p = grp; p < fuse.n_part_in; p += G) sum += fuse.ssq_in[(size_t)p * R + r0 + rl];
+            if (r0 + rl < R) {
+                const int np = fuse.n_part_in;
+                const float* row = fuse.ssq_in + (size_t)(r0 + rl) * np;
+                const int per = (np + G - 1) / G;
+                const int p0 = grp * per, p1 = min(np, p0 + per);
+                if ((np & 3) == 0 && (per & 3) == 0) {
+                    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 8
+                    for (int p = p0; p < p1; p += 4) {
+                        const float4 v = *reinterpret_cast<const float4*>(row + p);
+                        acc.x += v.x;
+                        acc.y += v.y;
+                        acc.z += v.z;
+                        acc.w += v.w;
+                    }
+                    sum = (acc.x + acc.y) + (acc.z + acc.w);
+                } else {
+                    for (int p = p0; p < p1; ++p) sum += row[p];
+                }
+            }
             red_s[t] = sum;
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (t < BN) {
@@ -298,7 +334,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (m < BN && r0 + m < R) {
                     float tot = 0.0f;
                     for (int i = 0; i < bm; ++i) tot += sq[m * BM + i];
-                    fuse.ssq_out[(size_t)blockIdx.x * R + r0 + m] = tot;
+                    fuse.ssq_out[(size_t)(r0 + m) * gridDim.x + blockIdx.x] = tot;
                 }
             }
         }
@@ -317,7 +353,89 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (threadIdx.x == 64) trace_mark(trace_id, 5);
         const float* recv = reinterpret_cast<const float*>(tiles + (size_t)stages * S::STAGE_BYTES);
         float* sq = reinterpret_cast<float*>(tiles);  // [BN][mw]; this CTA's stages are drained
-        if (EPI == 0) {
+        // Four neighbouring rows of the tile at a time where the sizes allow it
+        // (the slices are whole multiples of four and so are the output's rows):
+        // one 16-byte access per rank's partial, per residual, per result.
+        const bool quads = (mw & 3) == 0 && (N & 3) == 0 && (bm & 3) == 0;
+        if (quads && EPI == 0) {
+            const int mq = mw >> 2;
+            for (int e = threadIdx.x; e < BN * mq; e += THREADS) {
+                const int rr = e / mq, ml = 4 * (e % mq), mm = z * mw + ml;
+                const int r = r0 + rr, n = n0 + mm;
+                if (mm >= bm || r >= R || n >= N) continue;
+                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int p = 0; p < ksplit; ++p) {
+                    const float4 v = *reinterpret_cast<const float4*>(recv + ((size_t)p * BN + rr) * mw + ml);
+                    acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+                }
+                if (PRO) {
+                    const float f = rstd_s[rr];
+                    acc.x *= f, acc.y *= f, acc.z *= f, acc.w *= f;
+                }
+                store4(y + (size_t)r * N + n, acc);
+            }
+        } else if (quads && EPI == 1) {
+            const int mq = mw >> 2;
+            for (int e = threadIdx.x; e < BN * mq; e += THREADS) {
+                const int rr = e / mq, ml = 4 * (e % mq), mm = z * mw + ml;
+                const int r = r0 + rr, n = n0 + mm;
+                if (mm >= bm || r >= R || n >= N) continue;
+                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);  // gate, up, gate, up
+                for (int p = 0; p < ksplit; ++p) {
+                    const float4 v = *reinterpret_cast<const float4*>(recv + ((size_t)p * BN + rr) * mw + ml);
+                    acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+                }
+                if (PRO) {
+                    const float f = rstd_s[rr];
+                    acc.x *= f, acc.y *= f, acc.z *= f, acc.w *= f;
+                }
+                store2(y + (size_t)r * (N / 2) + n / 2, silu_mul(acc.x, acc.y), silu_mul(acc.z, acc.w));
+            }
+        } else if (quads && EPI == 2) {
+            const int mq = mw >> 2;
+            constexpr int MAX_IT = (BN * (BM / 8) + THREADS - 1) / THREADS;  // at two ranks; fewer with more
+            // the residual rows first, all of them, so that their latencies overlap
+            float4 hv[MAX_IT];
+#pragma unroll
+            for (int it = 0; it < MAX_IT; ++it) {
+                const int e = threadIdx.x + it * THREADS;
+                const int rr = e / mq, ml = 4 * (e % mq), mm = z * mw + ml;
+                const int r = r0 + rr, n = n0 + mm;
+                hv[it] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (e < BN * mq && mm < bm && r < R && n < N)
+                    hv[it] = *reinterpret_cast<const float4*>(fuse.h + (size_t)r * N + n);
+            }
+#pragma unroll
+            for (int it = 0; it < MAX_IT; ++it) {
+                const int e = threadIdx.x + it * THREADS;
+                if (e >= BN * mq) break;
+                const int rr = e / mq, ml = 4 * (e % mq), mm = z * mw + ml;
+                const int r = r0 + rr, n = n0 + mm;
+                float4 t = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (mm < bm && r < R && n < N) {
+                    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    for (int p = 0; p < ksplit; ++p) {
+                        const float4 v =
+                            *reinterpret_cast<const float4*>(recv + ((size_t)p * BN + rr) * mw + ml);
+                        acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+                    }
+                    t = make_float4(hv[it].x + acc.x, hv[it].y + acc.y, hv[it].z + acc.z, hv[it].w + acc.w);
+                    const size_t idx = (size_t)r * N + n;
+                    *reinterpret_cast<float4*>(fuse.h + idx) = t;
+                    const float4 w4 = *reinterpret_cast<const float4*>(fuse.nw + n);
+                    store4(fuse.hb + idx, make_float4(t.x * (fuse.nw_offset + w4.x), t.y * (fuse.nw_offset + w4.y),
+                                                      t.z * (fuse.nw_offset + w4.z), t.w * (fuse.nw_offset + w4.w)));
+                }
+                *reinterpret_cast<float4*>(sq + rr * mw + ml) = make_float4(t.x * t.x, t.y * t.y, t.z * t.z, t.w * t.w);
+            }
+            __syncthreads();
+            // this CTA's partial of each row's sum of squares, added in index order
+            if ((int)threadIdx.x < BN && r0 + (int)threadIdx.x < R) {
+                float tot = 0.0f;
+                for (int i = 0; i < mw; ++i) tot += sq[threadIdx.x * mw + i];
+                fuse.ssq_out[(size_t)(r0 + threadIdx.x) * (gridDim.x * ksplit) + blockIdx.x * ksplit + z] = tot;
+            }
+        } else         if (EPI == 0) {
             for (int e = threadIdx.x; e < BN * mw; e += THREADS) {
                 const int rr = e / mw, ml = e % mw, mm = z * mw + ml;
                 if (mm >= bm) continue;
@@ -365,7 +483,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             if ((int)threadIdx.x < BN && r0 + (int)threadIdx.x < R) {
                 float tot = 0.0f;
                 for (int i = 0; i < mw; ++i) tot += sq[threadIdx.x * mw + i];
-                fuse.ssq_out[((size_t)blockIdx.x * ksplit + z) * R + r0 + threadIdx.x] = tot;
+                fuse.ssq_out[(size_t)(r0 + threadIdx.x) * (gridDim.x * ksplit) + blockIdx.x * ksplit + z] = tot;
             }
         }
         if (threadIdx.x == 64) trace_mark(trace_id, 6);
@@ -526,7 +644,8 @@ int launch(const void* x, const void* W, void* y, int R, int N, int K, int kspli
     if (stages < 2) stages = 2;
     // after the stages, the tile that receives the cluster's partial rows
     constexpr int RECV_BYTES = BN * BM * 4;
-    while (stages > 3 && stages * S::STAGE_BYTES + RECV_BYTES > 112 * 1024) --stages;
+    const int cap = env_int("REFLEX_B200_GEMM_SMEM_CAP_KB", 112) * 1024;  // tuning aid
+    while (stages > 3 && stages * S::STAGE_BYTES + RECV_BYTES > cap) --stages;
     if (stages * S::STAGE_BYTES < BN * BM * 4) return RFX_ERR_UNSUPPORTED;  // the squares of EPI 2
     if (n_part_out) *n_part_out = cut.tiles * ks;
     if (EPI == 2 && r_tiles != 1) return RFX_ERR_UNSUPPORTED;
@@ -571,7 +690,7 @@ int check_common(const void* x, const void* W, int R, int N, int K) {
 // epilogue 1: W's rows alternate gate/up, N is even, y is [R, N / 2] =
 // silu(gate) * up.
 // ssq_in (optional, R <= 64): x is unnormalised; row r of the result is scaled by
-// 1 / sqrt(sum_p ssq_in[p][r] / norm_h + eps), p < n_part_in.
+// 1 / sqrt(sum_p ssq_in[r][p] / norm_h + eps), p < n_part_in.
 extern "C" int rfx_gemm_bf16_tc(const void* x, const void* W, void* y, int y_dt, int R, int N,
                                 int K, int ksplit, int epilogue, const float* ssq_in, int n_part_in,
                                 int norm_h, float eps, int* err, void* stream) {
@@ -603,7 +722,7 @@ extern "C" int rfx_gemm_bf16_tc(const void* x, const void* W, void* y, int y_dt,
 
 // The product as a delta of the residual stream, for R <= 64:
 //   h [R, N] (float32) += x . W^T;   hb [R, N] = bfloat16(h * (nw_offset + nw[n]));
-//   ssq_out[p][r] = this CTA's share of sum_n h[r, n]^2, p < *n_part_out
+//   ssq_out[r][p] = this CTA's share of sum_n h[r, n]^2, p < *n_part_out
 // (ssq_out must hold at least rfx_gemm_bf16_tc_max_parts(N) * R floats).
 extern "C" int rfx_gemm_bf16_tc_residual(const void* x, const void* W, float* h, const float* nw,
                                          float nw_offset, void* hb, float* ssq_out, int* n_part_out,

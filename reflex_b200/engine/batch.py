@@ -32,8 +32,9 @@ class StepBatch:
     seq_new: torch.Tensor      # [S]
     seq_row0: torch.Tensor     # [S + 1]
     want_rows: torch.Tensor    # [n_want]
-    # set by a captured decode step: an upper bound of the longest context for
-    # every step that replays the capture (kernels size their launches by it)
+    # decode steps: the longest context rounded up to its bucket
+    # (`decode_context_bucket`), so that kernels which size their launches by it
+    # make the same choice in an eager step and in every replay of a captured one
     context_hint: Optional[int] = None
 
     @property
@@ -57,6 +58,14 @@ class StepBatch:
         if self.context_hint is not None:
             return self.context_hint
         return max(s + n for s, n in zip(self.starts, self.new_counts))
+
+
+def decode_context_bucket(max_context: int, page_tokens: int = 64) -> int:
+    """The longest context of a decode step, rounded up to where its launch set
+    may change: steps of 4 pages up to 32 pages, then powers of two."""
+    pages = -(-max_context // page_tokens)
+    bucket = -(-pages // 4) * 4 if pages <= 32 else 1 << (pages - 1).bit_length()
+    return bucket * page_tokens
 
 
 def layout(n_rows: int, n_seqs: int, n_want: int):
@@ -114,8 +123,11 @@ def make_batch(tokens, slots, starts, want, device, buffer: Optional[torch.Tenso
         p, n = offs[name]
         return dev[p:p + n]
 
+    hint = None
+    if all(n == 1 for n in new_counts):
+        hint = decode_context_bucket(max(starts) + 1)
     return StepBatch(
         slots=list(slots), starts=list(starts), new_counts=new_counts, row0=row0,
         want_rows_host=want_rows, tokens=f("tokens"), row_pos=f("row_pos"), row_slot=f("row_slot"),
         seq_slot=f("seq_slot"), seq_start=f("seq_start"), seq_new=f("seq_new"),
-        seq_row0=f("seq_row0"), want_rows=f("want_rows"))
+        seq_row0=f("seq_row0"), want_rows=f("want_rows"), context_hint=hint)

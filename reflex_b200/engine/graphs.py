@@ -41,7 +41,6 @@ class DecodeGraph:
             done = eng._eager_decodes.get(self.n, 0)
             if done < self.WARMUP:
                 eng._eager_decodes[self.n] = done + 1
-                batch.context_hint = None
                 return eng.model.forward(batch, eng.cache)
             # capture: the eager call above has already sized every lazy buffer
             torch.cuda.synchronize()

@@ -19,7 +19,7 @@ import torch
 
 from ..cache.store import PAGE_TOKENS, Cache
 from ..errors import CacheError, InvalidInput
-from .batch import StepBatch, make_batch
+from .batch import StepBatch, decode_context_bucket, make_batch
 from .model import CausalLM
 
 StepEntry = Tuple[int, Sequence[int], Sequence[int]]  # (sequence, tokens, wanted places)
@@ -115,13 +115,12 @@ class Engine:
         n = len(tokens)
         # the launch set depends on the batch size and, through the attention
         # kernel's key splits, on how long the longest context is: one graph per
-        # (batch size, bucket of its pages: steps of 4 pages up to 32, then powers of two)
-        pages = -(-(max(starts) + 1) // PAGE_TOKENS)
-        bucket = -(-pages // 4) * 4 if pages <= 32 else 1 << (pages - 1).bit_length()
+        # (batch size, context bucket)
+        bucket = decode_context_bucket(max(starts) + 1, PAGE_TOKENS)
         key = (n, bucket)
         g = self._graphs.get(key)
         if g is None:
-            g = DecodeGraph(self, n, bucket * PAGE_TOKENS)
+            g = DecodeGraph(self, n, bucket)
             self._graphs[key] = g
         return g.run(tokens, slots, starts, want)
 

@@ -141,8 +141,8 @@ def wait_probe(limit_ns: int, device="cuda:0") -> None:
 
 class NormedInput:
     """Rows that still await their RMSNorm factor: `hb` = bfloat16(h * norm
-    weight) and `ssq[p][r]`, partial sums of squares of h's row r.  The product
-    that consumes them multiplies its row r by 1 / sqrt(sum_p ssq[p][r] / size +
+    weight) and `ssq[r][p]`, `n_part` partial sums of squares of h's row r.  The product
+    that consumes them multiplies its row r by 1 / sqrt(sum_p ssq[r][p] / size +
     eps), which is the same as normalising first.  Made by `gemm_tc_residual`."""
 
     def __init__(self, hb: torch.Tensor, ssq: torch.Tensor, n_part: int, size: int, eps: float):
@@ -227,7 +227,7 @@ def gemm_tc_residual(x: torch.Tensor, weight: torch.Tensor, hidden: torch.Tensor
     if tuple(hidden.shape) != (R, N) or norm_weight.numel() != N:
         raise InvalidInput("gemm_tc_residual: hidden must be [rows, out] and the norm weight [out]")
     hb = torch.empty((R, N), dtype=torch.bfloat16, device=x.device)
-    ssq = torch.empty((native.lib().rfx_gemm_bf16_tc_max_parts(N), R), dtype=torch.float32, device=x.device)
+    ssq = torch.empty((R * native.lib().rfx_gemm_bf16_tc_max_parts(N),), dtype=torch.float32, device=x.device)
     n_part = ctypes.c_int(0)
     st = native.lib().rfx_gemm_bf16_tc_residual(
         x.data_ptr(), weight.data_ptr(), hidden.data_ptr(), norm_weight.data_ptr(), float(norm_offset),
@@ -374,6 +374,56 @@ def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_sl
         partial.data_ptr() if partial is not None else 0, R, nq, nkv, head_dim, n_splits,
         int(window or 0), float(scale), _stream())
     native.check(st, f"attention_decode (head_dim={head_dim}, splits={n_splits})")
+    return out
+
+
+def fused_decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int) -> int:
+    """Ranks of the fused decode kernel's cluster over the key range: the same
+    estimate as `decode_splits`, with a cluster barrier (about 1 us) in place of
+    the combine kernel, and at most 8 ranks."""
+    forced = int(_os.environ.get("REFLEX_B200_DECODE_SPLITS", "0"))  # tuning aid
+    if forced > 0:
+        return max(s for s in (1, 2, 4, 8) if s <= forced)
+    ctas = n_rows * nkv * ((nq // nkv + 15) // 16)
+    best, best_cost = 1, None
+    for s in (1, 2, 4, 8):
+        if s > max(1, max_pages):
+            break
+        waves = max(1.0, ctas * s / (2.0 * SM_COUNT))
+        cost = 4.0 + -(-max_pages // s) * 0.8 * waves + (1.0 if s > 1 else 0.0)
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
+
+
+FUSE_DECODE_ATTENTION = _os.environ.get("REFLEX_B200_FUSE_ATTENTION", "1") != "0"
+
+
+def attention_decode_fused(qkv: torch.Tensor, q_weight, k_weight, eps: float, weight_offset: float,
+                           rope_denom, rotary_dim: int, k_pages, v_pages, page_table, page_size: int,
+                           row_pos, row_slot, nq: int, nkv: int, head_dim: int, writes_cache: bool,
+                           window, scale: float, n_splits: int = 1) -> torch.Tensor:
+    """Decode rows (one query position each) from the float32 q/k/v product to
+    the attention output in one launch: per-head norms, rotation, the new key
+    and value into the bfloat16 cache, attention, the splits merged inside a
+    thread-block cluster.  Returns bfloat16 [R, nq * head_dim]."""
+    R = qkv.shape[0]
+    _chk(qkv, "qkv", torch.float32)
+    nkv_in = nkv if writes_cache else 0
+    if qkv.shape[1] != (nq + 2 * nkv_in) * head_dim:
+        raise InvalidInput("attention_decode_fused: qkv width does not match the head counts")
+    if head_dim % 16 or not (16 <= head_dim <= 256):
+        raise InvalidInput(f"attention_decode_fused takes head_dim in steps of 16 up to 256, got {head_dim}")
+    out = torch.empty((R, nq * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    st = native.lib().rfx_attention_decode_fused(
+        qkv.data_ptr(), qkv.shape[1], nkv_in, _chk(q_weight, "q_norm", torch.float32),
+        _chk(k_weight, "k_norm", torch.float32), float(eps), float(weight_offset),
+        _chk(rope_denom, "rope_denom", torch.float32), int(rotary_dim),
+        _chk(k_pages, "k_pages", torch.bfloat16), _chk(v_pages, "v_pages", torch.bfloat16),
+        _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
+        _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32), out.data_ptr(),
+        R, nq, nkv, head_dim, int(n_splits), int(window or 0), float(scale), _stream())
+    native.check(st, f"attention_decode_fused (head_dim={head_dim}, splits={n_splits})")
     return out
 
 

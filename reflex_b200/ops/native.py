@@ -39,6 +39,9 @@ _SIGNATURES = {
                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "rfx_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "rfx_attention_decode_fused": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p,
+                                   c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "rfx_attention_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_float, c_void_p],

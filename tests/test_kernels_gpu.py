@@ -153,7 +153,7 @@ def test_gemm_tc_residual_add_with_the_norm_folded_into_the_next_product(R, N, K
         h_ref = h.double().numpy() + x.double().numpy() @ w.double().numpy().T
         assert relerr(hd, h_ref) < 3e-6 * math.sqrt(K)
         assert relerr(ni.hb, h_ref * nw.double().numpy()) < 5e-3
-        ssq = ni.ssq[: ni.n_part].sum(dim=0)
+        ssq = ni.ssq[: R * ni.n_part].view(R, ni.n_part).sum(dim=1)
         assert relerr(ssq, (h_ref * h_ref).sum(axis=1)) < 1e-4  # 32-bit h, K products each
         normed = pm.rms_norm(h_ref, nw.double().numpy(), eps)
         y = ops().linear(ni, w2.to(DEV), out_dtype=torch.float32)
@@ -328,6 +328,75 @@ def test_attention_decode_splits(nq, nkv, d, ctxs, window, splits):
                                  n_splits=splits)
     assert not bool(torch.isnan(out.float()).any())
     assert relerr(out.reshape(R, nq, d), ref) < 8e-3
+
+
+FUSED_CASES = [
+    # nq, nkv, d, rotary, contexts, window, splits, this run writes the cache
+    (4, 2, 16, 16, [1, 17, 64, 65], None, 1, True),
+    (6, 1, 32, 32, [100, 129], None, 2, True),
+    (3, 1, 48, 32, [300, 38, 37], 37, 4, True),
+    (32, 8, 128, 128, [640] * 4, None, 4, True),
+    (32, 8, 128, 128, [1, 63, 64, 4000], None, 8, True),
+    (32, 8, 128, 128, [520] * 8, None, 1, True),
+    (40, 2, 256, 64, [999], None, 4, True),
+    (7, 7, 80, 80, [255, 256], 100, 2, True),
+    (20, 1, 64, 64, [130, 64], None, 2, True),
+    (6, 2, 64, 64, [129, 5], None, 2, False),
+]
+
+
+@pytest.mark.parametrize("nq,nkv,d,rd,ctxs,window,splits,writes", FUSED_CASES)
+def test_fused_decode_attention_equals_the_separate_kernels(nq, nkv, d, rd, ctxs, window, splits, writes):
+    """From the q/k/v product's rows to the attention output in one launch:
+    the same bits as qkv_post followed by attention_decode with as many
+    splits, the same cache afterwards, and both right against the plain
+    formulas.  The row's own key and value are NaN in the cache beforehand
+    when the run writes them: the kernel must not read them from there."""
+    g = torch.Generator().manual_seed(nq * 7 + d)
+    slots, table, kp, vp, ks, vs = _paged(ctxs, nkv, d, torch.bfloat16, g)
+    R = len(ctxs)
+    theta, eps = 1e4, 1e-6
+    nkv_in = nkv if writes else 0
+    qkv = torch.randn(R, (nq + 2 * nkv_in) * d, generator=g) * 1.5
+    qw = 1 + 0.1 * torch.randn(d, generator=g)
+    kw = 1 + 0.1 * torch.randn(d, generator=g)
+    denom = torch.pow(torch.tensor(theta, dtype=torch.float64), torch.arange(rd // 2, dtype=torch.float64) * 2 / rd)
+    pos = [c - 1 for c in ctxs]
+    if writes:
+        for i, p in enumerate(pos):
+            page = int(table[slots[i], p // 64])
+            kp[page, :, p % 64] = float("nan")
+            vp[page, :, p % 64] = float("nan")
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    row_pos, row_slot = i32(pos), i32(slots)
+    common = (qw.to(DEV), kw.to(DEV), eps, 0.0, denom.float().to(DEV), rd)
+    # the separate kernels
+    kp1, vp1 = kp.to(DEV), vp.to(DEV)
+    q1 = ops().qkv_post(qkv.to(DEV), *common, row_pos, row_slot, kp1, vp1, table.to(DEV), 64, nq, nkv, d,
+                        writes, torch.bfloat16)
+    out1 = ops().attention_decode(q1, kp1, vp1, table.to(DEV), 64, row_pos, row_slot, nq, nkv, d, window,
+                                  d ** -0.5, n_splits=splits)
+    # the one kernel
+    kp2, vp2 = kp.to(DEV), vp.to(DEV)
+    out2 = ops().attention_decode_fused(qkv.to(DEV), *common, kp2, vp2, table.to(DEV), 64, row_pos, row_slot,
+                                        nq, nkv, d, writes, window, d ** -0.5, n_splits=splits)
+    assert not bool(torch.isnan(out2.float()).any())
+    assert torch.equal(out1.view(torch.int16), out2.view(torch.int16))
+    assert torch.equal(kp1.view(torch.int16), kp2.view(torch.int16))
+    assert torch.equal(vp1.view(torch.int16), vp2.view(torch.int16))
+    # against the plain formulas
+    x = qkv.double().numpy()
+    parr = np.array(pos)
+    qr = pm.rope_neox(pm.rms_norm(x[:, : nq * d].reshape(R, nq, d), qw.double().numpy(), eps), parr, theta, rd)
+    if writes:
+        kr = pm.rope_neox(pm.rms_norm(x[:, nq * d:(nq + nkv) * d].reshape(R, nkv, d), kw.double().numpy(), eps),
+                          parr, theta, rd)
+        vr = x[:, (nq + nkv) * d:].reshape(R, nkv, d)
+        for i, p in enumerate(pos):
+            ks[i][p] = torch.from_numpy(kr[i]).float()
+            vs[i][p] = torch.from_numpy(vr[i]).float()
+    ref = _ref_rows(torch.from_numpy(qr).float(), ks, vs, [(p, 1) for p in pos], d ** -0.5, window, torch.bfloat16)
+    assert relerr(out2.reshape(R, nq, d), ref) < 1e-2
 
 
 @pytest.mark.parametrize("kernel", ["plain_f32", "plain_bf16", "prefill_bf16", "prefill_tc_bf16", "decode_bf16"])

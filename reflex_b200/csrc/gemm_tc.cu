@@ -88,6 +88,14 @@ struct Fuse {
 // launch and no round trip of the [R, 2I] intermediate
 // (src/kernels_cuda/silu_and_mul.cu:7-23 is the reference's separate kernel).
 __device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+// The same for a result that is rounded to bfloat16 anyway: the fast exponential
+// and division are a few units in the last place of 32 bits off, far below that
+// rounding; their limits at large |g| are the function's own (0 and g).
+template <typename TO>
+__device__ __forceinline__ float silu_mul_for(float g, float u) {
+    if constexpr (sizeof(TO) == 2) return __fdividef(g, 1.0f + __expf(-g)) * u;
+    else return silu_mul(g, u);
+}
 
 // four (two) neighbouring results in one access; the address is a multiple of
 // their size by the callers' conditions
@@ -294,40 +302,67 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
             }
         } else {
-            // One CTA has the whole sum: finish straight from the registers.
+            // One CTA has the whole sum: finish straight from the registers.  The
+            // next 16 columns are on their way from tensor memory while these are
+            // worked on.
             float* sq = stage0;  // [BN][BM] squares of the new residual (EPI 2)
+            const uint32_t lane_base = tmem_d + ((uint32_t)(q * 32) << 16);
+            uint32_t ahead[16];
+            if (have) tmem_ld_16_nowait(lane_base, ahead);
 #pragma unroll 1
             for (int c = 0; c < BN / 16; ++c) {
                 float v[16];
                 if (have) {
-                    tmem_ld_16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 16), v);
+                    tmem_ld_wait_16(ahead);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(ahead[j]);
+                    if (c + 1 < BN / 16) tmem_ld_16_nowait(lane_base + (uint32_t)((c + 1) * 16), ahead);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] = 0.0f;
                 }
+                if (EPI == 1) {
+                    // Rows alternate gate, up: lanes 2i and 2i + 1 hold one feature's
+                    // pair.  Of every two columns the even lane finishes the first and
+                    // the odd lane the second, after one exchange.
+                    const bool even = (m & 1) == 0;
+                    const int n = n0 + m;
+                    const bool pair_ok = (m | 1) < bm && (n | 1) < N;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int rr = c * 16 + j, r = r0 + rr, n = n0 + m;
-                    float a = v[j];
-                    if (PRO) a *= rstd_s[rr];
-                    if (EPI == 0) {
-                        if (r < R && m < bm && n < N) rfx::st<TO>(y, (size_t)r * N + n, a);
-                    } else if (EPI == 1) {
-                        const float up = __shfl_down_sync(0xffffffffu, a, 1);  // the odd row above
-                        if ((m & 1) == 0 && r < R && m + 1 < bm && n + 1 < N)
-                            rfx::st<TO>(y, (size_t)r * (N / 2) + n / 2, silu_mul(a, up));
-                    } else {
-                        float hv = 0.0f;
-                        if (r < R && m < bm && n < N) {
-                            const size_t idx = (size_t)r * N + n;
-                            hv = fuse.h[idx] + a;
-                            fuse.h[idx] = hv;
-                            fuse.hb[idx] = __float2bfloat16_rn(hv * (fuse.nw_offset + fuse.nw[n]));
+                    for (int j = 0; j < 16; j += 2) {
+                        float a0 = v[j], a1 = v[j + 1];
+                        if (PRO) {
+                            a0 *= rstd_s[c * 16 + j];
+                            a1 *= rstd_s[c * 16 + j + 1];
                         }
-                        sq[rr * BM + m] = hv * hv;
+                        const float got = __shfl_xor_sync(0xffffffffu, even ? a1 : a0, 1);
+                        const float gate = even ? a0 : got, up = even ? got : a1;
+                        const int r = r0 + c * 16 + j + (even ? 0 : 1);
+                        if (pair_ok && r < R) rfx::st<TO>(y, (size_t)r * (N / 2) + n / 2, silu_mul_for<TO>(gate, up));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int rr = c * 16 + j, r = r0 + rr, n = n0 + m;
+                        float a = v[j];
+                        if (PRO) a *= rstd_s[rr];
+                        if (EPI == 0) {
+                            if (r < R && m < bm && n < N) rfx::st<TO>(y, (size_t)r * N + n, a);
+                        } else {
+                            float hv = 0.0f;
+                            if (r < R && m < bm && n < N) {
+                                const size_t idx = (size_t)r * N + n;
+                                hv = fuse.h[idx] + a;
+                                fuse.h[idx] = hv;
+                                fuse.hb[idx] = __float2bfloat16_rn(hv * (fuse.nw_offset + fuse.nw[n]));
+                            }
+                            sq[rr * BM + m] = hv * hv;
+                        }
                     }
                 }
+                if (c == 0 && threadIdx.x == 64) trace_mark(trace_id, 4);
             }
+            if (threadIdx.x == 64) trace_mark(trace_id, 5);
             if (EPI == 2) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 // this CTA's partial of each row's sum of squares, added in index order
@@ -389,7 +424,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     const float f = rstd_s[rr];
                     acc.x *= f, acc.y *= f, acc.z *= f, acc.w *= f;
                 }
-                store2(y + (size_t)r * (N / 2) + n / 2, silu_mul(acc.x, acc.y), silu_mul(acc.z, acc.w));
+                store2(y + (size_t)r * (N / 2) + n / 2, silu_mul_for<TO>(acc.x, acc.y), silu_mul_for<TO>(acc.z, acc.w));
             }
         } else if (quads && EPI == 2) {
             const int mq = mw >> 2;
@@ -405,14 +440,17 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (e < BN * mq && mm < bm && r < R && n < N)
                     hv[it] = *reinterpret_cast<const float4*>(fuse.h + (size_t)r * N + n);
             }
+            // A row's slice lies in mq neighbouring lanes; where mq is a power of
+            // two its squares are summed by shuffles, else through shared memory.
+            const bool seg = (mq & (mq - 1)) == 0 && mq <= 32;
 #pragma unroll
             for (int it = 0; it < MAX_IT; ++it) {
                 const int e = threadIdx.x + it * THREADS;
-                if (e >= BN * mq) break;
+                const bool in = e < BN * mq;
                 const int rr = e / mq, ml = 4 * (e % mq), mm = z * mw + ml;
                 const int r = r0 + rr, n = n0 + mm;
                 float4 t = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                if (mm < bm && r < R && n < N) {
+                if (in && mm < bm && r < R && n < N) {
                     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                     for (int p = 0; p < ksplit; ++p) {
                         const float4 v =
@@ -426,14 +464,25 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     store4(fuse.hb + idx, make_float4(t.x * (fuse.nw_offset + w4.x), t.y * (fuse.nw_offset + w4.y),
                                                       t.z * (fuse.nw_offset + w4.z), t.w * (fuse.nw_offset + w4.w)));
                 }
-                *reinterpret_cast<float4*>(sq + rr * mw + ml) = make_float4(t.x * t.x, t.y * t.y, t.z * t.z, t.w * t.w);
+                if (seg) {
+                    // the same order every time: pairs inside the quad, then lanes 1, 2, 4, .. apart
+                    float ss = (t.x * t.x + t.y * t.y) + (t.z * t.z + t.w * t.w);
+                    for (int d = 1; d < mq; d <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+                    if (in && (e % mq) == 0 && r < R)
+                        fuse.ssq_out[(size_t)r * (gridDim.x * ksplit) + blockIdx.x * ksplit + z] = ss;
+                } else if (in) {
+                    *reinterpret_cast<float4*>(sq + rr * mw + ml) =
+                        make_float4(t.x * t.x, t.y * t.y, t.z * t.z, t.w * t.w);
+                }
             }
-            __syncthreads();
-            // this CTA's partial of each row's sum of squares, added in index order
-            if ((int)threadIdx.x < BN && r0 + (int)threadIdx.x < R) {
-                float tot = 0.0f;
-                for (int i = 0; i < mw; ++i) tot += sq[threadIdx.x * mw + i];
-                fuse.ssq_out[(size_t)(r0 + threadIdx.x) * (gridDim.x * ksplit) + blockIdx.x * ksplit + z] = tot;
+            if (!seg) {
+                __syncthreads();
+                // this CTA's partial of each row's sum of squares, added in index order
+                if ((int)threadIdx.x < BN && r0 + (int)threadIdx.x < R) {
+                    float tot = 0.0f;
+                    for (int i = 0; i < mw; ++i) tot += sq[threadIdx.x * mw + i];
+                    fuse.ssq_out[(size_t)(r0 + threadIdx.x) * (gridDim.x * ksplit) + blockIdx.x * ksplit + z] = tot;
+                }
             }
         } else         if (EPI == 0) {
             for (int e = threadIdx.x; e < BN * mw; e += THREADS) {
@@ -461,7 +510,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 const int r = r0 + rr;
                 if (r < R && n0 + mm + 1 < N)
-                    rfx::st<TO>(y, (size_t)r * (N / 2) + (n0 + mm) / 2, silu_mul(g, u));
+                    rfx::st<TO>(y, (size_t)r * (N / 2) + (n0 + mm) / 2, silu_mul_for<TO>(g, u));
             }
         } else {
             for (int e = threadIdx.x; e < BN * mw; e += THREADS) {

@@ -195,6 +195,16 @@ __device__ __forceinline__ void tmem_ld_16_nowait(uint32_t taddr, uint32_t* r) {
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// The wait, tied to the registers of one such load: what reads them afterwards
+// cannot be scheduled above the wait.
+__device__ __forceinline__ void tmem_ld_wait_16(uint32_t* r) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
+                   "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]),
+                   "+r"(r[14]), "+r"(r[15])
+                 :
+                 : "memory");
+}
 // 32 lanes x 16 columns back into tensor memory
 __device__ __forceinline__ void tmem_st_16(uint32_t taddr, const uint32_t* r) {
     asm volatile(

@@ -92,36 +92,54 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             ++issued;
         }
     }
-    rfx::pdl_wait();
-    // the query heads of this tile; rows beyond the group are zero
-    for (int i = tid; i < 16 * (D / 8); i += DEC_THREADS) {
-        const int row = i / (D / 8), c = i % (D / 8);
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (row < nh) v = *reinterpret_cast<const uint4*>(q + ((size_t)r * nq + h0 + row) * D + c * 8);
-        *reinterpret_cast<uint4*>(qs + row * LD + c * 8) = v;
-    }
-
-#pragma unroll
-    for (int i = 0; i < DEC_STAGES - 1; ++i) {
-        if (i >= issued) {
-            if (pg0 + i < pg1) issue(pg0 + i, pages_first[i], i);
+    // The loop's first pass is a dry one, still before the wait: it runs the tile
+    // code on whatever the last ring buffer holds with every key masked, so that
+    // the instructions are in the cache when the real pages come; its results
+    // are thrown away.  Then the wait, the query rows, and the real passes.
+    int page_ahead = pages_first[DEC_STAGES - 1];
+#pragma unroll 1
+    for (int pg = pg0 - 1;;) {
+        const bool dry = pg < pg0;
+        const int buf = dry ? DEC_STAGES - 1 : (pg - pg0) % DEC_STAGES;
+        if (!dry) {
+            cp_async_wait<DEC_STAGES - 2>();  // page pg has landed (this thread's part)
+            __syncthreads();                  // everyone's part; and buffer (pg - 1) is free
+            const int nxt = pg + DEC_STAGES - 1;
+            const int page_now = page_ahead;
+            if (nxt + 1 < pg1) page_ahead = table[nxt + 1];
+            if (nxt < pg1) issue(nxt, page_now, (nxt - pg0) % DEC_STAGES);
             else cp_async_commit();
         }
-    }
-    int page_ahead = pages_first[DEC_STAGES - 1];
-    for (int pg = pg0; pg < pg1; ++pg) {
-        const int buf = (pg - pg0) % DEC_STAGES;
-        cp_async_wait<DEC_STAGES - 2>();  // page pg has landed (this thread's part)
-        __syncthreads();                  // everyone's part; and buffer (pg - 1) is free
-        const int nxt = pg + DEC_STAGES - 1;
-        const int page_now = page_ahead;
-        if (nxt + 1 < pg1) page_ahead = table[nxt + 1];
-        if (nxt < pg1) issue(nxt, page_now, (nxt - pg0) % DEC_STAGES);
-        else cp_async_commit();
         const int base = pg * PAGE;
-        auto visible = [&](int key, int) { return base + key >= lo && base + key <= pos; };
+        const int lo_eff = dry ? 0x7fffffff : lo;
+        auto visible = [&](int key, int) { return base + key >= lo_eff && base + key <= pos; };
         attend_tile<D, 2>(qs, kbuf + buf * PAGE * LD, vbuf + buf * PAGE * LD, warp * 16, scale_log2,
                           visible, m, l, acc);
+        if (dry) {
+            m[0] = m[1] = -INFINITY;
+            l[0] = l[1] = 0.0f;
+#pragma unroll
+            for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
+            rfx::pdl_wait();
+            // the query heads of this tile; rows beyond the group are zero
+            for (int i = tid; i < 16 * (D / 8); i += DEC_THREADS) {
+                const int row = i / (D / 8), c = i % (D / 8);
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (row < nh) v = *reinterpret_cast<const uint4*>(q + ((size_t)r * nq + h0 + row) * D + c * 8);
+                *reinterpret_cast<uint4*>(qs + row * LD + c * 8) = v;
+            }
+#pragma unroll
+            for (int i = 0; i < DEC_STAGES - 1; ++i) {
+                if (i >= issued) {
+                    if (pg0 + i < pg1) issue(pg0 + i, pages_first[i], i);
+                    else cp_async_commit();
+                }
+            }
+        }
+        ++pg;
+        if (pg >= pg1) break;
     }
     cp_async_wait<0>();
     __syncthreads();  // all warps are done with the tiles before they are reused below
@@ -136,10 +154,14 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         for (int n = 0; n < D / 8; ++n) {
             float* a0 = red + ((size_t)(warp * 16 + g0) * D) + n * 8 + 2 * c;
             float* a1 = red + ((size_t)(warp * 16 + g0 + 8) * D) + n * 8 + 2 * c;
-            a0[0] = acc[n][0];
-            a0[1] = acc[n][1];
-            a1[0] = acc[n][2];
-            a1[1] = acc[n][3];
+            if (g0 < nh) {  // rows beyond the group's heads hold nothing
+                a0[0] = acc[n][0];
+                a0[1] = acc[n][1];
+            }
+            if (g0 + 8 < nh) {
+                a1[0] = acc[n][2];
+                a1[1] = acc[n][3];
+            }
         }
         if (c == 0) {
             red_m[warp * 16 + g0] = m[0];

@@ -357,10 +357,14 @@ __global__ void __launch_bounds__(THREADS) attention_decode_fused_kernel(const F
         for (int n = 0; n < D / 8; ++n) {
             float* a0 = red + ((size_t)(warp * 16 + g0) * D) + n * 8 + 2 * c;
             float* a1 = red + ((size_t)(warp * 16 + g0 + 8) * D) + n * 8 + 2 * c;
-            a0[0] = acc[n][0];
-            a0[1] = acc[n][1];
-            a1[0] = acc[n][2];
-            a1[1] = acc[n][3];
+            if (g0 < nh) {  // rows beyond the group's heads hold nothing
+                a0[0] = acc[n][0];
+                a0[1] = acc[n][1];
+            }
+            if (g0 + 8 < nh) {
+                a1[0] = acc[n][2];
+                a1[1] = acc[n][3];
+            }
         }
         if (c == 0) {
             red_m[warp * 16 + g0] = m[0];

@@ -396,7 +396,12 @@ def fused_decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int) -> int:
     return best
 
 
-FUSE_DECODE_ATTENTION = _os.environ.get("REFLEX_B200_FUSE_ATTENTION", "1") != "0"
+# The one-launch form of a decode step's attention (`attention_decode_fused`) is
+# opt-in: measured on a B200 at Qwen3-8B sizes it is level with the separate
+# kernels at batch 8 (3.42 against 3.40 ms a step) and behind them at batch 32
+# and 64, because its larger CTAs become resident later behind the product
+# kernel before them, which costs more than the launches it saves.
+FUSE_DECODE_ATTENTION = _os.environ.get("REFLEX_B200_FUSE_ATTENTION", "0") == "1"
 
 
 def attention_decode_fused(qkv: torch.Tensor, q_weight, k_weight, eps: float, weight_offset: float,

@@ -207,40 +207,50 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial,
     __shared__ float wgt[MAX_SPLITS];
     __shared__ float lw[MAX_SPLITS];
     __shared__ float inv_l;
-    rfx::pdl_prologue();
+    rfx::pdl_launch_dependents();
     const size_t head = blockIdx.x;
     const float* p = partial + head * n_splits * (D + 2);
-    if (threadIdx.x < 32) {
-        float ms[MAX_SPLITS / 32], ls[MAX_SPLITS / 32];
-        float M = -INFINITY;
+    // Two passes over the same code: a dry one before the wait on the attention
+    // kernel (it reads zeros in place of the partials and stores nothing; it
+    // brings the instructions into the cache), then the work.
+#pragma unroll 1
+    for (int pass = 0; pass < 2; ++pass) {
+        const bool dry = pass == 0;
+        if (!dry) rfx::pdl_wait();
+        if (threadIdx.x < 32) {
+            float ms[MAX_SPLITS / 32], ls[MAX_SPLITS / 32];
+            float M = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < MAX_SPLITS / 32; ++i) {
-            const int sidx = threadIdx.x + 32 * i;
-            ms[i] = sidx < n_splits ? p[sidx * (D + 2) + D] : -INFINITY;
-            ls[i] = sidx < n_splits ? p[sidx * (D + 2) + D + 1] : 0.0f;
-            M = fmaxf(M, ms[i]);
-        }
-        M = rfx::warp_max(M);
+            for (int i = 0; i < MAX_SPLITS / 32; ++i) {
+                const int sidx = threadIdx.x + 32 * i;
+                const bool in = sidx < n_splits && !dry;
+                ms[i] = in ? p[sidx * (D + 2) + D] : -INFINITY;
+                ls[i] = in ? p[sidx * (D + 2) + D + 1] : 0.0f;
+                M = fmaxf(M, ms[i]);
+            }
+            M = rfx::warp_max(M);
 #pragma unroll
-        for (int i = 0; i < MAX_SPLITS / 32; ++i) {
-            const float e = ms[i] == -INFINITY ? 0.0f : exp2f(ms[i] - M);
-            wgt[threadIdx.x + 32 * i] = e;
-            lw[threadIdx.x + 32 * i] = ls[i] * e;
+            for (int i = 0; i < MAX_SPLITS / 32; ++i) {
+                const float e = ms[i] == -INFINITY ? 0.0f : exp2f(ms[i] - M);
+                wgt[threadIdx.x + 32 * i] = e;
+                lw[threadIdx.x + 32 * i] = ls[i] * e;
+            }
+            __syncwarp();
+            if (threadIdx.x == 0) {  // in split order, by one lane: the same bits every time
+                float L = 0.0f;
+                for (int sidx = 0; sidx < n_splits; ++sidx) L += lw[sidx];
+                inv_l = 1.0f / L;
+            }
         }
-        __syncwarp();
-        if (threadIdx.x == 0) {  // in split order, by one lane: the same bits every time
-            float L = 0.0f;
-            for (int sidx = 0; sidx < n_splits; ++sidx) L += lw[sidx];
-            inv_l = 1.0f / L;
-        }
-    }
-    __syncthreads();
-    const float inv = inv_l;
-    for (int e = threadIdx.x; e < D; e += blockDim.x) {
-        float A = 0.0f;
+        __syncthreads();
+        const float inv = inv_l;
+        for (int e = threadIdx.x; e < D; e += blockDim.x) {
+            float A = 0.0f;
 #pragma unroll 4
-        for (int sidx = 0; sidx < n_splits; ++sidx) A += p[sidx * (D + 2) + e] * wgt[sidx];
-        out[head * D + e] = __float2bfloat16_rn(A * inv);
+            for (int sidx = 0; sidx < n_splits; ++sidx) A += (dry ? 0.0f : p[sidx * (D + 2) + e]) * wgt[sidx];
+            if (!dry) out[head * D + e] = __float2bfloat16_rn(A * inv);
+        }
+        __syncthreads();  // wgt, lw and inv_l are written again by the next pass
     }
 }
 

@@ -383,15 +383,33 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // barrier, so CTAs may leave as they finish.
         cg::cluster_group cluster = cg::this_cluster();
         rfx::pdl_wait();
+        // Four neighbouring rows of the tile at a time where the sizes allow it
+        // (the slices are whole multiples of four and so are the output's rows):
+        // one 16-byte access per rank's partial, per residual, per result.
+        const bool quads = (mw & 3) == 0 && (N & 3) == 0 && (bm & 3) == 0;
+        // The residual rows this rank will add to (EPI 2) and their norm weights
+        // are on their way while the cluster's barrier is waited for.
+        constexpr int MAX_IT = (BN * (BM / 8) + THREADS - 1) / THREADS;  // at two ranks; fewer with more
+        float4 hv[EPI == 2 ? MAX_IT : 1], nwv[EPI == 2 ? MAX_IT : 1];
+        if (EPI == 2 && quads) {
+            const int mq = mw >> 2;
+#pragma unroll
+            for (int it = 0; it < MAX_IT; ++it) {
+                const int e = threadIdx.x + it * THREADS;
+                const int rr = e / mq, ml = 4 * (e % mq), mm = z * mw + ml;
+                const int r = r0 + rr, n = n0 + mm;
+                hv[it] = nwv[it] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (e < BN * mq && mm < bm && r < R && n < N) {
+                    hv[it] = *reinterpret_cast<const float4*>(fuse.h + (size_t)r * N + n);
+                    nwv[it] = *reinterpret_cast<const float4*>(fuse.nw + n);
+                }
+            }
+        }
         if (threadIdx.x == 64) trace_mark(trace_id, 4);
         cluster.sync();
         if (threadIdx.x == 64) trace_mark(trace_id, 5);
         const float* recv = reinterpret_cast<const float*>(tiles + (size_t)stages * S::STAGE_BYTES);
         float* sq = reinterpret_cast<float*>(tiles);  // [BN][mw]; this CTA's stages are drained
-        // Four neighbouring rows of the tile at a time where the sizes allow it
-        // (the slices are whole multiples of four and so are the output's rows):
-        // one 16-byte access per rank's partial, per residual, per result.
-        const bool quads = (mw & 3) == 0 && (N & 3) == 0 && (bm & 3) == 0;
         if (quads && EPI == 0) {
             const int mq = mw >> 2;
             for (int e = threadIdx.x; e < BN * mq; e += THREADS) {
@@ -428,18 +446,6 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
         } else if (quads && EPI == 2) {
             const int mq = mw >> 2;
-            constexpr int MAX_IT = (BN * (BM / 8) + THREADS - 1) / THREADS;  // at two ranks; fewer with more
-            // the residual rows first, all of them, so that their latencies overlap
-            float4 hv[MAX_IT];
-#pragma unroll
-            for (int it = 0; it < MAX_IT; ++it) {
-                const int e = threadIdx.x + it * THREADS;
-                const int rr = e / mq, ml = 4 * (e % mq), mm = z * mw + ml;
-                const int r = r0 + rr, n = n0 + mm;
-                hv[it] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                if (e < BN * mq && mm < bm && r < R && n < N)
-                    hv[it] = *reinterpret_cast<const float4*>(fuse.h + (size_t)r * N + n);
-            }
             // A row's slice lies in mq neighbouring lanes; where mq is a power of
             // two its squares are summed by shuffles, else through shared memory.
             const bool seg = (mq & (mq - 1)) == 0 && mq <= 32;
@@ -460,7 +466,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     t = make_float4(hv[it].x + acc.x, hv[it].y + acc.y, hv[it].z + acc.z, hv[it].w + acc.w);
                     const size_t idx = (size_t)r * N + n;
                     *reinterpret_cast<float4*>(fuse.h + idx) = t;
-                    const float4 w4 = *reinterpret_cast<const float4*>(fuse.nw + n);
+                    const float4 w4 = nwv[it];
                     store4(fuse.hb + idx, make_float4(t.x * (fuse.nw_offset + w4.x), t.y * (fuse.nw_offset + w4.y),
                                                       t.z * (fuse.nw_offset + w4.z), t.w * (fuse.nw_offset + w4.w)));
                 }

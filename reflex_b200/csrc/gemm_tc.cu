@@ -230,9 +230,12 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         __syncwarp();
     } else {
+        // ---- the four epilogue warps (threads 64 .. 191) -------------------------
         rfx::pdl_wait();         // y may still be read by an earlier kernel
         const int q = warp & 3;  // this warp may read TMEM lanes [32 q, 32 q + 32)
         const int m = q * 32 + lane;
+        const int et = threadIdx.x - 64;  // 0 .. 127 among the epilogue threads
+        constexpr int ET = 128;
         if (PRO) {
             // the rows' norm factors, while the main loop runs: 128 / BN threads
             // share a row's partials (a contiguous run each, read four at a
@@ -269,279 +272,316 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 rstd_s[t] = 1.0f / sqrtf(total * fuse.inv_h + fuse.eps);
             }
         }
-        bool have = nkb > 0;
-        if (have && !mbar_wait(&tmem_full_bar, 0)) {
-            if (lane == 0) atomicExch(err, 3);
-            have = false;
-        }
-        tc_fence_after_sync();
-        if (warp == 2 && lane == 0) trace_mark(trace_id, 2);
         // after the stages: a tile of [BN][BM] floats that receives partial rows from
         // the cluster's ranks (it must not alias the stages: a rank that is done
         // early sends while this CTA may still be streaming)
         float* stage0 = reinterpret_cast<float*>(tiles + (size_t)stages * S::STAGE_BYTES);
-        if (ksplit > 1) {
-            // Split K: this CTA's tile is a partial sum.  Row m of the tile belongs to
-            // rank m / mw of the cluster; send it there (remote shared-memory stores,
-            // nothing waits on them) into slot [this rank][column][m % mw].
-            cg::cluster_group cluster = cg::this_cluster();
-            const int owner = m / mw, ml = m % mw;
-            float* dst = cluster.map_shared_rank(stage0, owner < ksplit ? owner : 0) + (size_t)z * BN * mw + ml;
-#pragma unroll 1
-            for (int c = 0; c < BN / 16; ++c) {
-                float v[16];
-                if (have) {
-                    tmem_ld_16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 16), v);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = 0.0f;
-                }
-                if (m < bm) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) dst[(c * 16 + j) * mw] = v[j];
-                }
-            }
-        } else {
-            // One CTA has the whole sum: finish straight from the registers.  The
-            // next 16 columns are on their way from tensor memory while these are
-            // worked on.
-            float* sq = stage0;  // [BN][BM] squares of the new residual (EPI 2)
-            const uint32_t lane_base = tmem_d + ((uint32_t)(q * 32) << 16);
-            uint32_t ahead[16];
-            if (have) tmem_ld_16_nowait(lane_base, ahead);
-#pragma unroll 1
-            for (int c = 0; c < BN / 16; ++c) {
-                float v[16];
-                if (have) {
-                    tmem_ld_wait_16(ahead);
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(ahead[j]);
-                    if (c + 1 < BN / 16) tmem_ld_16_nowait(lane_base + (uint32_t)((c + 1) * 16), ahead);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = 0.0f;
-                }
-                if (EPI == 1) {
-                    // Rows alternate gate, up: lanes 2i and 2i + 1 hold one feature's
-                    // pair.  Of every two columns the even lane finishes the first and
-                    // the odd lane the second, after one exchange.
-                    const bool even = (m & 1) == 0;
-                    const int n = n0 + m;
-                    const bool pair_ok = (m | 1) < bm && (n | 1) < N;
-#pragma unroll
-                    for (int j = 0; j < 16; j += 2) {
-                        float a0 = v[j], a1 = v[j + 1];
-                        if (PRO) {
-                            a0 *= rstd_s[c * 16 + j];
-                            a1 *= rstd_s[c * 16 + j + 1];
-                        }
-                        const float got = __shfl_xor_sync(0xffffffffu, even ? a1 : a0, 1);
-                        const float gate = even ? a0 : got, up = even ? got : a1;
-                        const int r = r0 + c * 16 + j + (even ? 0 : 1);
-                        if (pair_ok && r < R) rfx::st<TO>(y, (size_t)r * (N / 2) + n / 2, silu_mul_for<TO>(gate, up));
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int rr = c * 16 + j, r = r0 + rr, n = n0 + m;
-                        float a = v[j];
-                        if (PRO) a *= rstd_s[rr];
-                        if (EPI == 0) {
-                            if (r < R && m < bm && n < N) rfx::st<TO>(y, (size_t)r * N + n, a);
-                        } else {
-                            float hv = 0.0f;
-                            if (r < R && m < bm && n < N) {
-                                const size_t idx = (size_t)r * N + n;
-                                hv = fuse.h[idx] + a;
-                                fuse.h[idx] = hv;
-                                fuse.hb[idx] = __float2bfloat16_rn(hv * (fuse.nw_offset + fuse.nw[n]));
-                            }
-                            sq[rr * BM + m] = hv * hv;
-                        }
-                    }
-                }
-                if (c == 0 && threadIdx.x == 64) trace_mark(trace_id, 4);
-            }
-            if (threadIdx.x == 64) trace_mark(trace_id, 5);
-            if (EPI == 2) {
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                // this CTA's partial of each row's sum of squares, added in index order
-                if (m < BN && r0 + m < R) {
-                    float tot = 0.0f;
-                    for (int i = 0; i < bm; ++i) tot += sq[m * BM + i];
-                    fuse.ssq_out[(size_t)(r0 + m) * gridDim.x + blockIdx.x] = tot;
-                }
-            }
-        }
-        tc_fence_before_sync();
-    }
-
-    if (ksplit > 1) {
-        // After one cluster barrier every rank holds all ranks' partial rows of its
-        // share of the tile in its own shared memory: [rank][column][row].  Sum in
-        // rank order, then the epilogue.  Nobody reads remote memory after the
-        // barrier, so CTAs may leave as they finish.
-        cg::cluster_group cluster = cg::this_cluster();
-        rfx::pdl_wait();
+        const float* recv = stage0;
+        float* sq = reinterpret_cast<float*>(tiles);  // [BN][mw] (split K); this CTA's stages are drained by then
         // Four neighbouring rows of the tile at a time where the sizes allow it
         // (the slices are whole multiples of four and so are the output's rows):
         // one 16-byte access per rank's partial, per residual, per result.
         const bool quads = (mw & 3) == 0 && (N & 3) == 0 && (bm & 3) == 0;
-        // The residual rows this rank will add to (EPI 2) and their norm weights
-        // are on their way while the cluster's barrier is waited for.
-        constexpr int MAX_IT = (BN * (BM / 8) + THREADS - 1) / THREADS;  // at two ranks; fewer with more
-        float4 hv[EPI == 2 ? MAX_IT : 1], nwv[EPI == 2 ? MAX_IT : 1];
-        if (EPI == 2 && quads) {
-            const int mq = mw >> 2;
+        const int mq = mw >> 2;
+        // Split K, EPI 2: the residual rows this rank will add to and their norm
+        // weights are fetched now, long before they are needed.
+        constexpr int MAX_IT = (EPI == 2 && BN <= 64) ? (BN * (BM / 8) + ET - 1) / ET : 1;  // two ranks or more
+        float4 hv[MAX_IT], nwv[MAX_IT];
+        if (EPI == 2 && BN <= 64 && ksplit > 1 && quads) {
 #pragma unroll
             for (int it = 0; it < MAX_IT; ++it) {
-                const int e = threadIdx.x + it * THREADS;
+                hv[it] = nwv[it] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (it * ET >= BN * mq) continue;
+                const int e = et + it * ET;
                 const int rr = e / mq, ml = 4 * (e % mq), mm = z * mw + ml;
                 const int r = r0 + rr, n = n0 + mm;
-                hv[it] = nwv[it] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                 if (e < BN * mq && mm < bm && r < R && n < N) {
                     hv[it] = *reinterpret_cast<const float4*>(fuse.h + (size_t)r * N + n);
                     nwv[it] = *reinterpret_cast<const float4*>(fuse.nw + n);
                 }
             }
         }
-        if (threadIdx.x == 64) trace_mark(trace_id, 4);
-        cluster.sync();
-        if (threadIdx.x == 64) trace_mark(trace_id, 5);
-        const float* recv = reinterpret_cast<const float*>(tiles + (size_t)stages * S::STAGE_BYTES);
-        float* sq = reinterpret_cast<float*>(tiles);  // [BN][mw]; this CTA's stages are drained
-        if (quads && EPI == 0) {
-            const int mq = mw >> 2;
-            for (int e = threadIdx.x; e < BN * mq; e += THREADS) {
-                const int rr = e / mq, ml = 4 * (e % mq), mm = z * mw + ml;
-                const int r = r0 + rr, n = n0 + mm;
-                if (mm >= bm || r >= R || n >= N) continue;
-                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                for (int p = 0; p < ksplit; ++p) {
-                    const float4 v = *reinterpret_cast<const float4*>(recv + ((size_t)p * BN + rr) * mw + ml);
-                    acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+
+        // Two passes over the same code.  The first is a dry one, while the main
+        // loop still runs: it reads no tensor memory, stores nothing and skips the
+        // waits; it brings the epilogue's instructions into the cache, which at
+        // one pass per launch would otherwise be fetched when every microsecond is
+        // on the critical path.  The second is the work.
+        bool have = nkb > 0;
+#pragma unroll 1
+        for (int pass = 0; pass < 2; ++pass) {
+            const bool dry = pass == 0;
+            if (!dry) {
+                if (have && !mbar_wait(&tmem_full_bar, 0)) {
+                    if (lane == 0) atomicExch(err, 3);
+                    have = false;
                 }
-                if (PRO) {
-                    const float f = rstd_s[rr];
-                    acc.x *= f, acc.y *= f, acc.z *= f, acc.w *= f;
-                }
-                store4(y + (size_t)r * N + n, acc);
+                tc_fence_after_sync();
+                if (warp == 2 && lane == 0) trace_mark(trace_id, 2);
             }
-        } else if (quads && EPI == 1) {
-            const int mq = mw >> 2;
-            for (int e = threadIdx.x; e < BN * mq; e += THREADS) {
-                const int rr = e / mq, ml = 4 * (e % mq), mm = z * mw + ml;
-                const int r = r0 + rr, n = n0 + mm;
-                if (mm >= bm || r >= R || n >= N) continue;
-                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);  // gate, up, gate, up
-                for (int p = 0; p < ksplit; ++p) {
-                    const float4 v = *reinterpret_cast<const float4*>(recv + ((size_t)p * BN + rr) * mw + ml);
-                    acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
-                }
-                if (PRO) {
-                    const float f = rstd_s[rr];
-                    acc.x *= f, acc.y *= f, acc.z *= f, acc.w *= f;
-                }
-                store2(y + (size_t)r * (N / 2) + n / 2, silu_mul_for<TO>(acc.x, acc.y), silu_mul_for<TO>(acc.z, acc.w));
-            }
-        } else if (quads && EPI == 2) {
-            const int mq = mw >> 2;
-            // A row's slice lies in mq neighbouring lanes; where mq is a power of
-            // two its squares are summed by shuffles, else through shared memory.
-            const bool seg = (mq & (mq - 1)) == 0 && mq <= 32;
+            const bool load = have && !dry;
+            const int chunks = dry ? 1 : BN / 16;
+            const uint32_t lane_base = tmem_d + ((uint32_t)(q * 32) << 16);
+            if (ksplit > 1) {
+                // Split K: this CTA's tile is a partial sum.  Row m of the tile belongs to
+                // rank m / mw of the cluster; send it there (remote shared-memory stores,
+                // nothing waits on them) into slot [this rank][column][m % mw].
+                cg::cluster_group cluster = cg::this_cluster();
+                const int owner = m / mw, ml = m % mw;
+                float* dst = cluster.map_shared_rank(stage0, owner < ksplit ? owner : 0) + (size_t)z * BN * mw + ml;
+                uint32_t ahead[16];
+                if (load) tmem_ld_16_nowait(lane_base, ahead);
+#pragma unroll 1
+                for (int c = 0; c < chunks; ++c) {
+                    float v[16];
+                    if (load) {
+                        tmem_ld_wait_16(ahead);
 #pragma unroll
-            for (int it = 0; it < MAX_IT; ++it) {
-                const int e = threadIdx.x + it * THREADS;
-                const bool in = e < BN * mq;
-                const int rr = e / mq, ml = 4 * (e % mq), mm = z * mw + ml;
-                const int r = r0 + rr, n = n0 + mm;
-                float4 t = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                if (in && mm < bm && r < R && n < N) {
-                    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                    for (int p = 0; p < ksplit; ++p) {
-                        const float4 v =
-                            *reinterpret_cast<const float4*>(recv + ((size_t)p * BN + rr) * mw + ml);
-                        acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+                        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(ahead[j]);
+                        if (c + 1 < chunks) tmem_ld_16_nowait(lane_base + (uint32_t)((c + 1) * 16), ahead);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0.0f;
                     }
-                    t = make_float4(hv[it].x + acc.x, hv[it].y + acc.y, hv[it].z + acc.z, hv[it].w + acc.w);
-                    const size_t idx = (size_t)r * N + n;
-                    *reinterpret_cast<float4*>(fuse.h + idx) = t;
-                    const float4 w4 = nwv[it];
-                    store4(fuse.hb + idx, make_float4(t.x * (fuse.nw_offset + w4.x), t.y * (fuse.nw_offset + w4.y),
-                                                      t.z * (fuse.nw_offset + w4.z), t.w * (fuse.nw_offset + w4.w)));
+                    if (m < bm && !dry) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) dst[(c * 16 + j) * mw] = v[j];
+                    }
                 }
-                if (seg) {
-                    // the same order every time: pairs inside the quad, then lanes 1, 2, 4, .. apart
-                    float ss = (t.x * t.x + t.y * t.y) + (t.z * t.z + t.w * t.w);
-                    for (int d = 1; d < mq; d <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
-                    if (in && (e % mq) == 0 && r < R)
-                        fuse.ssq_out[(size_t)r * (gridDim.x * ksplit) + blockIdx.x * ksplit + z] = ss;
-                } else if (in) {
-                    *reinterpret_cast<float4*>(sq + rr * mw + ml) =
-                        make_float4(t.x * t.x, t.y * t.y, t.z * t.z, t.w * t.w);
+                if (!dry) {
+                    tc_fence_before_sync();
+                    if (threadIdx.x == 64) trace_mark(trace_id, 4);
+                    // After one cluster barrier every rank holds all ranks' partial rows
+                    // of its share of the tile in its own shared memory: [rank][column]
+                    // [row].  Nobody reads remote memory after the barrier, so CTAs may
+                    // leave as they finish.
+                    cluster.sync();
+                    if (threadIdx.x == 64) trace_mark(trace_id, 5);
                 }
-            }
-            if (!seg) {
-                __syncthreads();
-                // this CTA's partial of each row's sum of squares, added in index order
-                if ((int)threadIdx.x < BN && r0 + (int)threadIdx.x < R) {
-                    float tot = 0.0f;
-                    for (int i = 0; i < mw; ++i) tot += sq[threadIdx.x * mw + i];
-                    fuse.ssq_out[(size_t)(r0 + threadIdx.x) * (gridDim.x * ksplit) + blockIdx.x * ksplit + z] = tot;
+                // Sum in rank order, then the epilogue.
+                if (quads && EPI == 0) {
+                    for (int e = et; e < BN * mq; e += ET) {
+                        const int rr = e / mq, ml4 = 4 * (e % mq), mm = z * mw + ml4;
+                        const int r = r0 + rr, n = n0 + mm;
+                        if (mm >= bm || r >= R || n >= N) continue;
+                        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                        for (int p = 0; p < 8; ++p) {  // every rank's load in flight at once
+                            if (p < ksplit) {
+                                const float4 v = *reinterpret_cast<const float4*>(recv + (p * BN + rr) * mw + ml4);
+                                acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+                            }
+                        }
+                        if (PRO) {
+                            const float f = rstd_s[rr];
+                            acc.x *= f, acc.y *= f, acc.z *= f, acc.w *= f;
+                        }
+                        if (!dry) store4(y + (size_t)r * N + n, acc);
+                    }
+                } else if (quads && EPI == 1) {
+                    for (int e = et; e < BN * mq; e += ET) {
+                        const int rr = e / mq, ml4 = 4 * (e % mq), mm = z * mw + ml4;
+                        const int r = r0 + rr, n = n0 + mm;
+                        if (mm >= bm || r >= R || n >= N) continue;
+                        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);  // gate, up, gate, up
+#pragma unroll
+                        for (int p = 0; p < 8; ++p) {  // every rank's load in flight at once
+                            if (p < ksplit) {
+                                const float4 v = *reinterpret_cast<const float4*>(recv + (p * BN + rr) * mw + ml4);
+                                acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+                            }
+                        }
+                        if (PRO) {
+                            const float f = rstd_s[rr];
+                            acc.x *= f, acc.y *= f, acc.z *= f, acc.w *= f;
+                        }
+                        const float o0 = silu_mul_for<TO>(acc.x, acc.y), o1 = silu_mul_for<TO>(acc.z, acc.w);
+                        if (!dry) store2(y + (size_t)r * (N / 2) + n / 2, o0, o1);
+                    }
+                } else if (quads && EPI == 2 && BN <= 64) {
+                    // A row's slice lies in mq neighbouring lanes; where mq is a power of
+                    // two its squares are summed by shuffles, else through shared memory.
+                    const bool seg = mq > 0 && (mq & (mq - 1)) == 0 && mq <= 32;
+                    const int mq_shift = 31 - __clz(mq > 0 ? mq : 1);
+#pragma unroll
+                    for (int it = 0; it < MAX_IT; ++it) {
+                        if (it * ET >= BN * mq) break;  // the same for every thread
+                        const int e = et + it * ET;
+                        const bool in = e < BN * mq;
+                        const int rr = seg ? e >> mq_shift : e / mq;
+                        const int ml4 = 4 * (seg ? e & (mq - 1) : e % mq), mm = z * mw + ml4;
+                        const int r = r0 + rr, n = n0 + mm;
+                        float4 t = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        if (in && mm < bm && r < R && n < N) {
+                            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                            for (int p = 0; p < 8; ++p) {  // every rank's load in flight at once
+                                if (p < ksplit) {
+                                    const float4 v = *reinterpret_cast<const float4*>(recv + (p * BN + rr) * mw + ml4);
+                                    acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+                                }
+                            }
+                            t = make_float4(hv[it].x + acc.x, hv[it].y + acc.y, hv[it].z + acc.z, hv[it].w + acc.w);
+                            const size_t idx = (size_t)r * N + n;
+                            const float4 w4 = nwv[it];
+                            const float4 hb4 = make_float4(t.x * (fuse.nw_offset + w4.x), t.y * (fuse.nw_offset + w4.y),
+                                                           t.z * (fuse.nw_offset + w4.z), t.w * (fuse.nw_offset + w4.w));
+                            if (!dry) {
+                                *reinterpret_cast<float4*>(fuse.h + idx) = t;
+                                store4(fuse.hb + idx, hb4);
+                            }
+                        }
+                        if (seg) {
+                            // the same order every time: pairs inside the quad, then lanes 1, 2, 4, .. apart
+                            float ss = (t.x * t.x + t.y * t.y) + (t.z * t.z + t.w * t.w);
+                            for (int d = 1; d < mq; d <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+                            if (in && (ml4 == 0) && r < R && !dry)
+                                fuse.ssq_out[(size_t)r * (gridDim.x * ksplit) + blockIdx.x * ksplit + z] = ss;
+                        } else if (in && !dry) {
+                            *reinterpret_cast<float4*>(sq + rr * mw + ml4) =
+                                make_float4(t.x * t.x, t.y * t.y, t.z * t.z, t.w * t.w);
+                        }
+                    }
+                    if (!seg) {
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        // this CTA's partial of each row's sum of squares, added in index order
+                        if (et < BN && r0 + et < R && !dry) {
+                            float tot = 0.0f;
+                            for (int i = 0; i < mw; ++i) tot += sq[et * mw + i];
+                            fuse.ssq_out[(size_t)(r0 + et) * (gridDim.x * ksplit) + blockIdx.x * ksplit + z] = tot;
+                        }
+                    }
+                } else if (EPI == 0) {
+                    for (int e = et; e < BN * mw; e += ET) {
+                        const int rr = e / mw, ml1 = e % mw, mm = z * mw + ml1;
+                        if (mm >= bm) continue;
+                        float acc = 0.0f;
+                        for (int p = 0; p < ksplit; ++p) acc += recv[((size_t)p * BN + rr) * mw + ml1];
+                        if (PRO) acc *= rstd_s[rr];
+                        const int r = r0 + rr;
+                        if (r < R && n0 + mm < N && !dry) rfx::st<TO>(y, (size_t)r * N + n0 + mm, acc);
+                    }
+                } else if (EPI == 1) {
+                    const int pw = mw / 2;
+                    for (int e = et; e < BN * pw; e += ET) {
+                        const int rr = e / pw, ml1 = 2 * (e % pw), mm = z * mw + ml1;
+                        if (mm + 1 >= bm) continue;
+                        float g = 0.0f, u = 0.0f;
+                        for (int p = 0; p < ksplit; ++p) {
+                            g += recv[((size_t)p * BN + rr) * mw + ml1];
+                            u += recv[((size_t)p * BN + rr) * mw + ml1 + 1];
+                        }
+                        if (PRO) {
+                            g *= rstd_s[rr];
+                            u *= rstd_s[rr];
+                        }
+                        const int r = r0 + rr;
+                        if (r < R && n0 + mm + 1 < N && !dry)
+                            rfx::st<TO>(y, (size_t)r * (N / 2) + (n0 + mm) / 2, silu_mul_for<TO>(g, u));
+                    }
+                } else {
+                    for (int e = et; e < BN * mw; e += ET) {
+                        const int rr = e / mw, ml1 = e % mw, mm = z * mw + ml1;
+                        const int r = r0 + rr, n = n0 + mm;
+                        float hv1 = 0.0f;
+                        if (mm < bm && r < R && n < N && !dry) {
+                            float acc = 0.0f;
+                            for (int p = 0; p < ksplit; ++p) acc += recv[((size_t)p * BN + rr) * mw + ml1];
+                            const size_t idx = (size_t)r * N + n;
+                            hv1 = fuse.h[idx] + acc;
+                            fuse.h[idx] = hv1;
+                            fuse.hb[idx] = __float2bfloat16_rn(hv1 * (fuse.nw_offset + fuse.nw[n]));
+                        }
+                        if (!dry) sq[rr * mw + ml1] = hv1 * hv1;
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    // this CTA's partial of each row's sum of squares, added in index order
+                    if (et < BN && r0 + et < R && !dry) {
+                        float tot = 0.0f;
+                        for (int i = 0; i < mw; ++i) tot += sq[et * mw + i];
+                        fuse.ssq_out[(size_t)(r0 + et) * (gridDim.x * ksplit) + blockIdx.x * ksplit + z] = tot;
+                    }
                 }
-            }
-        } else         if (EPI == 0) {
-            for (int e = threadIdx.x; e < BN * mw; e += THREADS) {
-                const int rr = e / mw, ml = e % mw, mm = z * mw + ml;
-                if (mm >= bm) continue;
-                float acc = 0.0f;
-                for (int p = 0; p < ksplit; ++p) acc += recv[((size_t)p * BN + rr) * mw + ml];
-                if (PRO) acc *= rstd_s[rr];
-                const int r = r0 + rr;
-                if (r < R && n0 + mm < N) rfx::st<TO>(y, (size_t)r * N + n0 + mm, acc);
-            }
-        } else if (EPI == 1) {
-            const int pw = mw / 2;
-            for (int e = threadIdx.x; e < BN * pw; e += THREADS) {
-                const int rr = e / pw, ml = 2 * (e % pw), mm = z * mw + ml;
-                if (mm + 1 >= bm) continue;
-                float g = 0.0f, u = 0.0f;
-                for (int p = 0; p < ksplit; ++p) {
-                    g += recv[((size_t)p * BN + rr) * mw + ml];
-                    u += recv[((size_t)p * BN + rr) * mw + ml + 1];
+                if (!dry && threadIdx.x == 64) trace_mark(trace_id, 6);
+            } else {
+                // One CTA has the whole sum: finish straight from the registers.  The
+                // next 16 columns are on their way from tensor memory while these are
+                // worked on.
+                float* sq1 = stage0;  // [BN][BM] squares of the new residual (EPI 2)
+                uint32_t ahead[16];
+                if (load) tmem_ld_16_nowait(lane_base, ahead);
+#pragma unroll 1
+                for (int c = 0; c < chunks; ++c) {
+                    float v[16];
+                    if (load) {
+                        tmem_ld_wait_16(ahead);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(ahead[j]);
+                        if (c + 1 < chunks) tmem_ld_16_nowait(lane_base + (uint32_t)((c + 1) * 16), ahead);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                    }
+                    if (EPI == 1) {
+                        // Rows alternate gate, up: lanes 2i and 2i + 1 hold one feature's
+                        // pair.  Of every two columns the even lane finishes the first and
+                        // the odd lane the second, after one exchange.
+                        const bool even = (m & 1) == 0;
+                        const int n = n0 + m;
+                        const bool pair_ok = (m | 1) < bm && (n | 1) < N && !dry;
+#pragma unroll
+                        for (int j = 0; j < 16; j += 2) {
+                            float a0 = v[j], a1 = v[j + 1];
+                            if (PRO) {
+                                a0 *= rstd_s[c * 16 + j];
+                                a1 *= rstd_s[c * 16 + j + 1];
+                            }
+                            const float got = __shfl_xor_sync(0xffffffffu, even ? a1 : a0, 1);
+                            const float gate = even ? a0 : got, up = even ? got : a1;
+                            const int r = r0 + c * 16 + j + (even ? 0 : 1);
+                            const float o = silu_mul_for<TO>(gate, up);
+                            if (pair_ok && r < R) rfx::st<TO>(y, (size_t)r * (N / 2) + n / 2, o);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int rr = c * 16 + j, r = r0 + rr, n = n0 + m;
+                            float a = v[j];
+                            if (PRO) a *= rstd_s[rr];
+                            if (EPI == 0) {
+                                if (r < R && m < bm && n < N && !dry) rfx::st<TO>(y, (size_t)r * N + n, a);
+                            } else {
+                                float hv1 = 0.0f;
+                                if (r < R && m < bm && n < N && !dry) {
+                                    const size_t idx = (size_t)r * N + n;
+                                    hv1 = fuse.h[idx] + a;
+                                    fuse.h[idx] = hv1;
+                                    fuse.hb[idx] = __float2bfloat16_rn(hv1 * (fuse.nw_offset + fuse.nw[n]));
+                                }
+                                if (!dry) sq1[rr * BM + m] = hv1 * hv1;
+                            }
+                        }
+                    }
+                    if (!dry && c == 0 && threadIdx.x == 64) trace_mark(trace_id, 4);
                 }
-                if (PRO) {
-                    g *= rstd_s[rr];
-                    u *= rstd_s[rr];
+                if (!dry && threadIdx.x == 64) trace_mark(trace_id, 5);
+                if (EPI == 2) {
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    // this CTA's partial of each row's sum of squares, added in index order
+                    if (m < BN && r0 + m < R && !dry) {
+                        float tot = 0.0f;
+                        for (int i = 0; i < bm; ++i) tot += sq1[m * BM + i];
+                        fuse.ssq_out[(size_t)(r0 + m) * gridDim.x + blockIdx.x] = tot;
+                    }
                 }
-                const int r = r0 + rr;
-                if (r < R && n0 + mm + 1 < N)
-                    rfx::st<TO>(y, (size_t)r * (N / 2) + (n0 + mm) / 2, silu_mul_for<TO>(g, u));
-            }
-        } else {
-            for (int e = threadIdx.x; e < BN * mw; e += THREADS) {
-                const int rr = e / mw, ml = e % mw, mm = z * mw + ml;
-                const int r = r0 + rr, n = n0 + mm;
-                float hv = 0.0f;
-                if (mm < bm && r < R && n < N) {
-                    float acc = 0.0f;
-                    for (int p = 0; p < ksplit; ++p) acc += recv[((size_t)p * BN + rr) * mw + ml];
-                    const size_t idx = (size_t)r * N + n;
-                    hv = fuse.h[idx] + acc;
-                    fuse.h[idx] = hv;
-                    fuse.hb[idx] = __float2bfloat16_rn(hv * (fuse.nw_offset + fuse.nw[n]));
-                }
-                sq[rr * mw + ml] = hv * hv;
-            }
-            __syncthreads();
-            // this CTA's partial of each row's sum of squares, added in index order
-            if ((int)threadIdx.x < BN && r0 + (int)threadIdx.x < R) {
-                float tot = 0.0f;
-                for (int i = 0; i < mw; ++i) tot += sq[threadIdx.x * mw + i];
-                fuse.ssq_out[(size_t)(r0 + threadIdx.x) * (gridDim.x * ksplit) + blockIdx.x * ksplit + z] = tot;
+                if (!dry) tc_fence_before_sync();
             }
         }
-        if (threadIdx.x == 64) trace_mark(trace_id, 6);
+    }
+    // the producer and the MMA warp take part in the cluster's barrier too
+    if (warp < 2 && ksplit > 1) {
+        rfx::pdl_wait();
+        cg::this_cluster().sync();
     }
 
     __syncthreads();

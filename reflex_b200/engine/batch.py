@@ -107,17 +107,51 @@ def pack_host(tokens: Sequence[Sequence[int]], slots: Sequence[int], starts: Seq
     return words, offs, new_counts, row0, want_rows
 
 
-def make_batch(tokens, slots, starts, want, device, buffer: Optional[torch.Tensor] = None) -> StepBatch:
-    """Build the step's descriptors with one host-to-device copy.  With
-    `buffer` (a device int32 tensor large enough) the words are copied into it,
-    so a captured graph that reads the buffer sees the new step."""
+class Staging:
+    """Pinned host memory for the steps' descriptors: a small ring of buffers,
+    each with the event of the copy that last read it, so that a step never
+    overwrites words a copy still in flight has to read."""
+
+    def __init__(self, device, depth: int = 4):
+        self.device = torch.device(device)
+        self.depth = depth
+        self.buffers: List[Optional[torch.Tensor]] = [None] * depth
+        self.events: List[Optional[torch.cuda.Event]] = [None] * depth
+        self.next = 0
+
+    def copy(self, words: List[int], dev: torch.Tensor) -> None:
+        """words -> pinned buffer -> `dev` (device int32, at least as long), on
+        the current stream, without blocking the host."""
+        i = self.next
+        self.next = (i + 1) % self.depth
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        n = len(words)
+        if self.buffers[i] is None or self.buffers[i].numel() < n:
+            self.buffers[i] = torch.empty((max(n, 256),), dtype=torch.int32, pin_memory=True)
+        host = self.buffers[i][:n]
+        host.copy_(torch.tensor(words, dtype=torch.int32))
+        dev[:n].copy_(host, non_blocking=True)
+        if self.events[i] is None:
+            self.events[i] = torch.cuda.Event()
+        self.events[i].record()
+
+
+def make_batch(tokens, slots, starts, want, device, buffer: Optional[torch.Tensor] = None,
+               staging: Optional[Staging] = None) -> StepBatch:
+    """Build the step's descriptors with one host-to-device copy (from pinned
+    memory when a `staging` ring is given).  With `buffer` (a device int32
+    tensor large enough) the words are copied into it, so a captured graph that
+    reads the buffer sees the new step."""
     words, offs, new_counts, row0, want_rows = pack_host(tokens, slots, starts, want)
-    host = torch.tensor(words, dtype=torch.int32)
     if buffer is None:
-        dev = host.to(device)
+        dev = torch.empty((len(words),), dtype=torch.int32, device=device)
     else:
         dev = buffer[: len(words)]
-        dev.copy_(host)
+    if staging is not None:
+        staging.copy(words, dev)
+    else:
+        dev.copy_(torch.tensor(words, dtype=torch.int32))
 
     def f(name):
         p, n = offs[name]

@@ -33,7 +33,7 @@ class DecodeGraph:
 
     def run(self, tokens, slots, starts, want) -> torch.Tensor:
         eng = self.engine
-        batch = make_batch(tokens, slots, starts, want, eng.device, buffer=self.buffer)
+        batch = make_batch(tokens, slots, starts, want, eng.device, buffer=self.buffer, staging=eng.staging)
         batch.context_hint = self.context_hint
         if self.graph is None:
             # the first decode steps of a batch size run eagerly: they size every

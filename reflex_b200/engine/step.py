@@ -19,7 +19,7 @@ import torch
 
 from ..cache.store import PAGE_TOKENS, Cache
 from ..errors import CacheError, InvalidInput
-from .batch import StepBatch, decode_context_bucket, make_batch
+from .batch import Staging, StepBatch, decode_context_bucket, make_batch
 from .model import CausalLM
 
 StepEntry = Tuple[int, Sequence[int], Sequence[int]]  # (sequence, tokens, wanted places)
@@ -37,6 +37,7 @@ class Engine:
         self._graphs: Dict[Tuple[int, int], "object"] = {}
         self._eager_decodes: Dict[int, int] = {}  # eager decode steps run so far, per batch size
         self.steps_run = 0
+        self.staging = Staging(self.device) if torch.device(self.device).type == "cuda" else None
 
     # --- sequences ----------------------------------------------------------
     def open(self) -> int:
@@ -93,7 +94,7 @@ class Engine:
             if self.use_graphs and all(len(t) == 1 for t in tokens) and n_want == len(tokens):
                 logits = self._decode_graphed(tokens, slots, starts, want)
             else:
-                batch = make_batch(tokens, slots, starts, want, self.device)
+                batch = make_batch(tokens, slots, starts, want, self.device, staging=self.staging)
                 if n_want:
                     logits = self.model.forward(batch, cache)
                 else:

@@ -495,12 +495,19 @@ def attention(q, k_pages, v_pages, page_table, page_size, batch, nq, nkv, head_d
 
 
 # ------------------------------------------------------------------ sampling
-def argmax(logits: torch.Tensor) -> torch.Tensor:
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None,
+           scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Index of the largest logit per row (ties: the highest index).  `out`
+    (int32 [B]) and `scratch` (float32, B * 128) may be given to spare the
+    allocations of a call a step."""
     B, V = logits.shape
     _chk(logits, "logits", torch.float32)
-    out = torch.empty((B,), dtype=torch.int32, device=logits.device)
-    scratch = torch.empty((B * 64 * 2,), dtype=torch.float32, device=logits.device)
-    st = native.lib().rfx_argmax(logits.data_ptr(), V, B, V, out.data_ptr(), scratch.data_ptr(), _stream())
+    if out is None:
+        out = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    if scratch is None:
+        scratch = torch.empty((B * 64 * 2,), dtype=torch.float32, device=logits.device)
+    st = native.lib().rfx_argmax(logits.data_ptr(), V, B, V, _chk(out, "out", torch.int32),
+                                 _chk(scratch, "scratch", torch.float32), _stream())
     native.check(st, "argmax")
     return out
 

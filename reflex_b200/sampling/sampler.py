@@ -21,6 +21,7 @@ class Sampler:
         self.seed = params.seed if params.seed is not None else fresh_seed()
         self._const = {}
         self._scratch = None
+        self._greedy = {}  # batch size -> (ids, scratch) reused by every greedy pick
 
     def _constants(self, n: int):
         if n not in self._const:
@@ -35,9 +36,13 @@ class Sampler:
     def pick(self, logits: torch.Tensor, requests: Sequence[int], steps: Sequence[int]) -> List[int]:
         """logits [n, V] for the given requests, each at its own step count;
         returns the chosen ids on the host."""
-        if self.params.is_greedy():
-            return ops.argmax(logits).tolist()
         n, V = logits.shape
+        if self.params.is_greedy():
+            if n not in self._greedy:
+                self._greedy[n] = (torch.empty((n,), dtype=torch.int32, device=self.device),
+                                   torch.empty((n * 128,), dtype=torch.float32, device=self.device))
+            out, scratch = self._greedy[n]
+            return ops.argmax(logits, out=out, scratch=scratch).tolist()
         u = torch.tensor([uniform(self.seed, r, s) for r, s in zip(requests, steps)],
                          dtype=torch.float32).to(self.device)
         t, k, tp = self._constants(n)

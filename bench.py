@@ -29,6 +29,12 @@ QWEN3_8B = {
     "max_position_embeddings": 40960, "hidden_act": "silu", "attention_bias": False,
     "rope_scaling": None, "use_sliding_window": False, "sliding_window": None,
 }
+# the other sizes of the family, for runs beyond the default (--shape)
+SHAPES = {
+    "8b": {},
+    "14b": {"num_hidden_layers": 40, "hidden_size": 5120, "num_attention_heads": 40, "intermediate_size": 17408},
+    "32b": {"num_hidden_layers": 64, "hidden_size": 5120, "num_attention_heads": 64, "intermediate_size": 25600},
+}
 CONTEXT = 4096
 PROMPT = 512
 PREFILL_TOKENS = 2048
@@ -113,6 +119,7 @@ def prefill_flops(cfg, layers, T):
 
 
 def main() -> int:
+    global PROMPT, CONTEXT
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -122,7 +129,11 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 decode points")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill")
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="layer sizes (default: Qwen3-8B)")
+    ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt tokens before the decode steps")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="cache positions per sequence")
     args = ap.parse_args()
+    PROMPT, CONTEXT = args.prompt, max(args.context, args.prompt + args.steps + args.warmup + 64)
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -144,6 +155,7 @@ def main() -> int:
     from reflex_b200.weights import random_model_on_device
 
     cfg = dict(QWEN3_8B)
+    cfg.update(SHAPES[args.shape])
     full_layers = cfg["num_hidden_layers"]
     layers = args.layers or full_layers
     cfg["num_hidden_layers"] = layers
@@ -215,13 +227,14 @@ def main() -> int:
            "h2d_bytes_per_step": words * 4, "d2h_bytes_per_step": args.batch * 4}
 
     out = {
-        "metric": "decode tokens/s at batch 8 (Qwen3-8B bf16, 512-token prompts, context 4096)",
+        "metric": f"decode tokens/s at batch {args.batch} (Qwen3-{args.shape.upper()} bf16, {PROMPT}-token prompts, "
+                  f"context {CONTEXT})",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random-init weights N(0, 0.02)",
         "impl": "ours",
         "config": {
-            "model": "Qwen3-8B layer sizes", "layers": layers, "layers_full_model": full_layers,
+            "model": f"Qwen3-{args.shape.upper()} layer sizes", "layers": layers, "layers_full_model": full_layers,
             "hidden_size": cfg["hidden_size"], "intermediate_size": cfg["intermediate_size"],
             "num_attention_heads": cfg["num_attention_heads"],
             "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],

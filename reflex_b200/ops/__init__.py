@@ -336,20 +336,22 @@ SM_COUNT = 148
 
 def decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int = 64) -> int:
     """Key-range splits of the decode kernel for rows whose longest context has
-    `max_pages` pages.  A split costs a second kernel (the combine) and buys
-    parallelism; fitted to step times on a B200 at batches of 1, 8 and 64: about
-    4 us fixed per launch, 0.8 us per page a CTA walks, 4 us for the partials,
-    the combine and its hand-off.  The smallest estimate wins."""
+    `max_pages` pages.  A split costs a second kernel (the combine, whose work
+    grows with the splits) and buys parallelism; fitted to step times on a B200
+    at batches of 1 to 64 and contexts of 512 to 16,000: about 4 us fixed per
+    launch, 0.8 us per page a CTA walks, CTAs in whole waves of two per SM,
+    3 us + 0.25 us a split for the partials, the combine and its hand-off.  The
+    smallest estimate wins."""
     forced = int(_os.environ.get("REFLEX_B200_DECODE_SPLITS", "0"))  # tuning aid
     if forced > 0:
         return forced
     ctas = n_rows * nkv * ((nq // nkv + 15) // 16)
     best, best_cost = 1, None
-    for s in (1, 2, 4, 8, 16):
+    for s in (1, 2, 4, 8, 16, 32, 64):
         if s > max(1, max_pages):
             break
-        waves = max(1.0, ctas * s / (2.0 * SM_COUNT))
-        cost = 4.0 + -(-max_pages // s) * 0.8 * waves + (4.0 if s > 1 else 0.0)
+        waves = -(-ctas * s // (2 * SM_COUNT))
+        cost = 4.0 + -(-max_pages // s) * 0.8 * waves + (3.0 + 0.25 * s if s > 1 else 0.0)
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best

@@ -29,8 +29,10 @@ struct alignas(sizeof(T) * N <= 16 ? sizeof(T) * N : 16) Pack {
 // VEC: head_dim == 32 * PER and a lane holds PER neighbouring elements, moved
 // with one wide access; a rotary pair (e, e + rd/2) then lies in two lanes at
 // the same place of their packs and is exchanged by a shuffle (rd/2 a multiple
-// of PER).  Otherwise lane l holds elements l, l + 32, ... and the pair is
-// exchanged through shared memory.
+// of PER).  What a lane needs for every head of the row (its norm weights, its
+// sines and cosines, the row's place in the cache) is fetched once per block.
+// Otherwise lane l holds elements l, l + 32, ... and the pair is exchanged
+// through shared memory.
 template <typename TI, typename TO, int PER, bool VEC>
 __global__ void __launch_bounds__(256)
 qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restrict__ q_w,
@@ -38,7 +40,7 @@ qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restr
                 const float* __restrict__ rope_denom, int rotary_dim,
                 const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                 TO* __restrict__ q_out, TO* __restrict__ k_pages, TO* __restrict__ v_pages,
-                PagedKV cache, int nq, int nkv_in) {
+                PagedKV cache, int nq, int nkv_in, int dry_pass) {
     extern __shared__ float smem[];  // [warps][head_dim], then cos[half], sin[half]
     pdl_launch_dependents();
     const int d = cache.head_dim;
@@ -53,126 +55,156 @@ qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restr
     // step's inputs, so this does not wait for the preceding kernel
     float* cs_tab = smem + nwarps * d;
     float* sn_tab = cs_tab + half;
-    if (rope_denom != nullptr) {
+    const bool rotate = rope_denom != nullptr && half > 0;
+    if (rotate) {
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
             const float theta = (float)pos / rope_denom[i];
             sincosf(theta, &sn_tab[i], &cs_tab[i]);
         }
     }
+    // where this row's key and value heads go: head 0's place, the others a tile apart
+    const size_t kv0 = nkv_in > 0 ? kv_offset(cache, slot, pos, 0) : 0;
+    const size_t kv_head_stride = (size_t)cache.page_size * d;
     __syncthreads();
+    const int stride = gridDim.y * nwarps;
+    auto destination = [&](int hh) -> TO* {
+        if (hh < nq) return q_out + ((size_t)r * nq + hh) * d;
+        if (hh < nq + nkv_in) return k_pages + kv0 + (size_t)(hh - nq) * kv_head_stride;
+        return v_pages + kv0 + (size_t)(hh - nq - nkv_in) * kv_head_stride;
+    };
 
     // Two passes over the same code.  The first, before the wait on the preceding
-    // kernel, is a dry one: it takes a norm weight vector for its input (never the
-    // other kernel's output), does one head and stores nothing; it brings the
-    // instructions into the cache.  The second is the work.
+    // kernel, is a dry one (decode-sized launches only): it takes a norm weight
+    // vector for its input (never the other kernel's output), does one head and
+    // stores nothing; it brings the instructions into the cache.  The second is
+    // the work.
     const TI* dry_src = reinterpret_cast<const TI*>(q_w ? q_w : k_w);
 #pragma unroll 1
-    for (int pass = dry_src ? 0 : 1; pass < 2; ++pass) {
-    const bool dry = pass == 0;
-    if (!dry) pdl_wait();
-    // one warp per (row, head): blockIdx.y walks the heads in groups of nwarps
-    for (int hh = blockIdx.y * nwarps + warp; hh < total; hh += gridDim.y * nwarps) {
-        if (dry && hh >= gridDim.y * nwarps) break;
-        const TI* src = dry ? dry_src : qkv + (size_t)r * row_stride + (size_t)hh * d;
-        const bool is_q = hh < nq;
-        const bool is_k = !is_q && hh < nq + nkv_in;
-        TO* dst;
-        if (is_q) {
-            dst = q_out + ((size_t)r * nq + hh) * d;
-        } else if (is_k) {
-            dst = k_pages + kv_offset(cache, slot, pos, hh - nq);
-        } else {
-            dst = v_pages + kv_offset(cache, slot, pos, hh - nq - nkv_in);
-        }
+    for (int pass = (dry_src && dry_pass) ? 0 : 1; pass < 2; ++pass) {
+        const bool dry = pass == 0;
+        if (!dry) pdl_wait();
         if constexpr (VEC) {
-            const Pack<TI, PER> in = *reinterpret_cast<const Pack<TI, PER>*>(src + lane * PER);
-            float v[PER];
+            // this lane's share of what every head of the row needs
+            const int e0 = lane * PER;
+            const bool turns = rotate && e0 < rotary_dim;  // a pack lies on one side of the rotation
+            const bool low = e0 < half;
+            const int hl = half / PER;  // lanes in half a rotation
+            const int partner = (low ? lane + hl : lane - hl) & 31;
+            Pack<float, PER> sn, cs, wq, wk;
 #pragma unroll
-            for (int i = 0; i < PER; ++i) v[i] = ld<TI>(in.a, i);
-            if (is_q || is_k) {
-                const float* w = is_q ? q_w : k_w;
-                if (w) {
-                    float ss = 0.0f;
+            for (int i = 0; i < PER; ++i) sn.a[i] = cs.a[i] = wq.a[i] = wk.a[i] = 0.0f;
+            if (turns) {
+                sn = *reinterpret_cast<const Pack<float, PER>*>(sn_tab + (low ? e0 : e0 - half));
+                cs = *reinterpret_cast<const Pack<float, PER>*>(cs_tab + (low ? e0 : e0 - half));
+            }
+            if (q_w) wq = *reinterpret_cast<const Pack<float, PER>*>(q_w + e0);
+            if (k_w) wk = *reinterpret_cast<const Pack<float, PER>*>(k_w + e0);
+            // three heads at a time: their loads first, so that the latencies
+            // overlap, then the arithmetic
+            constexpr int CH = 3;
+            for (int hh0 = blockIdx.y * nwarps + warp; hh0 < total; hh0 += stride * CH) {
+                Pack<TI, PER> in[CH];
 #pragma unroll
-                    for (int i = 0; i < PER; ++i) ss = fmaf(v[i], v[i], ss);
-                    const float rinv = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);
-                    const Pack<float, PER> ww = *reinterpret_cast<const Pack<float, PER>*>(w + lane * PER);
-#pragma unroll
-                    for (int i = 0; i < PER; ++i) v[i] = (v[i] * rinv) * (w_offset + ww.a[i]);
-                }
-                if (rope_denom != nullptr && half > 0) {
-                    const int hl = half / PER;  // lanes in half a rotation
-                    const int e0 = lane * PER;
-                    const int partner = lane < hl ? lane + hl : lane - hl;
-#pragma unroll
-                    for (int i = 0; i < PER; ++i) {
-                        const float other = __shfl_sync(0xffffffffu, v[i], partner & 31);
-                        const int e = e0 + i;
-                        if (e < rotary_dim) {
-                            const int fi = e < half ? e : e - half;
-                            const float sn = sn_tab[fi], cs = cs_tab[fi];
-                            v[i] = e < half ? v[i] * cs - other * sn : other * sn + v[i] * cs;
-                        }
+                for (int c = 0; c < CH; ++c) {
+                    const int hh = hh0 + c * stride;
+                    if (hh < total && !(dry && c > 0)) {
+                        const TI* src = dry ? dry_src : qkv + (size_t)r * row_stride + (size_t)hh * d;
+                        in[c] = *reinterpret_cast<const Pack<TI, PER>*>(src + e0);
                     }
                 }
+#pragma unroll
+                for (int c = 0; c < CH; ++c) {
+                    const int hh = hh0 + c * stride;
+                    if (hh >= total || (dry && c > 0)) break;
+                    const bool is_q = hh < nq, is_k = !is_q && hh < nq + nkv_in;
+                    float v[PER];
+#pragma unroll
+                    for (int i = 0; i < PER; ++i) v[i] = ld<TI>(in[c].a, i);
+                    if (is_q || is_k) {
+                        if (is_q ? q_w != nullptr : k_w != nullptr) {
+                            float ss = 0.0f;
+#pragma unroll
+                            for (int i = 0; i < PER; ++i) ss = fmaf(v[i], v[i], ss);
+                            const float rinv = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);
+#pragma unroll
+                            for (int i = 0; i < PER; ++i)
+                                v[i] = (v[i] * rinv) * (w_offset + (is_q ? wq.a[i] : wk.a[i]));
+                        }
+                        if (rotate) {
+#pragma unroll
+                            for (int i = 0; i < PER; ++i) {
+                                const float other = __shfl_sync(0xffffffffu, v[i], partner);
+                                if (turns)
+                                    v[i] = low ? v[i] * cs.a[i] - other * sn.a[i] : other * sn.a[i] + v[i] * cs.a[i];
+                            }
+                        }
+                    }
+                    Pack<TO, PER> o;
+#pragma unroll
+                    for (int i = 0; i < PER; ++i) st<TO>(o.a, i, v[i]);
+                    if (!dry) *reinterpret_cast<Pack<TO, PER>*>(destination(hh) + e0) = o;
+                }
+                if (dry) break;
             }
-            Pack<TO, PER> o;
-#pragma unroll
-            for (int i = 0; i < PER; ++i) st<TO>(o.a, i, v[i]);
-            if (!dry) *reinterpret_cast<Pack<TO, PER>*>(dst + lane * PER) = o;
-            continue;
+            continue;  // the next pass
         }
-        if (!is_q && !is_k) {  // v: stored as projected
-            for (int e = lane; e < d; e += 32)
-                if (!dry) st<TO>(dst, e, ld<TI>(src, e));
-            continue;
-        }
-        float v[PER];
-        float ss = 0.0f;
-#pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            const int e = i * 32 + lane;
-            v[i] = e < d ? ld<TI>(src, e) : 0.0f;
-            ss = fmaf(v[i], v[i], ss);
-        }
-        const float* w = is_q ? q_w : k_w;
-        if (w) {
-            const float rinv = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);
+        // one warp per (row, head): blockIdx.y walks the heads in groups of nwarps
+        for (int hh = blockIdx.y * nwarps + warp; hh < total; hh += stride) {
+            if (dry && hh >= stride) break;
+            const TI* src = dry ? dry_src : qkv + (size_t)r * row_stride + (size_t)hh * d;
+            const bool is_q = hh < nq, is_k = !is_q && hh < nq + nkv_in;
+            TO* dst = destination(hh);
+            if (!is_q && !is_k) {  // v: stored as projected
+                for (int e = lane; e < d; e += 32)
+                    if (!dry) st<TO>(dst, e, ld<TI>(src, e));
+                continue;
+            }
+            float v[PER];
+            float ss = 0.0f;
 #pragma unroll
             for (int i = 0; i < PER; ++i) {
                 const int e = i * 32 + lane;
-                if (e < d) v[i] = (v[i] * rinv) * (w_offset + w[e]);
+                v[i] = e < d ? ld<TI>(src, e) : 0.0f;
+                ss = fmaf(v[i], v[i], ss);
             }
-        }
-        if (rope_denom == nullptr || half == 0) {
+            const float* w = is_q ? q_w : k_w;
+            if (w) {
+                const float rinv = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);
+#pragma unroll
+                for (int i = 0; i < PER; ++i) {
+                    const int e = i * 32 + lane;
+                    if (e < d) v[i] = (v[i] * rinv) * (w_offset + w[e]);
+                }
+            }
+            if (!rotate) {
+#pragma unroll
+                for (int i = 0; i < PER; ++i) {
+                    const int e = i * 32 + lane;
+                    if (e < d && !dry) st<TO>(dst, e, v[i]);
+                }
+                continue;
+            }
+            __syncwarp();
 #pragma unroll
             for (int i = 0; i < PER; ++i) {
                 const int e = i * 32 + lane;
-                if (e < d && !dry) st<TO>(dst, e, v[i]);
+                if (e < d) buf[e] = v[i];
             }
-            continue;
-        }
-        __syncwarp();
+            __syncwarp();
 #pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            const int e = i * 32 + lane;
-            if (e < d) buf[e] = v[i];
-        }
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            const int e = i * 32 + lane;
-            if (e >= d) break;
-            float o = v[i];
-            if (e < rotary_dim) {
-                const int fi = e < half ? e : e - half;
-                const float sn = sn_tab[fi], cs = cs_tab[fi];
-                if (e < half) o = v[i] * cs - buf[e + half] * sn;
-                else o = buf[e - half] * sn + v[i] * cs;
+            for (int i = 0; i < PER; ++i) {
+                const int e = i * 32 + lane;
+                if (e >= d) break;
+                float o = v[i];
+                if (e < rotary_dim) {
+                    const int fi = e < half ? e : e - half;
+                    const float sn = sn_tab[fi], cs = cs_tab[fi];
+                    if (e < half) o = v[i] * cs - buf[e + half] * sn;
+                    else o = buf[e - half] * sn + v[i] * cs;
+                }
+                if (!dry) st<TO>(dst, e, o);
             }
-            if (!dry) st<TO>(dst, e, o);
         }
-    }
     }
 }
 
@@ -189,14 +221,16 @@ extern "C" int rfx_qkv_post(const void* qkv, int in_dt, int row_stride, const fl
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return RFX_ERR_BAD_ARG;
     if (nkv_in != 0 && nkv_in != nkv) return RFX_ERR_BAD_ARG;
     PagedKV cache{page_table, max_pages, page_size, nkv, head_dim};
-    const int threads = 256;  // eight heads a block
-    const size_t smem = ((size_t)(threads / 32) * head_dim + rotary_dim) * sizeof(float);
+    const int threads = 256;  // eight heads at a time
     cudaStream_t s = (cudaStream_t)stream;
-    // Few rows (decode): spread a row's heads over several blocks.  Many rows
-    // (prefill): one block a row, so the rotation table is made once per row.
-    int head_blocks = (nq + 2 * nkv_in + threads / 32 - 1) / (threads / 32);
-    if (R >= 512) head_blocks = 1;
+    // Few rows (decode): a row's heads spread over several blocks, with a dry
+    // pass.  Many rows (prefill): one block a row, and no dry pass (the code is
+    // warm after the first blocks).
+    const bool many = R >= 256;
+    int head_blocks = many ? 1 : (nq + 2 * nkv_in + threads / 32 - 1) / (threads / 32);
+    const size_t smem = ((size_t)(threads / 32) * head_dim + rotary_dim) * sizeof(float);
     dim3 grid(R, head_blocks < 65535 ? head_blocks : 65535);
+    const int dry_pass = many ? 0 : 1;
     // the wide-access form: a whole head in 32 lanes' packs, pairs a whole number of lanes apart
     const int per = head_dim / 32;
     const uintptr_t ptrs = reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
@@ -210,11 +244,13 @@ extern "C" int rfx_qkv_post(const void* qkv, int in_dt, int row_stride, const fl
         if (vec)                                                                                   \
             RFX_LAUNCH((qkv_post_kernel<TI, TO, P, true>), grid, threads, smem, s, (const TI*)qkv, \
                        row_stride, q_w, k_w, eps, w_offset, rope_denom, rotary_dim, row_pos,       \
-                       row_slot, (TO*)q_out, (TO*)k_pages, (TO*)v_pages, cache, nq, nkv_in);       \
+                       row_slot, (TO*)q_out, (TO*)k_pages, (TO*)v_pages, cache, nq, nkv_in,          \
+                       dry_pass);                                                          \
         else                                                                                       \
             RFX_LAUNCH((qkv_post_kernel<TI, TO, P, false>), grid, threads, smem, s, (const TI*)qkv, \
                        row_stride, q_w, k_w, eps, w_offset, rope_denom, rotary_dim, row_pos,       \
-                       row_slot, (TO*)q_out, (TO*)k_pages, (TO*)v_pages, cache, nq, nkv_in);       \
+                       row_slot, (TO*)q_out, (TO*)k_pages, (TO*)v_pages, cache, nq, nkv_in,          \
+                       dry_pass);                                                          \
     } while (0)
 #define RFX_POST(TI, TO)                                  \
     do {                                                  \

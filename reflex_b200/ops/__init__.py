@@ -339,8 +339,8 @@ def decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int = 64) -> int:
     `max_pages` pages.  A split costs a second kernel (the combine, whose work
     grows with the splits) and buys parallelism; fitted to step times on a B200
     at batches of 1 to 64 and contexts of 512 to 16,000: about 4 us fixed per
-    launch, 0.8 us per page a CTA walks, CTAs in whole waves of two per SM,
-    3 us + 0.25 us a split for the partials, the combine and its hand-off.  The
+    launch, 0.8 us per page a CTA walks plus 1.5 us per CTA, CTAs in whole waves
+    of two per SM, 3 us + 0.25 us a split for the partials, the combine and its hand-off.  The
     smallest estimate wins."""
     forced = int(_os.environ.get("REFLEX_B200_DECODE_SPLITS", "0"))  # tuning aid
     if forced > 0:
@@ -351,7 +351,7 @@ def decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int = 64) -> int:
         if s > max(1, max_pages):
             break
         waves = -(-ctas * s // (2 * SM_COUNT))
-        cost = 4.0 + -(-max_pages // s) * 0.8 * waves + (3.0 + 0.25 * s if s > 1 else 0.0)
+        cost = 4.0 + (-(-max_pages // s) * 0.8 + 1.5) * waves + (3.0 + 0.25 * s if s > 1 else 0.0)
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best

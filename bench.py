@@ -175,19 +175,22 @@ def main() -> int:
         prompts = torch.randint(0, V, (batch, PROMPT), generator=g).tolist()
         seqs = [eng.open() for _ in range(batch)]
         logits = eng.step([(s, p, [PROMPT - 1]) for s, p in zip(seqs, prompts)])
-        ids = ops.argmax(logits).tolist()
-        for _ in range(warmup):
-            logits = eng.step([(s, [t], [0]) for s, t in zip(seqs, ids)])
-            ids = ops.argmax(logits).tolist()
+        # the picked ids stay on the device and feed the next step (two buffers in turn)
+        ids = [torch.empty((batch,), dtype=torch.int32, device="cuda:0") for _ in range(2)]
+        scratch = torch.empty((batch * 128,), dtype=torch.float32, device="cuda:0")
+        ops.argmax(logits, out=ids[0], scratch=scratch)
+        for i in range(warmup):
+            logits = eng.step_decode(seqs, ids[i % 2])
+            ops.argmax(logits, out=ids[(i + 1) % 2], scratch=scratch)
         launches0 = ops.launch_count()
         ctx0 = eng.length(seqs[0])
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         t0 = sampler.mark() if sampler else 0
         start.record()
-        for _ in range(steps):
-            logits = eng.step([(s, [t], [0]) for s, t in zip(seqs, ids)])
-            ids = ops.argmax(logits).tolist()
+        for i in range(warmup, warmup + steps):
+            logits = eng.step_decode(seqs, ids[i % 2])
+            ops.argmax(logits, out=ids[(i + 1) % 2], scratch=scratch)
         end.record()
         torch.cuda.synchronize()
         t1 = sampler.mark() if sampler else 0

@@ -73,6 +73,8 @@ class Model:
         self.max_batch = max_batch
         self.engine = Engine(causal_lm, max_tokens=max_tokens, use_graphs=use_graphs)
         self.last_stats: Optional[GenerationStats] = None
+        # the generation loop keeps the device one step ahead of the host
+        self.decode_ahead = True
 
     @classmethod
     def load(cls, model_dir: str, weights: str = "bf16", device: str = "cuda:0", **kw) -> "Model":
@@ -104,7 +106,8 @@ class Model:
         stops = tuple(self.spec.eos_token_ids) + tuple(sampling.stop_token_ids)
         stats = GenerationStats()
         out = _generate(self.engine, plist, max_new_tokens, sampler.pick, stops,
-                        max_batch=self.max_batch, on_token=on_token, stats=stats)
+                        max_batch=self.max_batch, on_token=on_token, stats=stats,
+                        pick_async=sampler.pick_async if self.decode_ahead else None)
         self.last_stats = stats
         return out[0] if single else out
 

@@ -61,8 +61,13 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int,
              pick: Callable[[object, Sequence[int], Sequence[int]], List[int]],
              stop_token_ids: Sequence[int] = (), max_batch: int = 64,
              on_token: Optional[Callable[[int, int], None]] = None,
-             stats: Optional[GenerationStats] = None) -> List[List[int]]:
-    """Generated ids per prompt (the prompt itself is not repeated)."""
+             stats: Optional[GenerationStats] = None,
+             pick_async: Optional[Callable] = None) -> List[List[int]]:
+    """Generated ids per prompt (the prompt itself is not repeated).
+
+    With `pick_async` (a pick that leaves the ids on the device and hands back
+    an object with `.dev` and `.wait()`) and an engine that has `step_decode`,
+    the loop runs one step ahead of the host: see `_decode_ahead`."""
     if max_new_tokens < 1:
         raise InvalidInput("max_new_tokens must be at least 1")  # src/model/dense.rs:2011-2015
     if len(prompts) == 0:
@@ -78,6 +83,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int,
     outputs: List[List[int]] = [[] for _ in prompts]
     max_batch = max(1, min(max_batch, engine.cache.max_slots))
     check_errors = getattr(engine, "check_errors", lambda: None)
+    ahead = pick_async is not None and hasattr(engine, "step_decode")
     for batch in plan_batches([len(p) for p in prompts], max_new_tokens, engine.cache.max_tokens, max_batch):
         stats.batches += 1
         live = list(batch)
@@ -85,6 +91,10 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int,
         try:
             entries = [(seqs[i], list(prompts[i]), [len(prompts[i]) - 1]) for i in live]
             stats.prefill_tokens += sum(len(prompts[i]) for i in live)
+            if ahead:
+                _decode_ahead(engine, entries, live, seqs, outputs, max_new_tokens, stops, pick_async,
+                              on_token, stats, check_errors)
+                continue
             first = True
             while live:
                 logits = engine.step(entries)
@@ -112,3 +122,56 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int,
             for s in seqs.values():
                 engine.close(s)
     return outputs
+
+
+def _decode_ahead(engine, entries, live, seqs, outputs, max_new_tokens, stops, pick_async, on_token,
+                  stats, check_errors) -> None:
+    """One batch, the device kept one step ahead of the host.
+
+    The ids a step picks stay on the device and feed the next step at once; the
+    host reads them, an event behind, while that next step already runs.  So
+    when a request picks a stop token the host learns of it one step late: that
+    step carried the request's row for nothing, its pick is dropped, and its
+    slot is given back only after the step has finished with its pages.
+    Requests that end by count are known in time and never ride along.  The
+    tokens returned are the same as the loop that waits for every step gives."""
+    logits = engine.step(entries)
+    pending = pick_async(logits, live, [len(outputs[i]) for i in live])
+    ended: set = set()  # picked a stop token; their row may still be in flight
+    first = True
+    while live:
+        # who goes on, as far as the host knows: not ended, and not at its count
+        # once the pending token has arrived
+        goes_on = [i for i in live if i not in ended and len(outputs[i]) + 1 < max_new_tokens]
+        next_pending = None
+        if goes_on:
+            if len(goes_on) == len(live):
+                tokens_dev = pending.dev
+            else:
+                at = {i: r for r, i in enumerate(live)}
+                tokens_dev = pending.dev[[at[i] for i in goes_on]]
+            logits = engine.step_decode([seqs[i] for i in goes_on], tokens_dev)
+            next_pending = pick_async(logits, goes_on, [len(outputs[i]) + 1 for i in goes_on])
+        ids = pending.wait()  # the step that picked them is over: the rows it carried are free
+        if first or stats.decode_steps % 64 == 0:
+            check_errors()
+        if not first and any(i not in ended for i in live):
+            stats.decode_steps += 1  # a step that carried only ended requests is not counted
+        first = False
+        for i, tok in zip(live, ids):
+            if i in ended:  # rode along after its stop token: give the slot back now
+                engine.close(seqs.pop(i))
+                continue
+            tok = int(tok)
+            outputs[i].append(tok)
+            stats.decode_tokens += 0 if len(outputs[i]) == 1 else 1
+            if on_token is not None:
+                on_token(i, tok)
+            if len(outputs[i]) >= max_new_tokens or tok in stops:
+                if i in goes_on:
+                    ended.add(i)  # its row is in the step now running
+                else:
+                    engine.close(seqs.pop(i))
+        live = goes_on
+        pending = next_pending
+    check_errors()

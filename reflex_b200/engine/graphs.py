@@ -31,9 +31,14 @@ class DecodeGraph:
         self.calls = 0
         self.kernels = 0
 
-    def run(self, tokens, slots, starts, want) -> torch.Tensor:
+    def run(self, tokens, slots, starts, want, tokens_dev=None) -> torch.Tensor:
+        """`tokens_dev` (int32 [n] on the device), when given, takes the place of
+        the host `tokens`: it is copied over the descriptor's token field on the
+        stream, after the descriptor itself."""
         eng = self.engine
         batch = make_batch(tokens, slots, starts, want, eng.device, buffer=self.buffer, staging=eng.staging)
+        if tokens_dev is not None:
+            batch.tokens.copy_(tokens_dev)
         batch.context_hint = self.context_hint
         if self.graph is None:
             # the first decode steps of a batch size run eagerly: they size every

@@ -109,8 +109,46 @@ class Engine:
         self.steps_run += 1
         return logits
 
+    def step_decode(self, seqs: Sequence[int], tokens_dev: torch.Tensor) -> torch.Tensor:
+        """One decode step whose tokens are already on the device: sequence
+        `seqs[i]` goes on by token `tokens_dev[i]` (int32), and the logits of
+        every row come back, float32 [len(seqs), vocab].  Nothing waits for the
+        host, so a caller can enqueue the step while it is still reading the
+        ids that feed it (the generation loop does).  The ids must be valid
+        token ids: ids picked from this model's logits are."""
+        n = len(seqs)
+        if n == 0:
+            raise InvalidInput("a step needs at least one sequence")
+        if len(set(int(s) for s in seqs)) != n:
+            raise InvalidInput("a sequence appears twice in one step")
+        if tokens_dev.dtype != torch.int32 or tokens_dev.numel() != n or not tokens_dev.is_cuda:
+            raise InvalidInput(f"step_decode needs {n} int32 token ids on the device")
+        cache = self.cache
+        slots = [int(s) for s in seqs]
+        starts = [cache.length(s) for s in slots]
+        tokens = [[0]] * n  # placeholders: the token field is overwritten on the device
+        want = [[0]] * n
+        growth = [(s, 1) for s in slots]
+        before = [[g.end[s] for s in slots] for g in cache.kv_groups]
+        cache.reserve(growth)
+        try:
+            if self.use_graphs:
+                logits = self._decode_graphed(tokens, slots, starts, want, tokens_dev=tokens_dev)
+            else:
+                batch = make_batch(tokens, slots, starts, want, self.device, staging=self.staging)
+                batch.tokens.copy_(tokens_dev)
+                logits = self.model.forward(batch, cache)
+        except Exception:
+            for g, ends in zip(cache.kv_groups, before):
+                for s, e in zip(slots, ends):
+                    g.shrink_to(s, e)
+            raise
+        cache.commit(growth)
+        self.steps_run += 1
+        return logits
+
     # --- decode steps as CUDA graphs -----------------------------------------
-    def _decode_graphed(self, tokens, slots, starts, want) -> torch.Tensor:
+    def _decode_graphed(self, tokens, slots, starts, want, tokens_dev=None) -> torch.Tensor:
         from .graphs import DecodeGraph
 
         n = len(tokens)
@@ -123,7 +161,7 @@ class Engine:
         if g is None:
             g = DecodeGraph(self, n, bucket)
             self._graphs[key] = g
-        return g.run(tokens, slots, starts, want)
+        return g.run(tokens, slots, starts, want, tokens_dev=tokens_dev)
 
     def launches_per_decode_step(self, n_seqs: int) -> int:
         """This library's kernels in one decode step of `n_seqs` sequences

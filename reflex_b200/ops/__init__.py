@@ -516,12 +516,14 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None,
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
            top_k: Optional[torch.Tensor] = None, top_p: Optional[torch.Tensor] = None,
-           scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+           scratch: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     B, V = logits.shape
     _chk(logits, "logits", torch.float32)
     if scratch is None:
         scratch = torch.empty((B, V), dtype=torch.float32, device=logits.device)
-    out = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    if out is None:
+        out = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    _chk(out, "out", torch.int32)
     st = native.lib().rfx_sample(
         logits.data_ptr(), V, B, V, _chk(temperature, "temperature", torch.float32),
         _chk(top_k, "top_k", torch.int32), _chk(top_p, "top_p", torch.float32),

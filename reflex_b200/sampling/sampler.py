@@ -10,6 +10,18 @@ from .. import ops
 from .params import SamplingParams, fresh_seed, uniform
 
 
+class PendingIds:
+    """Ids picked on the device and on their way to the host: `dev` (int32 [n])
+    can feed the next step at once; `wait()` gives the host list."""
+
+    def __init__(self, dev: torch.Tensor, host: torch.Tensor, event):
+        self.dev, self.host, self.event = dev, host, event
+
+    def wait(self) -> List[int]:
+        self.event.synchronize()
+        return self.host.tolist()
+
+
 class Sampler:
     """One generation call's chooser: greedy argmax, or temperature / top-k /
     top-p with counter-based uniforms keyed by (seed, request, step)."""
@@ -21,7 +33,7 @@ class Sampler:
         self.seed = params.seed if params.seed is not None else fresh_seed()
         self._const = {}
         self._scratch = None
-        self._greedy = {}  # batch size -> (ids, scratch) reused by every greedy pick
+        self._rings = {}  # batch size -> ring of pick buffers
 
     def _constants(self, n: int):
         if n not in self._const:
@@ -33,19 +45,40 @@ class Sampler:
             self._const[n] = (t, k, tp)
         return self._const[n]
 
+    RING = 3  # picks in flight at most: the one being read and the one feeding the next step
+
+    def _slot(self, n: int):
+        """(ids on the device, argmax scratch, pinned host ids, event) for the
+        next pick of n rows, from a small ring per batch size."""
+        ring = self._rings.setdefault(n, {"next": 0, "slots": [None] * self.RING})
+        i = ring["next"]
+        ring["next"] = (i + 1) % self.RING
+        if ring["slots"][i] is None:
+            ring["slots"][i] = (torch.empty((n,), dtype=torch.int32, device=self.device),
+                                torch.empty((n * 128,), dtype=torch.float32, device=self.device),
+                                torch.empty((n,), dtype=torch.int32, pin_memory=True),
+                                torch.cuda.Event())
+        return ring["slots"][i]
+
+    def pick_async(self, logits: torch.Tensor, requests: Sequence[int], steps: Sequence[int]) -> PendingIds:
+        """As `pick`, without waiting: the ids stay on the device for the next
+        step and travel to the host behind an event."""
+        n, V = logits.shape
+        dev, scratch, host, event = self._slot(n)
+        if self.params.is_greedy():
+            ops.argmax(logits, out=dev, scratch=scratch)
+        else:
+            u = torch.tensor([uniform(self.seed, r, s) for r, s in zip(requests, steps)],
+                             dtype=torch.float32).to(self.device)
+            t, k, tp = self._constants(n)
+            if self._scratch is None or self._scratch.shape[0] < n or self._scratch.shape[1] != V:
+                self._scratch = torch.empty((n, V), dtype=torch.float32, device=self.device)
+            ops.sample(logits, t, u, top_k=k, top_p=tp, scratch=self._scratch[:n], out=dev)
+        host.copy_(dev, non_blocking=True)
+        event.record()
+        return PendingIds(dev, host, event)
+
     def pick(self, logits: torch.Tensor, requests: Sequence[int], steps: Sequence[int]) -> List[int]:
         """logits [n, V] for the given requests, each at its own step count;
         returns the chosen ids on the host."""
-        n, V = logits.shape
-        if self.params.is_greedy():
-            if n not in self._greedy:
-                self._greedy[n] = (torch.empty((n,), dtype=torch.int32, device=self.device),
-                                   torch.empty((n * 128,), dtype=torch.float32, device=self.device))
-            out, scratch = self._greedy[n]
-            return ops.argmax(logits, out=out, scratch=scratch).tolist()
-        u = torch.tensor([uniform(self.seed, r, s) for r, s in zip(requests, steps)],
-                         dtype=torch.float32).to(self.device)
-        t, k, tp = self._constants(n)
-        if self._scratch is None or self._scratch.shape[0] < n or self._scratch.shape[1] != V:
-            self._scratch = torch.empty((n, V), dtype=torch.float32, device=self.device)
-        return ops.sample(logits, t, u, top_k=k, top_p=tp, scratch=self._scratch[:n]).tolist()
+        return self.pick_async(logits, requests, steps).wait()

@@ -137,3 +137,70 @@ def test_uniform_depends_only_on_seed_request_step():
     assert len(set(a)) > 190
     assert abs(sum(a) / len(a) - 0.5) < 0.08
     assert uniform(2, 0, 0) != uniform(1, 0, 0)
+
+
+# ---- the loop that keeps the device one step ahead of the host ---------------
+
+
+class AheadEngine(FakeEngine):
+    """Adds `step_decode`, and checks what the ahead loop must respect: a slot
+    is never given back while a step that carries its row is still 'running'
+    (here: until the pick made from that step's logits has been waited for)."""
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.in_flight = []  # slots of steps whose picks have not been waited for
+
+    def step(self, entries):
+        self.in_flight.append([s for s, _, _ in entries])
+        return super().step(entries)
+
+    def step_decode(self, seqs, tokens_dev):
+        toks = [int(t) for t in tokens_dev]
+        assert len(toks) == len(seqs)
+        return self.step([(s, [t], [0]) for s, t in zip(seqs, toks)])
+
+    def close(self, s):
+        assert all(s not in slots for slots in self.in_flight), "slot freed under a running step"
+        super().close(s)
+
+
+class FakePending:
+    def __init__(self, engine, ids):
+        self.engine, self.dev, self.ids = engine, torch.tensor(ids, dtype=torch.int32), ids
+
+    def wait(self):
+        self.engine.in_flight.pop(0)  # picks are waited for in order: the oldest step is over
+        return list(self.ids)
+
+
+def ahead_pick(engine):
+    return lambda logits, requests, steps: FakePending(engine, logits.argmax(dim=1).tolist())
+
+
+@pytest.mark.parametrize("prompts,n,stops", [
+    ([[3, 4, 5], [10]], 4, []),
+    ([[1], [20], [30]], 10, [3, 21]),
+    ([[1], [20], [30]], 1, []),
+    ([[5], [6], [7], [8], [9]], 6, [8, 9, 12]),
+    ([[40], [41]], 7, [44, 45]),  # both end on the same step by stop tokens
+])
+def test_the_ahead_loop_returns_the_same_tokens_and_frees_everything(prompts, n, stops):
+    plain = FakeEngine(max_slots=3)
+    want_stats = GenerationStats()
+    want = generate(plain, prompts, n, greedy, stop_token_ids=stops, max_batch=3, stats=want_stats)
+    e = AheadEngine(max_slots=3)
+    stats = GenerationStats()
+    seen = []
+    got = generate(e, prompts, n, greedy, stop_token_ids=stops, max_batch=3, stats=stats,
+                   pick_async=ahead_pick(e), on_token=lambda i, t: seen.append((i, t)))
+    assert got == want
+    assert sorted(seen) == sorted((i, t) for i, out in enumerate(want) for t in out)
+    assert e.cache.slots.held_count == 0 and all(g.pool.held_count == 0 for g in e.cache.kv_groups)
+    assert not e.in_flight
+    assert (stats.prefill_tokens, stats.decode_tokens, stats.batches) == \
+        (want_stats.prefill_tokens, want_stats.decode_tokens, want_stats.batches)
+    assert stats.decode_steps == want_stats.decode_steps
+    # a request that picked a stop token rides along for at most one more step
+    assert sum(len(st) for st in plain.steps) <= sum(len(st) for st in e.steps) \
+        <= sum(len(st) for st in plain.steps) + len(prompts)

@@ -13,6 +13,8 @@
 // kernel combines the splits in split order
 // (src/kernels_cuda/attention_online.cu:51-78).  Softmax runs in 32-bit on
 // base-2 exponentials: p = 2^((s - m) * scale * log2 e).
+#include <cooperative_groups.h>
+
 #include <mutex>
 
 #include "attn_mma.cuh"
@@ -22,12 +24,14 @@
 
 namespace {
 
+namespace cg = cooperative_groups;
 using namespace attn;
 using rfx::PagedKV;
 
 constexpr int PAGE = 64;
 constexpr int DEC_THREADS = 128;
 constexpr int DEC_STAGES = 3;  // pages in flight per CTA
+constexpr int MAX_RANKS = 8;   // portable cluster size
 
 template <int D>
 __global__ void __launch_bounds__(DEC_THREADS)
@@ -35,12 +39,17 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const __nv_bfloat16* __restrict__ v_pages, PagedKV cache,
                         const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                         __nv_bfloat16* __restrict__ out, float* __restrict__ partial, int nq,
-                        int n_htiles, int n_splits, int window, float scale_log2) {
+                        int n_htiles, int n_splits, int window, float scale_log2, int cluster_merge,
+                        int tile_heads) {
     constexpr int LD = D + 8;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [16][LD]
     __nv_bfloat16* kbuf = qs + 16 * LD;                               // [STAGES][PAGE][LD]
     __nv_bfloat16* vbuf = kbuf + DEC_STAGES * PAGE * LD;              // [STAGES][PAGE][LD]
+    // with the splits merged inside a cluster: what the other ranks send
+    float* recv_m = reinterpret_cast<float*>(vbuf + DEC_STAGES * PAGE * LD);  // [ranks][16]
+    float* recv_l = recv_m + MAX_RANKS * 16;                                  // [ranks][16]
+    float* recv_a = recv_l + MAX_RANKS * 16;                                  // [ranks][slice]
 
     rfx::pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -171,7 +180,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         }
     }
     __syncthreads();
-    for (int i = tid; i < nh * D; i += DEC_THREADS) {
+    const int total = nh * D;
+    const int slice = (total + n_splits - 1) / n_splits;  // elements of the tile's output a rank merges
+    for (int i = tid; i < total; i += DEC_THREADS) {
         const int row = i / D, e = i % D;
         float M = -INFINITY;
 #pragma unroll
@@ -188,15 +199,50 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         const size_t head = (size_t)r * nq + h0 + row;
         if (n_splits == 1) {
             out[head * D + e] = __float2bfloat16_rn(A / L);
-        } else {
+        } else if (!cluster_merge) {
             float* p = partial + (head * n_splits + split) * (D + 2);
             p[e] = A;
             if (e == 0) {
                 p[D] = M;
                 p[D + 1] = L;
             }
+        } else {
+            // element i of the tile's output belongs to rank i / slice: send the
+            // partial there, and its (max, sum) to every rank
+            cg::cluster_group cluster = cg::this_cluster();
+            const int owner = i / slice, off = i % slice;
+            cluster.map_shared_rank(recv_a, owner)[(size_t)split * slice + off] = A;
+            if (e == 0) {
+                for (int dst = 0; dst < n_splits; ++dst) {
+                    cluster.map_shared_rank(recv_m, dst)[split * 16 + row] = M;
+                    cluster.map_shared_rank(recv_l, dst)[split * 16 + row] = L;
+                }
+            }
         }
     }
+    if (n_splits > 1 && cluster_merge) {
+        // One cluster barrier, then every rank merges its slice in rank order with
+        // the combine kernel's arithmetic (the same bits) and writes it.  Nobody
+        // reads another rank's memory after the barrier.
+        cg::this_cluster().sync();
+        for (int off = tid; off < slice; off += DEC_THREADS) {
+            const int i = split * slice + off;
+            if (i >= total) break;
+            const int row = i / D, e = i % D;
+            float M = -INFINITY;
+            for (int sidx = 0; sidx < n_splits; ++sidx) M = fmaxf(M, recv_m[sidx * 16 + row]);
+            float L = 0.0f, A = 0.0f;
+            for (int sidx = 0; sidx < n_splits; ++sidx) {
+                const float ms = recv_m[sidx * 16 + row];
+                const float f = ms == -INFINITY ? 0.0f : exp2f(ms - M);
+                L = __fadd_rn(L, __fmul_rn(recv_l[sidx * 16 + row], f));
+                A += recv_a[(size_t)sidx * slice + off] * f;
+            }
+            const float inv = 1.0f / L;
+            out[((size_t)r * nq + h0 + row) * D + e] = __float2bfloat16_rn(A * inv);
+        }
+    }
+    (void)tile_heads;
 }
 
 // out[head] = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in order.
@@ -257,25 +303,57 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial,
 template <int D>
 int launch_decode(const void* q, const void* k_pages, const void* v_pages, const PagedKV& cache,
                   const int* row_pos, const int* row_slot, void* out, float* partial, int R, int nq,
-                  int n_splits, int window, float scale, cudaStream_t s) {
+                  int n_splits, int window, float scale, int cluster_merge, cudaStream_t s) {
     constexpr int LD = D + 8;
     const int g = nq / cache.n_kv_heads;
     const int n_htiles = (g + 15) / 16;
+    const int tile_heads = g < 16 ? g : 16;
     size_t smem = (size_t)(16 + 2 * DEC_STAGES * PAGE) * LD * 2;
     const size_t red = (size_t)(4 * 16 * D + 2 * 4 * 16) * 4;
     if (red > (size_t)2 * DEC_STAGES * PAGE * LD * 2) return RFX_ERR_UNSUPPORTED;
+    if (cluster_merge) {
+        smem += (size_t)(2 * MAX_RANKS * 16 + tile_heads * D) * 4;
+        if (smem > 227 * 1024) return RFX_ERR_UNSUPPORTED;
+    }
     auto kernel = attention_decode_kernel<D>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(R, cache.n_kv_heads * n_htiles, n_splits);
-    RFX_LAUNCH(kernel, grid, DEC_THREADS, smem, s, (const __nv_bfloat16*)q,
-               (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, cache, row_pos, row_slot,
-               (__nv_bfloat16*)out, partial, nq, n_htiles, n_splits, window,
-               scale * 1.4426950408889634f);
-    if (n_splits > 1)
+    e = rfx::launch(kernel, grid, dim3(DEC_THREADS), smem, s, cluster_merge ? n_splits : 1,
+                    (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
+                    cache, row_pos, row_slot, (__nv_bfloat16*)out, partial, nq, n_htiles, n_splits, window,
+                    scale * 1.4426950408889634f, cluster_merge, tile_heads);
+    if (e != cudaSuccess) return (int)e;
+    if (n_splits > 1 && !cluster_merge)
         RFX_LAUNCH(attention_combine_kernel, R * nq, D <= 128 ? 64 : 128, 0, s, (const float*)partial,
                    (__nv_bfloat16*)out, D, n_splits);
     return 0;
+}
+
+int decode_entry(const void* q, const void* k_pages, const void* v_pages, const int* page_table,
+                 int max_pages, int page_size, const int* row_pos, const int* row_slot, void* out,
+                 float* partial, int R, int nq, int nkv, int head_dim, int n_splits, int window,
+                 float scale, int cluster_merge, void* stream) {
+    if (R <= 0) return 0;
+    if (page_size != PAGE || nkv <= 0 || nq % nkv != 0 || n_splits < 1) return RFX_ERR_BAD_ARG;
+    if (n_splits > 1 && !partial && !cluster_merge) return RFX_ERR_BAD_ARG;
+    if (cluster_merge && n_splits != 2 && n_splits != 4 && n_splits != 8) return RFX_ERR_UNSUPPORTED;
+    if (n_splits > MAX_SPLITS) return RFX_ERR_UNSUPPORTED;
+    if (n_splits > 65535 || (long long)nkv * ((nq / nkv + 15) / 16) > 65535) return RFX_ERR_UNSUPPORTED;
+    PagedKV cache{page_table, max_pages, page_size, nkv, head_dim};
+    cudaStream_t s = (cudaStream_t)stream;
+#define RFX_CASE(DD)                                                                            \
+    case DD:                                                                                    \
+        return launch_decode<DD>(q, k_pages, v_pages, cache, row_pos, row_slot, out, partial, R, \
+                                 nq, n_splits, window, scale, cluster_merge, s);
+    switch (head_dim) {
+        RFX_CASE(16) RFX_CASE(32) RFX_CASE(48) RFX_CASE(64) RFX_CASE(80) RFX_CASE(96)
+        RFX_CASE(112) RFX_CASE(128) RFX_CASE(144) RFX_CASE(160) RFX_CASE(176) RFX_CASE(192)
+        RFX_CASE(208) RFX_CASE(224) RFX_CASE(240) RFX_CASE(256)
+        default:
+            return RFX_ERR_UNSUPPORTED;
+    }
+#undef RFX_CASE
 }
 
 }  // namespace
@@ -288,25 +366,23 @@ extern "C" int rfx_attention_decode(const void* q, const void* k_pages, const vo
                                     const int* row_pos, const int* row_slot, void* out,
                                     float* partial, int R, int nq, int nkv, int head_dim,
                                     int n_splits, int window, float scale, void* stream) {
-    if (R <= 0) return 0;
-    if (page_size != PAGE || nkv <= 0 || nq % nkv != 0 || n_splits < 1) return RFX_ERR_BAD_ARG;
-    if (n_splits > 1 && !partial) return RFX_ERR_BAD_ARG;
-    if (n_splits > MAX_SPLITS) return RFX_ERR_UNSUPPORTED;
-    if (n_splits > 65535 || (long long)nkv * ((nq / nkv + 15) / 16) > 65535) return RFX_ERR_UNSUPPORTED;
-    PagedKV cache{page_table, max_pages, page_size, nkv, head_dim};
-    cudaStream_t s = (cudaStream_t)stream;
-#define RFX_CASE(DD)                                                                            \
-    case DD:                                                                                    \
-        return launch_decode<DD>(q, k_pages, v_pages, cache, row_pos, row_slot, out, partial, R, \
-                                 nq, n_splits, window, scale, s);
-    switch (head_dim) {
-        RFX_CASE(16) RFX_CASE(32) RFX_CASE(48) RFX_CASE(64) RFX_CASE(80) RFX_CASE(96)
-        RFX_CASE(112) RFX_CASE(128) RFX_CASE(144) RFX_CASE(160) RFX_CASE(176) RFX_CASE(192)
-        RFX_CASE(208) RFX_CASE(224) RFX_CASE(240) RFX_CASE(256)
-        default:
-            return RFX_ERR_UNSUPPORTED;
-    }
-#undef RFX_CASE
+    return decode_entry(q, k_pages, v_pages, page_table, max_pages, page_size, row_pos, row_slot, out,
+                        partial, R, nq, nkv, head_dim, n_splits, window, scale, 0, stream);
+}
+
+// The same with 2, 4 or 8 splits that form a thread-block cluster: every rank
+// sends its partial to the rank that owns that slice of the output over
+// distributed shared memory, one cluster barrier, and the owners merge in rank
+// order with the combine kernel's arithmetic.  No scratch, no second kernel.
+// RFX_ERR_UNSUPPORTED for other split counts or sizes that leave no shared
+// memory for the exchange: the caller then takes the entry point above.
+extern "C" int rfx_attention_decode_cluster(const void* q, const void* k_pages, const void* v_pages,
+                                            const int* page_table, int max_pages, int page_size,
+                                            const int* row_pos, const int* row_slot, void* out, int R,
+                                            int nq, int nkv, int head_dim, int n_splits, int window,
+                                            float scale, void* stream) {
+    return decode_entry(q, k_pages, v_pages, page_table, max_pages, page_size, row_pos, row_slot, out,
+                        nullptr, R, nq, nkv, head_dim, n_splits, window, scale, 1, stream);
 }
 
 // ---------------------------------------------------------------------------

@@ -367,6 +367,16 @@ def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_sl
         raise InvalidInput(f"attention_decode takes head_dim in steps of 16 up to 256, got {head_dim}")
     n_splits = n_splits or decode_splits(R, nq, nkv)
     out = torch.empty_like(q)
+    if CLUSTER_MERGE and n_splits in (2, 4, 8):
+        # the splits as one thread-block cluster that merges its partials itself
+        st = native.lib().rfx_attention_decode_cluster(
+            q.data_ptr(), _chk(k_pages, "k_pages", torch.bfloat16), _chk(v_pages, "v_pages", torch.bfloat16),
+            _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
+            _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32), out.data_ptr(),
+            R, nq, nkv, head_dim, n_splits, int(window or 0), float(scale), _stream())
+        if st != native.ERR_UNSUPPORTED:
+            native.check(st, f"attention_decode_cluster (head_dim={head_dim}, splits={n_splits})")
+            return out
     partial = (torch.empty((R * nq * n_splits * (head_dim + 2),), dtype=torch.float32, device=q.device)
                if n_splits > 1 else None)
     st = native.lib().rfx_attention_decode(
@@ -377,6 +387,9 @@ def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_sl
         int(window or 0), float(scale), _stream())
     native.check(st, f"attention_decode (head_dim={head_dim}, splits={n_splits})")
     return out
+
+
+CLUSTER_MERGE = _os.environ.get("REFLEX_B200_CLUSTER_MERGE", "1") != "0"
 
 
 def fused_decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int) -> int:

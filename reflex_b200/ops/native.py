@@ -39,6 +39,8 @@ _SIGNATURES = {
                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "rfx_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "rfx_attention_decode_cluster": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "rfx_attention_decode_fused": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p,
                                    c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
@@ -94,6 +96,9 @@ def register_signature(name: str, argtypes) -> None:
 
 
 LAUNCHES = 0  # kernels of this library launched (or captured into a graph) so far
+
+
+ERR_UNSUPPORTED = -2  # a kernel's answer for sizes it does not take
 
 
 def check(status: int, what: str) -> None:

@@ -340,7 +340,8 @@ def decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int = 64) -> int:
     grows with the splits) and buys parallelism; fitted to step times on a B200
     at batches of 1 to 64 and contexts of 512 to 16,000: about 4 us fixed per
     launch, 0.8 us per page a CTA walks plus 1.5 us per CTA, CTAs in whole waves
-    of two per SM, 3 us + 0.25 us a split for the partials, the combine and its hand-off.  The
+    of two per SM; for the merge 2 us + 0.1 us a split inside a cluster (up to 8
+    splits), 3 us + 0.25 us a split through the combine kernel.  The
     smallest estimate wins."""
     forced = int(_os.environ.get("REFLEX_B200_DECODE_SPLITS", "0"))  # tuning aid
     if forced > 0:
@@ -351,7 +352,8 @@ def decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int = 64) -> int:
         if s > max(1, max_pages):
             break
         waves = -(-ctas * s // (2 * SM_COUNT))
-        cost = 4.0 + (-(-max_pages // s) * 0.8 + 1.5) * waves + (3.0 + 0.25 * s if s > 1 else 0.0)
+        merge = 0.0 if s == 1 else (2.0 + 0.1 * s if s <= 8 else 3.0 + 0.25 * s)
+        cost = 4.0 + (-(-max_pages // s) * 0.8 + 1.5) * waves + merge
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best

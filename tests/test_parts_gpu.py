@@ -215,3 +215,124 @@ def test_a_toy_mixer_with_state_of_its_own():
     for r, g in zip(reqs, got):
         assert helpers.rel_err(g, plain(r)) < 1e-5
     assert eng.cache.slots.held_count == 0
+
+
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding():
+    """Two more parts registered from here and chosen layer by layer: a
+    feed-forward that routes each row to its best expert of three (router in
+    32-bit), and a rotary encoding whose positions are divided by a factor.
+    Layer 0 uses both with windowed attention, layer 1 the library's own parts:
+    one model, different mixers' options and feed-forwards in different layers."""
+    from reflex_b200.config.spec import (FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec,
+                                         PositionSpec)
+    from reflex_b200.engine import CausalLM, Engine
+    from reflex_b200.parts import TensorInfo, register_feed_forward, register_position
+    from reflex_b200.weights import random_tensors
+
+    @register_feed_forward("toy_routed")
+    class ToyRouted:
+        def __init__(self, spec, dtype, device):
+            self.spec, self.dtype, self.device = spec, dtype, device
+            self.n_experts = dict(spec.params)["experts"]
+
+        @classmethod
+        def tensor_specs(cls, spec):
+            E, H, I = dict(spec.params)["experts"], spec.hidden_size, spec.intermediate_size
+            return {"router": TensorInfo((E, H), "matrix"), "w_in": TensorInfo((E * I, H), "matrix"),
+                    "w_out": TensorInfo((E * H, I), "matrix")}
+
+        def bind(self, tensors):
+            E, H, I = self.n_experts, self.spec.hidden_size, self.spec.intermediate_size
+            self.router = tensors["router"].to(self.device, torch.float32)
+            self.w_in = tensors["w_in"].to(self.device, torch.float32).reshape(E, I, H)
+            self.w_out = tensors["w_out"].to(self.device, torch.float32).reshape(E, H, I)
+
+        def forward(self, x):
+            xf = x.float()
+            pick = (xf @ self.router.T).argmax(dim=1)  # router logits and choice in 32-bit
+            out = torch.zeros((x.shape[0], self.spec.hidden_size), dtype=torch.float32, device=x.device)
+            for e in range(self.n_experts):  # experts in a fixed order
+                rows = (pick == e).nonzero()[:, 0]
+                if rows.numel():
+                    out[rows] = torch.relu(xf[rows] @ self.w_in[e].T) @ self.w_out[e].T
+            return out
+
+    @register_position("toy_rope_divided")
+    class ToyDividedRope:
+        """NeoX pairs; angle = (position / factor) / theta^(2i/d)."""
+
+        def __init__(self, spec, dtype, device):
+            self.spec = spec
+            factor = dict(spec.params)["factor"]
+            half = spec.rotary_dim // 2
+            exps = torch.arange(half, dtype=torch.float64) * 2.0 / spec.rotary_dim
+            self.denominators = (torch.pow(torch.tensor(spec.theta, dtype=torch.float64), exps) * factor).float().to(device)
+
+        @classmethod
+        def tensor_specs(cls, spec):
+            return {}
+
+        def bind(self, tensors):
+            pass
+
+        def rotation(self):
+            return self.denominators, self.spec.rotary_dim
+
+    H, V, nq, nkv, d, I, E = 48, 101, 3, 1, 32, 40, 3
+    theta, factor, window, eps = 1e4, 4.0, 9, 1e-5
+    names = (("q_proj", "att.q"), ("k_proj", "att.k"), ("v_proj", "att.v"), ("o_proj", "att.o"),
+             ("q_norm", "att.qn"), ("k_norm", "att.kn"))
+
+    def mixer(position_kind, params, win):
+        return MixerSpec("gqa_attention", hidden_size=H, num_heads=nq, num_kv_heads=nkv, head_dim=d,
+                         scale=d ** -0.5, window=win, qk_norm=NormSpec("rmsnorm", d, eps),
+                         position=PositionSpec(position_kind, d, d, theta, params=params), names=names)
+
+    routed = FeedForwardSpec("toy_routed", H, I, names=(("router", "moe.r"), ("w_in", "moe.i"), ("w_out", "moe.o")),
+                             params=(("experts", E),))
+    dense = FeedForwardSpec("swiglu", H, 56, names=(("gate_proj", "ff.g"), ("up_proj", "ff.u"), ("down_proj", "ff.d")))
+    norm = NormSpec("rmsnorm", H, eps)
+    lnames = (("mixer_norm", "n1"), ("feed_forward_norm", "n2"))
+    layers = [LayerSpec("prenorm", "blocks.0.", mixer("toy_rope_divided", (("factor", factor),), window), routed, norm, norm, names=lnames),
+              LayerSpec("prenorm", "blocks.1.", mixer("rope_neox", (), None), dense, norm, norm, names=lnames)]
+    spec = ModelSpec("toy2", V, H, layers, norm, tie_word_embeddings=False, max_positions=256,
+                     embedding_name="emb", final_norm_name="fn", head_name="head")
+    model = CausalLM(spec, torch.float32, DEV)
+    tensors = dict(random_tensors(spec, 3, torch.float32))
+    # spread the router so that choices are clear of ties
+    tensors["blocks.0.moe.r"] = tensors["blocks.0.moe.r"] * 50
+    model.bind(tensors)
+    eng = Engine(model, max_tokens=512)
+    assert len(eng.cache.kv_groups) == 2  # a windowed group and a full one, storage of their own
+
+    w = {k: v.double().numpy() for k, v in tensors.items()}
+
+    def attention(h, p, positions, win):
+        T = h.shape[0]
+        x = pm.rms_norm(h, w[p + "n1"], eps)
+        q = pm.rms_norm((x @ w[p + "att.q"].T).reshape(T, nq, d), w[p + "att.qn"], eps)
+        k = pm.rms_norm((x @ w[p + "att.k"].T).reshape(T, nkv, d), w[p + "att.kn"], eps)
+        v = (x @ w[p + "att.v"].T).reshape(T, nkv, d)
+        q, k = pm.rope_neox(q, positions, theta, d), pm.rope_neox(k, positions, theta, d)
+        return h + pm.causal_attention(q, k, v, d ** -0.5, win).reshape(T, nq * d) @ w[p + "att.o"].T
+
+    def plain(tokens):
+        T = len(tokens)
+        h = w["emb"][np.array(tokens)]
+        h = attention(h, "blocks.0.", np.arange(T) / factor, window)
+        x = pm.rms_norm(h, w["blocks.0.n2"], eps)
+        pick = (x @ w["blocks.0.moe.r"].T).argmax(axis=1)
+        w_in, w_out = w["blocks.0.moe.i"].reshape(E, I, H), w["blocks.0.moe.o"].reshape(E, H, I)
+        h = h + np.stack([np.maximum(x[t] @ w_in[pick[t]].T, 0) @ w_out[pick[t]].T for t in range(T)])
+        h = attention(h, "blocks.1.", np.arange(T), None)
+        x = pm.rms_norm(h, w["blocks.1.n2"], eps)
+        h = h + pm.swiglu(x, w["blocks.1.ff.g"], w["blocks.1.ff.u"], w["blocks.1.ff.d"])
+        return pm.rms_norm(h, w["fn"], eps) @ w["head"].T
+
+    reqs = [helpers.random_tokens(n, V, n) for n in (23, 5, 40, 12)]
+    got = helpers.run_batches(eng, reqs, 2, [6, 3, 1])
+    for r, g in zip(reqs, got):
+        assert helpers.rel_err(g, plain(r)) < 2e-5
+    whole = helpers.run_whole(eng, reqs[2])
+    assert helpers.rel_err(whole, plain(reqs[2])) < 2e-5
+    assert eng.cache.slots.held_count == 0

@@ -1,16 +1,18 @@
 // Decode attention on tensor cores: one query position per row, split over
 // the keys.
 //
-// A CTA serves one (row, kv head, tile of up to 16 query heads of that kv
-// head's group, split of the key range).  The query heads that share the kv
-// head are the 16 rows of the MMA tile, so each K/V page is read once for the
-// whole group (the reference's decode kernel does the same with CUDA cores:
+// A CTA serves one (row, kv head, tile of up to 8 query heads of that kv
+// head's group, split of the key range).  The keys are the rows of the MMA
+// tiles and the query heads that share the kv head its 8 columns
+// (attn_mma.cuh: attend_keys16), so each K/V page is read once for the whole
+// group (the reference's decode kernel does the same with CUDA cores:
 // src/kernels_cuda/attention_decode.cuh:34-176).  Pages of 64 keys stream
-// through a double-buffered pair of shared-memory tiles; warp w takes keys
+// through a three-stage ring of shared-memory tiles; warp w takes keys
 // [16 w, 16 w + 16) of every page with its own running (max, sum, acc), and
-// the four warps are merged at the end.  With more than one split the CTA
-// writes an unnormalised partial (acc, max, sum) to scratch and a second
-// kernel combines the splits in split order
+// the four warps are merged at the end.  With more than one split the splits
+// either form a thread-block cluster that merges its partials over distributed
+// shared memory, or write unnormalised partials (acc, max, sum) to scratch for
+// a second kernel that combines them in split order
 // (src/kernels_cuda/attention_online.cu:51-78).  Softmax runs in 32-bit on
 // base-2 exponentials: p = 2^((s - m) * scale * log2 e).
 #include <cooperative_groups.h>
@@ -43,7 +45,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         int tile_heads) {
     constexpr int LD = D + 8;
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [16][LD]
+    __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [16][LD], rows 0..7 used
     __nv_bfloat16* kbuf = qs + 16 * LD;                               // [STAGES][PAGE][LD]
     __nv_bfloat16* vbuf = kbuf + DEC_STAGES * PAGE * LD;              // [STAGES][PAGE][LD]
     // with the splits merged inside a cluster: what the other ranks send
@@ -57,8 +59,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     const int kvh = blockIdx.y / n_htiles, ht = blockIdx.y % n_htiles;
     const int split = blockIdx.z;
     const int g = nq / cache.n_kv_heads;
-    const int h0 = kvh * g + ht * 16;
-    const int nh = min(16, g - ht * 16);
+    const int h0 = kvh * g + ht * 8;  // a tile holds up to eight query heads: the MMA's columns
+    const int nh = min(8, g - ht * 8);
     const int pos = row_pos[r], slot = row_slot[r];
     const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
     const int first_page = lo / PAGE, last_page = pos / PAGE;
@@ -76,12 +78,15 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         cp_async_commit();
     };
 
+    // this thread's heads are 2 (lane % 4) and 2 (lane % 4) + 1 (attn_mma.cuh: attend_keys16)
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
-    float acc[D / 8][4];
+    float acc[D / 16][4];
 #pragma unroll
-    for (int n = 0; n < D / 8; ++n)
+    for (int n = 0; n < D / 16; ++n)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
+    uint32_t qf[D / 16][2];
+    load_query_fragments<D>(qs, qf);  // whatever the tile holds: the dry pass only needs operands
 
     // a ring of DEC_STAGES pages: one commit group per page, empty groups past the end
     // The page id of a load is read one iteration before the load is issued, so
@@ -121,24 +126,27 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         }
         const int base = pg * PAGE;
         const int lo_eff = dry ? 0x7fffffff : lo;
-        auto visible = [&](int key, int) { return base + key >= lo_eff && base + key <= pos; };
-        attend_tile<D, 2>(qs, kbuf + buf * PAGE * LD, vbuf + buf * PAGE * LD, warp * 16, scale_log2,
-                          visible, m, l, acc);
+        auto visible = [&](int key) { return base + key >= lo_eff && base + key <= pos; };
+        attend_keys16<D>(qf, kbuf + buf * PAGE * LD, vbuf + buf * PAGE * LD, warp * 16, scale_log2, visible,
+                         m, l, acc);
         if (dry) {
             m[0] = m[1] = -INFINITY;
             l[0] = l[1] = 0.0f;
 #pragma unroll
-            for (int n = 0; n < D / 8; ++n)
+            for (int n = 0; n < D / 16; ++n)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
             rfx::pdl_wait();
             // the query heads of this tile; rows beyond the group are zero
-            for (int i = tid; i < 16 * (D / 8); i += DEC_THREADS) {
+            __syncthreads();  // every warp has read the tile for its dry pass
+            for (int i = tid; i < 8 * (D / 8); i += DEC_THREADS) {
                 const int row = i / (D / 8), c = i % (D / 8);
                 uint4 v = make_uint4(0, 0, 0, 0);
                 if (row < nh) v = *reinterpret_cast<const uint4*>(q + ((size_t)r * nq + h0 + row) * D + c * 8);
                 *reinterpret_cast<uint4*>(qs + row * LD + c * 8) = v;
             }
+            __syncthreads();
+            load_query_fragments<D>(qs, qf);
 #pragma unroll
             for (int i = 0; i < DEC_STAGES - 1; ++i) {
                 if (i >= issued) {
@@ -153,30 +161,34 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     cp_async_wait<0>();
     __syncthreads();  // all warps are done with the tiles before they are reused below
 
+    // a head's sum lies in the eight lanes that share lane % 4
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        l[j] += __shfl_xor_sync(0xffffffffu, l[j], 4);
+        l[j] += __shfl_xor_sync(0xffffffffu, l[j], 8);
+        l[j] += __shfl_xor_sync(0xffffffffu, l[j], 16);
+    }
     // merge the four warps: each holds (m, l, acc) over its quarter of the keys
-    float* red = reinterpret_cast<float*>(kbuf);       // [4][16][D] acc, then [4][16] m, [4][16] l
-    float* red_m = red + 4 * 16 * D;
-    float* red_l = red_m + 4 * 16;
+    float* red = reinterpret_cast<float*>(kbuf);  // [4][8][D] acc, then [4][8] m, [4][8] l
+    float* red_m = red + 4 * 8 * D;
+    float* red_l = red_m + 4 * 8;
     {
         const int g0 = lane >> 2, c = lane & 3;
 #pragma unroll
-        for (int n = 0; n < D / 8; ++n) {
-            float* a0 = red + ((size_t)(warp * 16 + g0) * D) + n * 8 + 2 * c;
-            float* a1 = red + ((size_t)(warp * 16 + g0 + 8) * D) + n * 8 + 2 * c;
-            if (g0 < nh) {  // rows beyond the group's heads hold nothing
-                a0[0] = acc[n][0];
-                a0[1] = acc[n][1];
+        for (int j = 0; j < 2; ++j) {
+            const int head = 2 * c + j;
+            if (head < nh) {  // columns beyond the group's heads hold nothing
+                float* dst = red + (size_t)(warp * 8 + head) * D + g0;
+#pragma unroll
+                for (int i = 0; i < D / 16; ++i) {
+                    dst[16 * i] = acc[i][j];
+                    dst[16 * i + 8] = acc[i][2 + j];
+                }
+                if (g0 == 0) {
+                    red_m[warp * 8 + head] = m[j];
+                    red_l[warp * 8 + head] = l[j];
+                }
             }
-            if (g0 + 8 < nh) {
-                a1[0] = acc[n][2];
-                a1[1] = acc[n][3];
-            }
-        }
-        if (c == 0) {
-            red_m[warp * 16 + g0] = m[0];
-            red_m[warp * 16 + g0 + 8] = m[1];
-            red_l[warp * 16 + g0] = l[0];
-            red_l[warp * 16 + g0 + 8] = l[1];
         }
     }
     __syncthreads();
@@ -186,14 +198,14 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         const int row = i / D, e = i % D;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, red_m[w * 16 + row]);
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, red_m[w * 8 + row]);
         float L = 0.0f, A = 0.0f;
         if (M != -INFINITY) {
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
-                const float f = exp2f(red_m[w * 16 + row] - M);
-                L += red_l[w * 16 + row] * f;
-                A += red[(size_t)(w * 16 + row) * D + e] * f;
+                const float f = exp2f(red_m[w * 8 + row] - M);
+                L += red_l[w * 8 + row] * f;
+                A += red[(size_t)(w * 8 + row) * D + e] * f;
             }
         }
         const size_t head = (size_t)r * nq + h0 + row;
@@ -306,8 +318,8 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
                   int n_splits, int window, float scale, int cluster_merge, cudaStream_t s) {
     constexpr int LD = D + 8;
     const int g = nq / cache.n_kv_heads;
-    const int n_htiles = (g + 15) / 16;
-    const int tile_heads = g < 16 ? g : 16;
+    const int n_htiles = (g + 7) / 8;
+    const int tile_heads = g < 8 ? g : 8;
     size_t smem = (size_t)(16 + 2 * DEC_STAGES * PAGE) * LD * 2;
     const size_t red = (size_t)(4 * 16 * D + 2 * 4 * 16) * 4;
     if (red > (size_t)2 * DEC_STAGES * PAGE * LD * 2) return RFX_ERR_UNSUPPORTED;
@@ -339,7 +351,7 @@ int decode_entry(const void* q, const void* k_pages, const void* v_pages, const 
     if (n_splits > 1 && !partial && !cluster_merge) return RFX_ERR_BAD_ARG;
     if (cluster_merge && n_splits != 2 && n_splits != 4 && n_splits != 8) return RFX_ERR_UNSUPPORTED;
     if (n_splits > MAX_SPLITS) return RFX_ERR_UNSUPPORTED;
-    if (n_splits > 65535 || (long long)nkv * ((nq / nkv + 15) / 16) > 65535) return RFX_ERR_UNSUPPORTED;
+    if (n_splits > 65535 || (long long)nkv * ((nq / nkv + 7) / 8) > 65535) return RFX_ERR_UNSUPPORTED;
     PagedKV cache{page_table, max_pages, page_size, nkv, head_dim};
     cudaStream_t s = (cudaStream_t)stream;
 #define RFX_CASE(DD)                                                                            \

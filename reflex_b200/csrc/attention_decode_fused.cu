@@ -8,7 +8,7 @@
 // combine); at one token per sequence each of them is a few microseconds of
 // launch and hand-off around almost no work, so here they are one.
 //
-// A CTA serves one (row, kv head, tile of up to 16 query heads of the group,
+// A CTA serves one (row, kv head, tile of up to 8 query heads of the group,
 // split of the key range), as in attention_decode.cu.  The splits of one
 // (row, kv head, tile) form a thread-block cluster: every rank sends its
 // unnormalised partial (acc, max, sum) to the rank that owns that slice of the
@@ -177,8 +177,8 @@ __global__ void __launch_bounds__(THREADS) attention_decode_fused_kernel(const F
     const int kvh = blockIdx.y / a.n_htiles, ht = blockIdx.y % a.n_htiles;
     const int split = blockIdx.z, n_splits = a.n_splits;
     const int g = a.nq / cache.n_kv_heads;
-    const int h0 = kvh * g + ht * 16;
-    const int nh = min(16, g - ht * 16);
+    const int h0 = kvh * g + ht * 8;  // a tile holds up to eight query heads: the MMA's columns
+    const int nh = min(8, g - ht * 8);
     const int pos = a.row_pos[r], slot = a.row_slot[r];
     const int window = a.window;
     const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
@@ -200,12 +200,15 @@ __global__ void __launch_bounds__(THREADS) attention_decode_fused_kernel(const F
         cp_async_commit();
     };
 
+    // this thread's heads are 2 (lane % 4) and 2 (lane % 4) + 1 (attn_mma.cuh: attend_keys16)
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
-    float acc[D / 8][4];
+    float acc[D / 16][4];
 #pragma unroll
-    for (int n = 0; n < D / 8; ++n)
+    for (int n = 0; n < D / 16; ++n)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
+    uint32_t qf[D / 16][2];
+    load_query_fragments<D>(qs, qf);  // whatever the tile holds: the dry pass only needs operands
 
     int pages_first[STAGES];
 #pragma unroll
@@ -237,7 +240,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_fused_kernel(const F
         wq[i] = (a.q_w && e < D) ? a.q_w[e] : 0.0f;
         wk[i] = (a.k_w && e < D) ? a.k_w[e] : 0.0f;
     }
-    for (int i = tid; i < (16 - nh) * (D / 8); i += THREADS) {
+    for (int i = tid; i < (8 - nh) * (D / 8); i += THREADS) {
         const int rr = nh + i / (D / 8), c = i % (D / 8);
         *reinterpret_cast<uint4*>(qs + rr * LD + c * 8) = make_uint4(0, 0, 0, 0);
     }
@@ -278,15 +281,15 @@ __global__ void __launch_bounds__(THREADS) attention_decode_fused_kernel(const F
         }
         const int base = pg * PAGE;
         const int lo_eff = dry ? 0x7fffffff : lo;
-        auto visible = [&](int key, int) { return base + key >= lo_eff && base + key <= pos; };
-        attend_tile<D, 2>(qs, kbuf + buf * PAGE * LD, vbuf + buf * PAGE * LD, warp * 16, a.scale_log2,
-                          visible, m, l, acc);
+        auto visible = [&](int key) { return base + key >= lo_eff && base + key <= pos; };
+        attend_keys16<D>(qf, kbuf + buf * PAGE * LD, vbuf + buf * PAGE * LD, warp * 16, a.scale_log2, visible,
+                         m, l, acc);
         if (!dry && pg - pg0 < 4) trace_mark(9 + 2 * (pg - pg0));
         if (dry) {
             m[0] = m[1] = -INFINITY;
             l[0] = l[1] = 0.0f;
 #pragma unroll
-            for (int n = 0; n < D / 8; ++n)
+            for (int n = 0; n < D / 16; ++n)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
             trace_mark(7);
@@ -296,7 +299,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_fused_kernel(const F
             // ---- this row's vectors: raw loads first, so their latency overlaps
             // tasks of the CTA: query heads 0 .. nh-1, then (tail rank) the key, the value
             const int n_tasks = nh + ((has_new && tail) ? 2 : 0);
-            constexpr int MAX_T = 5;  // (16 + 2 + 3) / 4
+            constexpr int MAX_T = 3;  // (8 + 2 + 3) / 4
             float raw[MAX_T][PER];
             const float* row = a.qkv + (size_t)r * a.row_stride;
 #pragma unroll
@@ -330,7 +333,9 @@ __global__ void __launch_bounds__(THREADS) attention_decode_fused_kernel(const F
                                    dst, lane);
                 }
             }
-            // (the next pass's __syncthreads makes qs, knew and vnew visible to all warps)
+            // (the next pass's __syncthreads makes knew and vnew visible to all warps)
+            __syncthreads();
+            load_query_fragments<D>(qs, qf);
             trace_mark(2);
 #pragma unroll
             for (int i = 0; i < STAGES - 1; ++i) {
@@ -347,30 +352,34 @@ __global__ void __launch_bounds__(THREADS) attention_decode_fused_kernel(const F
     __syncthreads();  // all warps are done with the tiles (and, with no page, qs is complete)
     trace_mark(3);
 
+    // a head's sum lies in the eight lanes that share lane % 4
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        l[j] += __shfl_xor_sync(0xffffffffu, l[j], 4);
+        l[j] += __shfl_xor_sync(0xffffffffu, l[j], 8);
+        l[j] += __shfl_xor_sync(0xffffffffu, l[j], 16);
+    }
     // merge the four warps: each holds (m, l, acc) over its quarter of the keys
-    float* red = reinterpret_cast<float*>(kbuf);  // [4][16][D] acc, then [4][16] m, [4][16] l
-    float* red_m = red + 4 * 16 * D;
-    float* red_l = red_m + 4 * 16;
+    float* red = reinterpret_cast<float*>(kbuf);  // [4][8][D] acc, then [4][8] m, [4][8] l
+    float* red_m = red + 4 * 8 * D;
+    float* red_l = red_m + 4 * 8;
     {
         const int g0 = lane >> 2, c = lane & 3;
 #pragma unroll
-        for (int n = 0; n < D / 8; ++n) {
-            float* a0 = red + ((size_t)(warp * 16 + g0) * D) + n * 8 + 2 * c;
-            float* a1 = red + ((size_t)(warp * 16 + g0 + 8) * D) + n * 8 + 2 * c;
-            if (g0 < nh) {  // rows beyond the group's heads hold nothing
-                a0[0] = acc[n][0];
-                a0[1] = acc[n][1];
+        for (int j = 0; j < 2; ++j) {
+            const int head = 2 * c + j;
+            if (head < nh) {  // columns beyond the group's heads hold nothing
+                float* dst = red + (size_t)(warp * 8 + head) * D + g0;
+#pragma unroll
+                for (int i = 0; i < D / 16; ++i) {
+                    dst[16 * i] = acc[i][j];
+                    dst[16 * i + 8] = acc[i][2 + j];
+                }
+                if (g0 == 0) {
+                    red_m[warp * 8 + head] = m[j];
+                    red_l[warp * 8 + head] = l[j];
+                }
             }
-            if (g0 + 8 < nh) {
-                a1[0] = acc[n][2];
-                a1[1] = acc[n][3];
-            }
-        }
-        if (c == 0) {
-            red_m[warp * 16 + g0] = m[0];
-            red_m[warp * 16 + g0 + 8] = m[1];
-            red_l[warp * 16 + g0] = l[0];
-            red_l[warp * 16 + g0 + 8] = l[1];
         }
     }
     __syncthreads();
@@ -381,14 +390,14 @@ __global__ void __launch_bounds__(THREADS) attention_decode_fused_kernel(const F
             const int rr = i / D, e = i % D;
             float M = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < 4; ++w) M = fmaxf(M, red_m[w * 16 + rr]);
+            for (int w = 0; w < 4; ++w) M = fmaxf(M, red_m[w * 8 + rr]);
             float L = 0.0f, A = 0.0f;
             if (M != -INFINITY) {
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
-                    const float f = exp2f(red_m[w * 16 + rr] - M);
-                    L += red_l[w * 16 + rr] * f;
-                    A += red[(size_t)(w * 16 + rr) * D + e] * f;
+                    const float f = exp2f(red_m[w * 8 + rr] - M);
+                    L += red_l[w * 8 + rr] * f;
+                    A += red[(size_t)(w * 8 + rr) * D + e] * f;
                 }
             }
             a.out[((size_t)r * a.nq + h0 + rr) * D + e] = __float2bfloat16_rn(A / L);
@@ -405,14 +414,14 @@ __global__ void __launch_bounds__(THREADS) attention_decode_fused_kernel(const F
         const int rr = i / D, e = i % D;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, red_m[w * 16 + rr]);
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, red_m[w * 8 + rr]);
         float L = 0.0f, A = 0.0f;
         if (M != -INFINITY) {
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
-                const float f = exp2f(red_m[w * 16 + rr] - M);
-                L += red_l[w * 16 + rr] * f;
-                A += red[(size_t)(w * 16 + rr) * D + e] * f;
+                const float f = exp2f(red_m[w * 8 + rr] - M);
+                L += red_l[w * 8 + rr] * f;
+                A += red[(size_t)(w * 8 + rr) * D + e] * f;
             }
         }
         const int owner = i / slice, off = i % slice;
@@ -494,7 +503,7 @@ extern "C" int rfx_attention_decode_fused(const float* qkv, int row_stride, int 
     if (nkv_in != 0 && nkv_in != nkv) return RFX_ERR_BAD_ARG;
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return RFX_ERR_BAD_ARG;
     if (row_stride < (nq + 2 * nkv_in) * head_dim) return RFX_ERR_BAD_ARG;
-    if ((long long)nkv * ((nq / nkv + 15) / 16) > 65535) return RFX_ERR_UNSUPPORTED;
+    if ((long long)nkv * ((nq / nkv + 7) / 8) > 65535) return RFX_ERR_UNSUPPORTED;
     FusedArgs a;
     a.qkv = qkv;
     a.row_stride = row_stride;
@@ -512,11 +521,11 @@ extern "C" int rfx_attention_decode_fused(const float* qkv, int row_stride, int 
     a.row_slot = row_slot;
     a.out = (__nv_bfloat16*)out;
     a.nq = nq;
-    a.n_htiles = (nq / nkv + 15) / 16;
+    a.n_htiles = (nq / nkv + 7) / 8;
     a.n_splits = n_splits;
     a.window = window;
     a.scale_log2 = scale * 1.4426950408889634f;
-    a.tile_heads = nq / nkv < 16 ? nq / nkv : 16;
+    a.tile_heads = nq / nkv < 8 ? nq / nkv : 8;
     a.use_scratch = (a.rope_denom != nullptr && (rotary_dim / 2) % 32 != 0) ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
 #define RFX_CASE(DD) \

@@ -35,6 +35,18 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                  : "r"(smem_u32(p)));
 }
+__device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];"
+                 : "=r"(r[0]), "=r"(r[1])
+                 : "r"(smem_u32(p)));
+}
+// An 8 x 8 matrix of 16-bit elements held one row pair per thread, transposed
+// across the warp.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
@@ -163,6 +175,87 @@ __device__ __forceinline__ void attend_tile(const __nv_bfloat16* qs, const __nv_
             mma_bf16(acc[n], a, b[0], b[1]);
             mma_bf16(acc[n + 1], a, b[2], b[3]);
         }
+    }
+}
+
+// ---- decode: the keys as the rows of the MMA ---------------------------------
+// One query position has only its group's few heads for rows, so the tile is
+// turned around: S^T [16 keys x 8 heads] = K [16 x D] . Q^T, O^T [D x 8 heads] +=
+// V^T [D x 16 keys] . P [16 keys x 8 heads].  Against heads as rows this halves
+// the MMAs and fragment loads per key, and all eight columns are heads (four
+// of them real at a group of four, against four of sixteen rows).
+//
+// The query heads are the B operand of every step: their fragments are loaded
+// once (qf[k] for the k-th 16 columns of D) from a tile qs [8][D + 8].
+template <int D>
+__device__ __forceinline__ void load_query_fragments(const __nv_bfloat16* qs, uint32_t (&qf)[D / 16][2]) {
+    const int lane = threadIdx.x & 31;
+    constexpr int LD = D + 8;
+#pragma unroll
+    for (int k = 0; k < D / 16; ++k)
+        ldmatrix_x2(qf[k], qs + (lane & 7) * LD + k * 16 + 8 * ((lane >> 3) & 1));
+}
+
+// One warp, 16 keys of a K/V tile starting at tile row `key0`.  A thread's
+// state covers heads 2 (lane % 4) and 2 (lane % 4) + 1: running maxima m[2]
+// (the same in the eight lanes that share lane % 4), its own share of their
+// sums l[2] (added across those lanes by the caller at the end), and
+// acc[i][..]: rows 16 i + lane / 4 (+ 8) of O^T for the two heads.
+//   visible(j): whether tile key j (0-based in the tile) is visible
+template <int D, typename Visible>
+__device__ __forceinline__ void attend_keys16(const uint32_t (&qf)[D / 16][2], const __nv_bfloat16* ks,
+                                              const __nv_bfloat16* vs, int key0, float scale_log2,
+                                              Visible visible, float (&m)[2], float (&l)[2],
+                                              float (&acc)[D / 16][4]) {
+    const int lane = threadIdx.x & 31;
+    constexpr int LD = D + 8;
+    float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int k = 0; k < D / 16; ++k) {
+        uint32_t a[4];
+        ldmatrix_x4(a, ks + (key0 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LD + k * 16 + 8 * (lane >> 4));
+        mma_bf16(s, a, qf[k][0], qf[k][1]);
+    }
+    // s[0], s[1]: key lane / 4, the two heads; s[2], s[3]: key lane / 4 + 8
+    const int ka = key0 + (lane >> 2), kb = ka + 8;
+    const bool va = visible(ka), vb = visible(kb);
+    float v[4];
+    v[0] = va ? s[0] * scale_log2 : -INFINITY;
+    v[1] = va ? s[1] * scale_log2 : -INFINITY;
+    v[2] = vb ? s[2] * scale_log2 : -INFINITY;
+    v[3] = vb ? s[3] * scale_log2 : -INFINITY;
+    float corr[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        float mx = fmaxf(v[j], v[j + 2]);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+        const float m_new = fmaxf(m[j], mx);
+        // all keys so far masked: keep the state untouched
+        corr[j] = (m_new == -INFINITY) ? 1.0f : exp2f(m[j] - m_new);
+        m[j] = m_new;
+    }
+    float e[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) e[i] = (m[i & 1] == -INFINITY) ? 0.0f : exp2f(v[i] - m[i & 1]);
+    l[0] = l[0] * corr[0] + (e[0] + e[2]);
+    l[1] = l[1] * corr[1] + (e[1] + e[3]);
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) {
+        acc[i][0] *= corr[0];
+        acc[i][1] *= corr[1];
+        acc[i][2] *= corr[0];
+        acc[i][3] *= corr[1];
+    }
+    // P [keys x heads] as the B operand: each 8 x 8 half transposed across the warp
+    const uint32_t b0 = movmatrix_trans(pack_bf16(e[0], e[1]));
+    const uint32_t b1 = movmatrix_trans(pack_bf16(e[2], e[3]));
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) {
+        uint32_t a[4];
+        ldmatrix_x4_trans(a, vs + (key0 + (lane & 7) + 8 * (lane >> 4)) * LD + i * 16 + 8 * ((lane >> 3) & 1));
+        mma_bf16(acc[i], a, b0, b1);
     }
 }
 

@@ -108,7 +108,7 @@ def swiglu(gate_up: torch.Tensor, alternating: bool = False) -> torch.Tensor:
 
 
 # -------------------------------------------------------------------- linear
-GEMV_MAX_ROWS = 64  # up to here the weight-streaming tensor-core kernel runs
+GEMV_MAX_ROWS = int(_os.environ.get("REFLEX_B200_GEMV_MAX_ROWS", "64"))  # up to here the weight-streaming tensor-core kernel runs
 
 _ERR = {}
 
@@ -346,7 +346,7 @@ def decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int = 64) -> int:
     forced = int(_os.environ.get("REFLEX_B200_DECODE_SPLITS", "0"))  # tuning aid
     if forced > 0:
         return forced
-    ctas = n_rows * nkv * ((nq // nkv + 15) // 16)
+    ctas = n_rows * nkv * ((nq // nkv + 7) // 8)
     best, best_cost = 1, None
     for s in (1, 2, 4, 8, 16, 32, 64):
         if s > max(1, max_pages):
@@ -401,7 +401,7 @@ def fused_decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int) -> int:
     forced = int(_os.environ.get("REFLEX_B200_DECODE_SPLITS", "0"))  # tuning aid
     if forced > 0:
         return max(s for s in (1, 2, 4, 8) if s <= forced)
-    ctas = n_rows * nkv * ((nq // nkv + 15) // 16)
+    ctas = n_rows * nkv * ((nq // nkv + 7) // 8)
     best, best_cost = 1, None
     for s in (1, 2, 4, 8):
         if s > max(1, max_pages):

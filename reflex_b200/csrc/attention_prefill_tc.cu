@@ -31,6 +31,19 @@
 
 namespace {
 
+// Optional timeline for tuning: when a buffer is set (rfx_attention_prefill_tc_trace),
+// chosen threads store %globaltimer at up to 32 places per CTA; the last launch wins.
+static __device__ unsigned long long* g_trace = nullptr;
+static __device__ int g_trace_ctas = 0;
+__device__ __forceinline__ void trace_mark(int which) {
+    if (g_trace == nullptr) return;
+    const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    if (cta >= g_trace_ctas) return;
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    g_trace[(size_t)cta * 32 + which] = t;
+}
+
 using namespace sm100;
 using rfx::PagedKV;
 
@@ -203,8 +216,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                 const uint32_t phs = (j / KV_STAGES) & 1;
                 // S_j reuses the columns of S_{j-2} and P_{j-2}: PV_{j-2} was issued
                 // before this and the tensor core runs MMAs in issue order
+                if (j >= 4 && j < 8) trace_mark(16 + (j - 4) * 4 + 0);
                 if (!mbar_wait(&k_full[s], phs)) { atomicExch(err, 18); ok = false; break; }
                 tc_fence_after_sync();
+                if (j >= 4 && j < 8) trace_mark(16 + (j - 4) * 4 + 1);
                 const uint32_t qa = smem_u32(q_tile), ka = smem_u32(k_ring + s * KV_BYTES);
 #pragma unroll
                 for (int kb = 0; kb < KB; ++kb)
@@ -216,7 +231,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                     }
                 umma_commit(&k_empty[s]);
                 umma_commit(&s_full[b]);
+                if (j >= 4 && j < 8) trace_mark(16 + (j - 4) * 4 + 2);
                 if (j > 0) ok = pv(j - 1);
+                if (j >= 4 && j < 8) trace_mark(16 + (j - 4) * 4 + 3);
             }
             if (ok && n_pages > 0) ok = pv(n_pages - 1);
             if (!ok) abort_flag = 1;
@@ -239,36 +256,40 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         for (int j = 0; j < n_pages && ok; ++j) {
             const int b = j & 1;
             const uint32_t ph2 = (j >> 1) & 1;
+            if (t == 0 && j >= 4 && j < 8) trace_mark((j - 4) * 4 + 0);
             if (!mbar_wait(&s_full[b], ph2)) { atomicExch(err, 22); ok = false; break; }
             tc_fence_after_sync();
+            if (t == 0 && j >= 4 && j < 8) trace_mark((j - 4) * 4 + 1);
             uint32_t sr[PAGE];
 #pragma unroll
             for (int c = 0; c < PAGE / 16; ++c)
                 tmem_ld_16_nowait(tmem + lane_addr + S_COL + b * PAGE + c * 16, sr + c * 16);
             tmem_ld_wait();
+            if (t == 0 && j >= 4 && j < 8) trace_mark((j - 4) * 4 + 2);
 
             const int basej = (pg0 + j) * PAGE;
             // every key of the page visible to every valid row of the tile: no compares
             const bool all_visible = basej + PAGE - 1 <= pos_first && basej >= lo_last && n_rows == ROWS;
             // four independent chains each for the maximum and the sum: one warp per
             // scheduler has nothing else to hide a dependent chain's latency with
-            float s[PAGE];
+            float s[PAGE];  // raw scores; the scale (positive) goes into the exponent's multiply-add
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (all_visible) {
 #pragma unroll
-                for (int c = 0; c < PAGE; ++c) {
-                    s[c] = __uint_as_float(sr[c]) * scale_log2;
-                    mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
-                }
+                for (int c = 0; c < PAGE; ++c) s[c] = __uint_as_float(sr[c]);
+#pragma unroll
+                for (int c = 0; c < PAGE; c += 8)  // two new values per maximum: a three-input instruction
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) mx4[k] = fmaxf(fmaxf(mx4[k], s[c + 2 * k]), s[c + 2 * k + 1]);
             } else {
 #pragma unroll
                 for (int c = 0; c < PAGE; ++c) {
                     const int key = basej + c;
-                    s[c] = (key <= row_pos && key >= row_lo) ? __uint_as_float(sr[c]) * scale_log2 : -INFINITY;
+                    s[c] = (key <= row_pos && key >= row_lo) ? __uint_as_float(sr[c]) : -INFINITY;
                     mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
                 }
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
             // the reference maximum moves only when it must
             float corr = 1.0f;
             const bool raise = mx > m + RAISE || (m == -INFINITY && mx != -INFINITY);
@@ -283,8 +304,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             uint32_t packed[PAGE / 2];
 #pragma unroll
             for (int c = 0; c < PAGE; c += 2) {
-                const float e0 = ex2(s[c] - shift);
-                const float e1 = ex2(s[c + 1] - shift);
+                const float e0 = ex2(fmaf(s[c], scale_log2, -shift));
+                const float e1 = ex2(fmaf(s[c + 1], scale_log2, -shift));
                 rs4[(c >> 1) & 3] += e0 + e1;
                 __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
                 packed[c / 2] = *reinterpret_cast<uint32_t*>(&h);
@@ -330,6 +351,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_full[b]);
+            if (t == 0 && j >= 4 && j < 8) trace_mark((j - 4) * 4 + 3);
         }
         if (ok && n_pages > 0) {
             if (!mbar_wait(&o_full, (uint32_t)((n_pages - 1) & 1))) { atomicExch(err, 25); ok = false; }
@@ -436,6 +458,15 @@ int launch_tc(const void* q, const void* k_pages, const void* v_pages, long long
 // As rfx_attention_prefill, for head_dim 64 or 128.  `n_pages_total` is the
 // number of pages of the K/V store (for the TMA maps), R the number of rows of
 // q.  `err` is a device word that receives a code if a bounded wait ran out.
+// Tuning aid: 32 64-bit timestamps per CTA of the launches that follow (null
+// switches it off).
+extern "C" int rfx_attention_prefill_tc_trace(void* buffer, int ctas) {
+    unsigned long long* p = (unsigned long long*)buffer;
+    cudaError_t e = cudaMemcpyToSymbol(g_trace, &p, sizeof(p));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_trace_ctas, &ctas, sizeof(int));
+    return (int)e;
+}
+
 extern "C" int rfx_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages,
                                         long long n_pages_total, const int* page_table, int max_pages,
                                         int page_size, const int* seq_slot, const int* seq_start,

@@ -32,7 +32,8 @@
 namespace {
 
 // Optional timeline for tuning: when a buffer is set (rfx_attention_prefill_tc_trace),
-// chosen threads store %globaltimer at up to 32 places per CTA; the last launch wins.
+// chosen threads store %globaltimer at a few places of a CTA's life (32 slots per
+// CTA); the last launch wins.
 static __device__ unsigned long long* g_trace = nullptr;
 static __device__ int g_trace_ctas = 0;
 __device__ __forceinline__ void trace_mark(int which) {
@@ -124,9 +125,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     uint8_t* v_ring = k_ring + KV_STAGES * KV_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int seq = blockIdx.y, kvh = blockIdx.z;
+    if (threadIdx.x == 0) trace_mark(0);  // 0 entry, 1 set up, 2 first scores, 3 last page done, 4 output written, 5 exit
+    // CTAs are handed out with x fastest: kv heads and sequences vary fastest and
+    // the tile slowest, so that the longest tiles of every head start first
+    const int kvh = blockIdx.x, seq = blockIdx.y;
     const int n_new = seq_new[seq];
-    const int q0 = (gridDim.x - 1 - blockIdx.x) * bq;  // the longest tiles first
+    const int q0 = (gridDim.z - 1 - blockIdx.z) * bq;  // the longest tiles first
     const bool active = q0 < n_new;
     const int g = nq / cache.n_kv_heads;
     const int slot = seq_slot[seq], start = seq_start[seq], row0 = seq_row0[seq];
@@ -162,6 +166,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     tc_fence_after_sync();
     const uint32_t tmem = tmem_base_smem;
     rfx::pdl_prologue();  // q and this step's keys and values come from the kernel before
+    if (threadIdx.x == 0) trace_mark(1);
 
     if (!active) {
         // nothing to do for this tile; fall through to the teardown
@@ -216,10 +221,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                 const uint32_t phs = (j / KV_STAGES) & 1;
                 // S_j reuses the columns of S_{j-2} and P_{j-2}: PV_{j-2} was issued
                 // before this and the tensor core runs MMAs in issue order
-                if (j >= 4 && j < 8) trace_mark(16 + (j - 4) * 4 + 0);
                 if (!mbar_wait(&k_full[s], phs)) { atomicExch(err, 18); ok = false; break; }
                 tc_fence_after_sync();
-                if (j >= 4 && j < 8) trace_mark(16 + (j - 4) * 4 + 1);
                 const uint32_t qa = smem_u32(q_tile), ka = smem_u32(k_ring + s * KV_BYTES);
 #pragma unroll
                 for (int kb = 0; kb < KB; ++kb)
@@ -231,9 +234,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                     }
                 umma_commit(&k_empty[s]);
                 umma_commit(&s_full[b]);
-                if (j >= 4 && j < 8) trace_mark(16 + (j - 4) * 4 + 2);
                 if (j > 0) ok = pv(j - 1);
-                if (j >= 4 && j < 8) trace_mark(16 + (j - 4) * 4 + 3);
             }
             if (ok && n_pages > 0) ok = pv(n_pages - 1);
             if (!ok) abort_flag = 1;
@@ -256,16 +257,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         for (int j = 0; j < n_pages && ok; ++j) {
             const int b = j & 1;
             const uint32_t ph2 = (j >> 1) & 1;
-            if (t == 0 && j >= 4 && j < 8) trace_mark((j - 4) * 4 + 0);
             if (!mbar_wait(&s_full[b], ph2)) { atomicExch(err, 22); ok = false; break; }
             tc_fence_after_sync();
-            if (t == 0 && j >= 4 && j < 8) trace_mark((j - 4) * 4 + 1);
+            if (t == 0 && j == 0) trace_mark(2);
             uint32_t sr[PAGE];
 #pragma unroll
             for (int c = 0; c < PAGE / 16; ++c)
                 tmem_ld_16_nowait(tmem + lane_addr + S_COL + b * PAGE + c * 16, sr + c * 16);
             tmem_ld_wait();
-            if (t == 0 && j >= 4 && j < 8) trace_mark((j - 4) * 4 + 2);
 
             const int basej = (pg0 + j) * PAGE;
             // every key of the page visible to every valid row of the tile: no compares
@@ -351,8 +350,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_full[b]);
-            if (t == 0 && j >= 4 && j < 8) trace_mark((j - 4) * 4 + 3);
         }
+        if (t == 0) trace_mark(3);
         if (ok && n_pages > 0) {
             if (!mbar_wait(&o_full, (uint32_t)((n_pages - 1) & 1))) { atomicExch(err, 25); ok = false; }
         }
@@ -360,11 +359,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             tc_fence_after_sync();
             const float inv = 1.0f / l;
             __nv_bfloat16* o = out + ((size_t)(row0 + q0 + row_p) * nq + kvh * g + row_h) * D;
+            // two loads of 16 columns in flight: the next one travels while this one is stored
+            uint32_t rr[2][16];
+            tmem_ld_16_nowait(tmem + lane_addr + O_COL, rr[0]);
 #pragma unroll
             for (int c = 0; c < D / 16; ++c) {
-                uint32_t r[16];
-                tmem_ld_16_nowait(tmem + lane_addr + O_COL + c * 16, r);
-                tmem_ld_wait();
+                tmem_ld_wait_16(rr[c & 1]);
+                if (c + 1 < D / 16) tmem_ld_16_nowait(tmem + lane_addr + O_COL + (c + 1) * 16, rr[(c + 1) & 1]);
+                uint32_t(&r)[16] = rr[c & 1];
                 if (row_valid) {
                     uint4 v[2];
                     __nv_bfloat162* pv2 = reinterpret_cast<__nv_bfloat162*>(v);
@@ -376,10 +378,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                 }
             }
         }
+        if (t == 0) trace_mark(4);
         tc_fence_before_sync();
     }
 
     __syncthreads();
+    if (threadIdx.x == 0) trace_mark(5);
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, TMEM_COLS);
@@ -446,7 +450,8 @@ int launch_tc(const void* q, const void* k_pages, const void* v_pages, long long
     auto kernel = attention_prefill_tc_kernel<D>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    dim3 grid((max_new + bq - 1) / bq, S, cache.n_kv_heads);
+    if ((max_new + bq - 1) / bq > 65535 || S > 65535) return RFX_ERR_UNSUPPORTED;
+    dim3 grid(cache.n_kv_heads, S, (max_new + bq - 1) / bq);
     if (grid.y > 65535 || grid.z > 65535) return RFX_ERR_UNSUPPORTED;
     RFX_LAUNCH(kernel, grid, THREADS, smem, s, mq, mk, mv, cache, seq_slot, seq_start, seq_new, seq_row0,
                (__nv_bfloat16*)out, nq, bq, window, scale * 1.4426950408889634f, err);

@@ -10,6 +10,12 @@ from .. import ops
 from .params import SamplingParams, fresh_seed, uniform
 
 
+# Pick buffers (device ids, scratch, pinned host ids, event) by (device, batch
+# size), kept for the life of the process: pinned allocations take milliseconds
+# and synchronise the device, far too much for every generation call.
+_RINGS: dict = {}
+
+
 class PendingIds:
     """Ids picked on the device and on their way to the host: `dev` (int32 [n])
     can feed the next step at once; `wait()` gives the host list."""
@@ -33,7 +39,6 @@ class Sampler:
         self.seed = params.seed if params.seed is not None else fresh_seed()
         self._const = {}
         self._scratch = None
-        self._rings = {}  # batch size -> ring of pick buffers
 
     def _constants(self, n: int):
         if n not in self._const:
@@ -50,7 +55,7 @@ class Sampler:
     def _slot(self, n: int):
         """(ids on the device, argmax scratch, pinned host ids, event) for the
         next pick of n rows, from a small ring per batch size."""
-        ring = self._rings.setdefault(n, {"next": 0, "slots": [None] * self.RING})
+        ring = _RINGS.setdefault((str(self.device), n), {"next": 0, "slots": [None] * self.RING})
         i = ring["next"]
         ring["next"] = (i + 1) % self.RING
         if ring["slots"][i] is None:

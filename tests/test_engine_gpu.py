@@ -25,6 +25,8 @@ cut into steps or batched: every kernel there reduces in an order that does not
 depend on the batch, so any difference is a fault of the cache or the batch.
 """
 
+import math
+
 import numpy as np
 import pytest
 import torch
@@ -184,3 +186,50 @@ def test_step_errors_leave_the_cache_as_it_was():
     out = eng.step([(s, [1, 2, 3], [2])])
     assert out.shape == (1, 512) and eng.length(s) == 3
     eng.close(s)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_one_layer_at_the_benchmark_models_widths(dtype):
+    """The tiny configurations keep every size small; here one layer has the
+    benchmark model's widths (hidden 4096, 32 query and 8 kv heads of 128,
+    feed-forward 12288; the vocabulary cut to 2048 so that the plain
+    implementation stays quick), which is where the tensor-core kernels' tile
+    cuts, K splits and clusters are what they are in use.  A prompt whole, then
+    its last tokens one by one, and a batch of three, against the plain
+    implementation.  In 32-bit the bound is the tiny models' bound scaled by the
+    square root of the longest reduction (12288 terms here against 320 there):
+    sequential 32-bit sums round once per term.  The cuttings still agree bit
+    for bit."""
+    import shutil
+    import tempfile
+
+    import plain_model
+    from reflex_b200.weights import write_random_model
+
+    cfg = {
+        "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 1,
+        "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+        "intermediate_size": 12288, "vocab_size": 2048, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+        "tie_word_embeddings": False, "max_position_embeddings": 4096,
+    }
+    folder = tempfile.mkdtemp(prefix="rfx_wide_")
+    try:
+        write_random_model(cfg, 11, folder, stored(dtype))
+        eng = helpers.make_engine(folder, dtype, max_tokens=1024)
+        pcfg, w = plain_model.read_model(folder)
+        toks = helpers.random_tokens(70, 2048, 5)
+        ref = plain_model.forward(pcfg, w, toks)
+        bound = tol(dtype) * (math.sqrt(12288 / 320) if dtype == "float32" else 1.0)
+        whole = helpers.run_whole(eng, toks)
+        tail = helpers.run_tail_one_by_one(eng, toks, 6)
+        assert helpers.rel_err(whole, ref) < bound
+        assert helpers.rel_err(tail, ref) < bound
+        if dtype == "float32":
+            assert np.array_equal(whole, tail)
+        reqs = [toks[:9], toks[9:40], toks[40:]]
+        got = helpers.run_batches(eng, reqs, 3, [4, 20, 8])
+        for r, g in zip(reqs, got):
+            assert helpers.rel_err(g, plain_model.forward(pcfg, w, r)) < bound
+        assert eng.cache.slots.held_count == 0
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)

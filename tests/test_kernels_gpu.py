@@ -280,11 +280,13 @@ ATT_CASES = [
 ]
 
 
-@pytest.mark.parametrize("nq,nkv,d,seqs,window", ATT_CASES)
-@pytest.mark.parametrize("kernel", ["plain_f32", "plain_bf16", "prefill_bf16", "prefill_tc_bf16"])
-def test_attention_over_the_paged_cache(nq, nkv, d, seqs, window, kernel):
-    if kernel == "prefill_tc_bf16" and d not in (64, 128):
-        pytest.skip("the tcgen05 kernel takes head sizes 64 and 128")
+# every case with every kernel that takes its head size (the tcgen05 kernel: 64 and 128)
+ATT_RUNS = [(k,) + c for k in ("plain_f32", "plain_bf16", "prefill_bf16", "prefill_tc_bf16") for c in ATT_CASES
+            if k != "prefill_tc_bf16" or c[2] in (64, 128)]
+
+
+@pytest.mark.parametrize("kernel,nq,nkv,d,seqs,window", ATT_RUNS)
+def test_attention_over_the_paged_cache(kernel, nq, nkv, d, seqs, window):
     g = torch.Generator().manual_seed(nq * 31 + d)
     dtype = torch.float32 if kernel == "plain_f32" else torch.bfloat16
     slots, table, kp, vp, ks, vs = _paged([a + b for a, b in seqs], nkv, d, dtype, g)

@@ -1,8 +1,8 @@
 """The command line, in the manner of `reflex <subcommand>`
 (src/bin/reflex/main.rs:36-50): `generate`, `system1`, `check`, `bench`,
-with the reference's option names and meanings where it has them
-(src/bin/reflex/generate.rs:186-250, system1.rs:88-107, check.rs:42-78,
-bench.rs:50-55).  A model is a folder (config.json + safetensors) instead of a
+`smoke`, `doctor`, with the reference's option names and meanings where it has
+them (src/bin/reflex/generate.rs:186-250, system1.rs:88-107, check.rs:42-78,
+bench.rs:50-55, smoke.rs:1-16, doctor.rs:1-40).  A model is a folder (config.json + safetensors) instead of a
 GGUF file, and prompts and candidates are comma-separated token ids instead of
 text, since this library has no tokenizer.  Results are one `KEY=value` line
 per command (`REFLEX_GENERATE_OK ...`), or one JSON line with `--json`; errors
@@ -24,6 +24,8 @@ USAGE = """usage: reflex <subcommand> ...
   check    <model-dir> <prompt-ids> [--max-tokens N] [--reference file] [--tolerance F]
   bench    <model-dir> [--warmup N] [--iters N] [--weights bf16|f32]
   random   <config.json> <out-dir> [--seed N] [--dtype bfloat16|float32]
+  smoke    [--json]      one kernel through the whole path: build, load, launch, check
+  doctor   [--json]      is this machine set up for the library? (exit 0 / 1 / 2)
 prompt-ids and candidates are comma-separated token ids."""
 
 DEFAULT_PROMPT = [1, 2, 3, 4]
@@ -241,6 +243,106 @@ def cmd_random(argv: List[str], t0: float) -> int:
     return 0
 
 
+def cmd_smoke(argv: List[str], t0: float) -> int:
+    """The first thing to run on a fresh machine: builds (if needed) and loads
+    the kernel library, launches one kernel and checks its result; reports the
+    time from process start to that first result (src/bin/reflex/smoke.rs:1-16,
+    :105)."""
+    a = Args(argv, set(), {"--json"})
+    import torch
+
+    from . import ops
+
+    if not torch.cuda.is_available():
+        fail("smoke: no CUDA device")
+    x = torch.arange(1, 65, dtype=torch.float32, device="cuda:0").reshape(1, 64)
+    w = torch.ones(64, dtype=torch.float32, device="cuda:0")
+    y = ops.rmsnorm(x, w, 0.0, torch.float32)
+    want = x / torch.sqrt((x * x).mean())
+    ok = bool(torch.allclose(y, want, rtol=1e-6, atol=0))
+    ms = (time.perf_counter() - t0) * 1000.0
+    if not ok:
+        fail("smoke: the kernel's result is wrong")
+    if "--json" in a.bools:
+        print(json.dumps({"ok": True, "process_start_to_first_result_ms": round(ms, 3)}))
+    else:
+        print(f"REFLEX_SMOKE_OK process_start_to_first_result_ms={ms:.3f}")
+    return 0
+
+
+def cmd_doctor(argv: List[str], t0: float) -> int:
+    """A health report of the GPU and the toolchain, no model involved
+    (src/bin/reflex/doctor.rs:1-40): one `REFLEX_DOCTOR_CHECK name= status=
+    detail=` line per check, then `REFLEX_DOCTOR_OK` (exit 0; warnings allowed)
+    or `REFLEX_DOCTOR_FAIL` (exit 1)."""
+    if any(x not in ("--json",) for x in argv):
+        print(USAGE, file=sys.stderr)
+        return 2
+    as_json = "--json" in argv
+    checks = []
+
+    def add(name, status, detail):
+        checks.append({"name": name, "status": status, "detail": detail})
+        if as_json:
+            print(json.dumps({"check": name, "status": status, "detail": detail}))
+        else:
+            print(f"REFLEX_DOCTOR_CHECK name={name} status={status} detail={json.dumps(detail)}")
+
+    import torch
+
+    gpu = torch.cuda.is_available()
+    if gpu:
+        props = torch.cuda.get_device_properties(0)
+        add("cuda_device", "pass", f"{props.name}, {props.total_memory >> 20} MiB, {props.multi_processor_count} SMs")
+        cc = f"{props.major}.{props.minor}"
+        add("compute_capability", "pass" if (props.major, props.minor) == (10, 0) else "fail",
+            f"device {cc}, kernels are built for sm_100a")
+    else:
+        add("cuda_device", "fail", "no CUDA device is visible")
+    try:
+        from .csrc import build
+
+        add("compiler", "pass", build.find_nvcc())
+    except RuntimeError as e:
+        add("compiler", "warn", f"{e} (only needed when the library has to be rebuilt)")
+    try:
+        from .csrc import build
+
+        add("kernel_library", "pass", build.ensure_built())
+    except Exception as e:  # a report, not a crash
+        add("kernel_library", "fail", str(e))
+    if gpu and checks[-1]["status"] == "pass":
+        try:
+            from . import ops
+
+            g = torch.Generator().manual_seed(0)
+            x = torch.randn(4, 256, generator=g).bfloat16().cuda()
+            w = torch.randn(384, 256, generator=g).bfloat16().cuda()
+            y = ops.gemm_tc(x, w, torch.float32)
+            ops.check_device_errors("cuda:0")
+            err = float((y - x.float() @ w.float().T).abs().max())
+            add("kernel_launch", "pass" if err < 1e-2 else "fail",
+                f"tcgen05 product 4x256x384, largest difference to the library product {err:.2e}")
+        except Exception as e:
+            add("kernel_launch", "fail", str(e))
+        free, total = torch.cuda.mem_get_info(0)
+        add("device_memory", "pass" if free > (1 << 30) else "warn", f"{free >> 20} of {total >> 20} MiB free")
+    try:
+        import pynvml  # noqa: F401
+
+        add("nvml", "pass", "pynvml importable (clocks and power can be sampled)")
+    except Exception:
+        add("nvml", "warn", "pynvml not importable; nvidia-smi is used for clocks where needed")
+    n = {k: sum(c["status"] == k for c in checks) for k in ("pass", "warn", "fail")}
+    ok = n["fail"] == 0
+    if as_json:
+        print(json.dumps({"ok": ok, "checks_passed": n["pass"], "checks_warned": n["warn"], "checks_failed": n["fail"]}))
+    else:
+        print(f"REFLEX_DOCTOR_{'OK' if ok else 'FAIL'} checks_passed={n['pass']} checks_warned={n['warn']} "
+              f"checks_failed={n['fail']}")
+    return 0 if ok else 1
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     t0 = time.perf_counter()
     argv = list(sys.argv[1:] if argv is None else argv)
@@ -250,7 +352,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     from .errors import ReflexError
 
     cmds = {"generate": cmd_generate, "system1": cmd_system1, "check": cmd_check,
-            "bench": cmd_bench, "random": cmd_random}
+            "bench": cmd_bench, "random": cmd_random, "smoke": cmd_smoke, "doctor": cmd_doctor}
     if argv[0] not in cmds:
         fail(f"unknown subcommand {argv[0]!r}\n{USAGE}")
     try:

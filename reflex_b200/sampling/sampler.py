@@ -2,6 +2,8 @@
 
 from __future__ import annotations
 
+import os
+import sys
 from typing import List, Optional, Sequence
 
 import torch
@@ -14,6 +16,19 @@ from .params import SamplingParams, fresh_seed, uniform
 # size), kept for the life of the process: pinned allocations take milliseconds
 # and synchronise the device, far too much for every generation call.
 _RINGS: dict = {}
+
+
+# `REFLEX_TOP2_TRACE=1`: a numerics probe that prints, to stderr, the two
+# highest logits of every picked position (src/sampling.rs:166-191); comparing
+# two runs' traces gives the margin a greedy choice had where they part.
+TOP2_TRACE = os.environ.get("REFLEX_TOP2_TRACE", "") not in ("", "0")
+
+
+def trace_top2(logits: torch.Tensor, requests: Sequence[int]) -> None:
+    top = torch.topk(logits, 2, dim=1)
+    for r, ids, vals in zip(requests, top.indices.tolist(), top.values.tolist()):
+        print(f"REFLEX_TOP2 request={r} top1_id={ids[0]} top1_logit={vals[0]} top2_id={ids[1]} "
+              f"top2_logit={vals[1]}", file=sys.stderr)
 
 
 class PendingIds:
@@ -70,6 +85,8 @@ class Sampler:
         step and travel to the host behind an event."""
         n, V = logits.shape
         dev, scratch, host, event = self._slot(n)
+        if TOP2_TRACE:
+            trace_top2(logits, requests)
         if self.params.is_greedy():
             ops.argmax(logits, out=dev, scratch=scratch)
         else:

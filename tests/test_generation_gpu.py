@@ -135,6 +135,26 @@ def test_command_line_generate_and_system1():
     assert bad.returncode == 1 and "error:" in bad.stderr
 
 
+def test_command_line_smoke_doctor_and_the_top2_probe():
+    folder = helpers.model_folder("A", 7, "float32")
+    exe = [sys.executable, os.path.join(ROOT, "bin", "reflex")]
+    out = subprocess.run(exe + ["smoke"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and "REFLEX_SMOKE_OK process_start_to_first_result_ms=" in out.stdout, out.stderr
+    out = subprocess.run(exe + ["doctor"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout + out.stderr
+    checks = [l for l in out.stdout.splitlines() if l.startswith("REFLEX_DOCTOR_CHECK")]
+    assert any("name=kernel_launch status=pass" in l for l in checks)
+    assert out.stdout.strip().splitlines()[-1].startswith("REFLEX_DOCTOR_OK checks_passed=")
+    assert subprocess.run(exe + ["doctor", "--what"], capture_output=True, text=True, timeout=300).returncode == 2
+    env = dict(os.environ, REFLEX_TOP2_TRACE="1")
+    out = subprocess.run(exe + ["generate", folder, "5,17,3", "--max-tokens", "3", "--weights", "f32"],
+                         capture_output=True, text=True, timeout=300, env=env)
+    assert out.returncode == 0, out.stderr
+    probes = [l for l in out.stderr.splitlines() if l.startswith("REFLEX_TOP2 ")]
+    ids = [int(t) for t in out.stdout.split("token_ids=[")[1].split("]")[0].split(",")]
+    assert [int(l.split("top1_id=")[1].split()[0]) for l in probes] == ids  # greedy: the top id is the pick
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_replays_steps_and_writes_logits(dtype, tmp_path):
     """bin/trace_run as a subprocess: two requests start together with unequal

@@ -87,7 +87,9 @@ class CausalLM:
 
     # --- forward ----------------------------------------------------------
     def hidden_states(self, batch, cache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        ops.prof_mark("start")
         h = ops.embed(self.embedding, batch.tokens, self.spec.embedding_scale, self.err_flag)
+        ops.prof_mark("embed")
         pending = None
         order = self.spec.run_order
         for i, run in enumerate(order):
@@ -120,6 +122,7 @@ class CausalLM:
         out = ops.linear(normed, self.head, out_dtype=torch.float32)
         if self.spec.logit_scale != 1.0:
             out = out * self.spec.logit_scale
+        ops.prof_mark("head")
         return out
 
     def forward(self, batch, cache) -> torch.Tensor:

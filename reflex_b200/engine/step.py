@@ -25,6 +25,12 @@ from .model import CausalLM
 StepEntry = Tuple[int, Sequence[int], Sequence[int]]  # (sequence, tokens, wanted places)
 
 
+def ops_profile_on() -> bool:
+    from .. import ops
+
+    return ops.PROFILE
+
+
 class Engine:
     def __init__(self, model: CausalLM, max_tokens: int, max_slots: Optional[int] = None,
                  use_graphs: bool = True):
@@ -107,6 +113,10 @@ class Engine:
             raise
         cache.commit(growth)
         self.steps_run += 1
+        if ops_profile_on():
+            from .. import ops
+
+            ops.prof_report(f"{self.steps_run - 1}:rows={sum(len(t) for t in tokens)}")
         return logits
 
     def step_decode(self, seqs: Sequence[int], tokens_dev: torch.Tensor) -> torch.Tensor:

@@ -108,7 +108,70 @@ def swiglu(gate_up: torch.Tensor, alternating: bool = False) -> torch.Tensor:
 
 
 # -------------------------------------------------------------------- linear
-GEMV_MAX_ROWS = int(_os.environ.get("REFLEX_B200_GEMV_MAX_ROWS", "64"))  # up to here the weight-streaming tensor-core kernel runs
+def _env_int(name: str, default: int, lo: int = 0, hi: int = 1 << 30) -> int:
+    """A run-time switch read once from the environment; a bad value is an
+    `InvalidInput`, as the reference treats its own switches
+    (src/model/kernels.rs:244-259)."""
+    raw = _os.environ.get(name)
+    if raw is None or raw == "":
+        return default
+    try:
+        v = int(raw)
+    except ValueError:
+        raise InvalidInput(f"{name} must be an integer, got {raw!r}") from None
+    if not (lo <= v <= hi):
+        raise InvalidInput(f"{name} must be between {lo} and {hi}, got {v}")
+    return v
+
+
+def _env_flag(name: str, default: bool) -> bool:
+    raw = _os.environ.get(name)
+    if raw is None or raw == "":
+        return default
+    if raw not in ("0", "1"):
+        raise InvalidInput(f"{name} must be 0 or 1, got {raw!r}")
+    return raw == "1"
+
+
+# `REFLEX_PREFILL_PROFILE=1`: CUDA events at phase marks of every eager step
+# (embed, norm, qkv_gemm, norm_rope, attn, o_proj, ffn_gate_up, ffn_down, head),
+# totals per phase printed to stderr after the step; a no-op when off and
+# inside graph capture (src/model/prefill_profile.rs:1-18, 26-59).
+PROFILE = _env_flag("REFLEX_PREFILL_PROFILE", False)
+_prof_events: list = []
+
+
+def prof_mark(name: str) -> None:
+    if not PROFILE or torch.cuda.is_current_stream_capturing():
+        return
+    ev = torch.cuda.Event(enable_timing=True)
+    ev.record()
+    _prof_events.append((name, ev))
+
+
+def prof_report(label: str) -> None:
+    """Waits for the device and prints, per phase, the time between each mark
+    and the one before it, summed over the step."""
+    import sys
+
+    if not PROFILE or len(_prof_events) < 2:
+        _prof_events.clear()
+        return
+    torch.cuda.synchronize()
+    totals, order = {}, []
+    for (_, e0), (name, e1) in zip(_prof_events, _prof_events[1:]):
+        if name not in totals:
+            totals[name] = 0.0
+            order.append(name)
+        totals[name] += e0.elapsed_time(e1)
+    whole = _prof_events[0][1].elapsed_time(_prof_events[-1][1])
+    for name in order:
+        print(f"REFLEX_PREFILL_PROFILE step={label} phase={name} ms={totals[name]:.3f}", file=sys.stderr)
+    print(f"REFLEX_PREFILL_PROFILE step={label} phase=total ms={whole:.3f}", file=sys.stderr)
+    _prof_events.clear()
+
+
+GEMV_MAX_ROWS = _env_int("REFLEX_B200_GEMV_MAX_ROWS", 64, 0, 64)  # up to here the weight-streaming tensor-core kernel runs
 
 _ERR = {}
 
@@ -266,7 +329,7 @@ def linear_residual(x: torch.Tensor, weight: torch.Tensor, hidden: torch.Tensor,
     return gemm_tc_residual(x, weight, hidden, w, spec.weight_offset, spec.eps)
 
 
-FUSE_NORM = _os.environ.get("REFLEX_B200_FUSE_NORM", "1") != "0"
+FUSE_NORM = _env_flag("REFLEX_B200_FUSE_NORM", True)
 
 
 def linear_swiglu(x: torch.Tensor, weight_pairs: torch.Tensor) -> torch.Tensor:
@@ -343,7 +406,7 @@ def decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int = 64) -> int:
     of two per SM; for the merge 2 us + 0.1 us a split inside a cluster (up to 8
     splits), 3 us + 0.25 us a split through the combine kernel.  The
     smallest estimate wins."""
-    forced = int(_os.environ.get("REFLEX_B200_DECODE_SPLITS", "0"))  # tuning aid
+    forced = _env_int("REFLEX_B200_DECODE_SPLITS", 0, 0, 64)  # tuning aid
     if forced > 0:
         return forced
     ctas = n_rows * nkv * ((nq // nkv + 7) // 8)
@@ -391,14 +454,14 @@ def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_sl
     return out
 
 
-CLUSTER_MERGE = _os.environ.get("REFLEX_B200_CLUSTER_MERGE", "1") != "0"
+CLUSTER_MERGE = _env_flag("REFLEX_B200_CLUSTER_MERGE", True)
 
 
 def fused_decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int) -> int:
     """Ranks of the fused decode kernel's cluster over the key range: the same
     estimate as `decode_splits`, with a cluster barrier (about 1 us) in place of
     the combine kernel, and at most 8 ranks."""
-    forced = int(_os.environ.get("REFLEX_B200_DECODE_SPLITS", "0"))  # tuning aid
+    forced = _env_int("REFLEX_B200_DECODE_SPLITS", 0, 0, 64)  # tuning aid
     if forced > 0:
         return max(s for s in (1, 2, 4, 8) if s <= forced)
     ctas = n_rows * nkv * ((nq // nkv + 7) // 8)
@@ -418,7 +481,7 @@ def fused_decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int) -> int:
 # kernels at batch 8 (3.42 against 3.40 ms a step) and behind them at batch 32
 # and 64, because its larger CTAs become resident later behind the product
 # kernel before them, which costs more than the launches it saves.
-FUSE_DECODE_ATTENTION = _os.environ.get("REFLEX_B200_FUSE_ATTENTION", "0") == "1"
+FUSE_DECODE_ATTENTION = _env_flag("REFLEX_B200_FUSE_ATTENTION", False)
 
 
 def attention_decode_fused(qkv: torch.Tensor, q_weight, k_weight, eps: float, weight_offset: float,

@@ -89,6 +89,7 @@ class GQAttention:
         batch = ctx.batch
         w = self.qkv if ctx.writes_cache else self.q_only
         qkv = ops.linear(x, w, out_dtype=torch.float32 if x.shape[0] <= ops.GEMV_MAX_ROWS else None)
+        ops.prof_mark("qkv_gemm")
         denom, rotary_dim = (None, 0) if self.position is None else self.position.rotation()
         norm = s.qk_norm
         if (ops.FUSE_DECODE_ATTENTION and batch.is_decode and qkv.dtype == torch.float32
@@ -108,12 +109,15 @@ class GQAttention:
                 norm.weight_offset if norm else 0.0, denom, rotary_dim, batch.row_pos, batch.row_slot,
                 kv.k_pages, kv.v_pages, kv.page_table, kv.page_size, s.num_heads, s.num_kv_heads,
                 s.head_dim, ctx.writes_cache, self.dtype)
+            ops.prof_mark("norm_rope")
             attn = ops.attention(q, kv.k_pages, kv.v_pages, kv.page_table, kv.page_size, batch,
                                  s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale)
+        ops.prof_mark("attn")
         if residual is not None:
             fused = ops.linear_residual(attn, self.o, residual[0], residual[1])
-            if fused is ops.ADDED:
-                return None  # nothing left to add
             if fused is not None:
-                return fused
-        return ops.linear(attn, self.o, out_dtype=torch.float32)
+                ops.prof_mark("o_proj")
+                return None if fused is ops.ADDED else fused  # None: nothing left to add
+        out = ops.linear(attn, self.o, out_dtype=torch.float32)
+        ops.prof_mark("o_proj")
+        return out

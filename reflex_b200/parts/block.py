@@ -66,11 +66,16 @@ class PreNormBlock:
             x = pending
         else:
             x = self.mixer_norm(hidden, delta=pending)
+            ops.prof_mark("norm")
         if getattr(self.mixer, "supports_fused_residual", False):
             a = self.mixer.forward(x, ctx, residual=(hidden, self.feed_forward_norm))
         else:
             a = self.mixer.forward(x, ctx)
-        x = a if isinstance(a, ops.NormedInput) else self.feed_forward_norm(hidden, delta=a)
+        if isinstance(a, ops.NormedInput):
+            x = a
+        else:
+            x = self.feed_forward_norm(hidden, delta=a)
+            ops.prof_mark("norm")
         if getattr(self.feed_forward, "supports_fused_residual", False):
             f = self.feed_forward.forward(x, residual=(hidden, next_norm))
         else:

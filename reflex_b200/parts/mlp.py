@@ -53,10 +53,12 @@ class SwiGLU:
         (`ops.NormedInput`) or None (added, the norm not begun).  Otherwise it
         returns the delta."""
         act = ops.linear_swiglu(x, self.gate_up)
+        ops.prof_mark("ffn_gate_up")
         if residual is not None:
             fused = ops.linear_residual(act, self.down, residual[0], residual[1])
-            if fused is ops.ADDED:
-                return None  # nothing left to add
             if fused is not None:
-                return fused
-        return ops.linear(act, self.down, out_dtype=torch.float32)
+                ops.prof_mark("ffn_down")
+                return None if fused is ops.ADDED else fused  # None: nothing left to add
+        out = ops.linear(act, self.down, out_dtype=torch.float32)
+        ops.prof_mark("ffn_down")
+        return out

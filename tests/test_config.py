@@ -121,3 +121,25 @@ def test_run_order_defaults_and_cache_entries():
     _, spec = spec_from_config_dict(TINY_B)
     assert [(r.layer, r.cache, r.writes_cache) for r in spec.run_order] == [(i, i, True) for i in range(3)]
     assert spec.cache_entries() == {0: 0, 1: 1, 2: 2}
+
+
+def test_run_time_switches_are_validated():
+    """A bad value of an environment switch is an error that names it, not a
+    silent default (the reference validates its own the same way:
+    src/model/kernels.rs:244-259)."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for name, bad in (("REFLEX_B200_FUSE_NORM", "yes"), ("REFLEX_B200_DECODE_SPLITS", "many"),
+                      ("REFLEX_B200_GEMV_MAX_ROWS", "4096")):
+        env = dict(os.environ, **{name: bad})
+        res = subprocess.run([sys.executable, "-c", "import reflex_b200.ops"], cwd=root, env=env,
+                             capture_output=True, text=True)
+        if name == "REFLEX_B200_DECODE_SPLITS":
+            # read when a decode step picks its splits, not at import
+            res = subprocess.run([sys.executable, "-c",
+                                  "import reflex_b200.ops as o; o.decode_splits(1, 8, 8, 4)"],
+                                 cwd=root, env=env, capture_output=True, text=True)
+        assert res.returncode != 0 and "InvalidInput" in res.stderr and name in res.stderr, res.stderr

@@ -320,8 +320,8 @@ def linear_residual(x: torch.Tensor, weight: torch.Tensor, hidden: torch.Tensor,
         _chk(hidden, "hidden", torch.float32)
         torch.addmm(hidden, x, weight.t(), out_dtype=torch.float32, out=hidden)
         return ADDED
-    if next_norm is None:
-        return None
+    if next_norm is None or weight.shape[0] % 8:
+        return None  # the product that takes these rows streams them by TMA: whole 16-byte units
     w = getattr(next_norm, "weight", None)
     spec = getattr(next_norm, "spec", None)
     if w is None or spec is None or getattr(spec, "kind", None) != "rmsnorm" or w.numel() != weight.shape[0]:

@@ -35,4 +35,16 @@ TINY_C = {
     "layer_types": ["full_attention", "sliding_attention", "full_attention", "sliding_attention"],
 }
 
-ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# widths that are no multiple of 8 (hidden 100, intermediate 100, vocabulary 333):
+# no 16-byte unit fits their bfloat16 rows, so the tensor-core products hand over
+# to the library product and nothing may assume they ran; five heads, no grouping
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 100, "num_attention_heads": 5, "num_key_value_heads": 5,
+    "head_dim": 16, "intermediate_size": 100, "vocab_size": 333, "rope_theta": 7777.0,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 512,
+    "hidden_act": "silu", "attention_bias": False, "rope_scaling": None,
+    "use_sliding_window": False, "sliding_window": None,
+}
+
+ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}

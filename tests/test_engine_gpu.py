@@ -233,3 +233,61 @@ def test_one_layer_at_the_benchmark_models_widths(dtype):
         assert eng.cache.slots.held_count == 0
     finally:
         shutil.rmtree(folder, ignore_errors=True)
+
+
+def _random_config(seed):
+    """A configuration drawn from sizes that strain the kernels' cuts: widths
+    that are and are not multiples of 8, head sizes from 16 to 256, groups up
+    to 17, windows shorter and longer than a page."""
+    import random
+
+    rng = random.Random(seed)
+    d = rng.choice([16, 32, 48, 64, 80, 96, 112, 128, 160, 256])
+    nkv = rng.choice([1, 1, 2, 3, 4, 8])
+    g = rng.choice([1, 2, 3, 4, 5, 6, 7, 8, 9, 16, 17])
+    layers = rng.choice([1, 2, 3])
+    window = rng.choice([None, None, 5, 20, 64, 70])
+    types = [rng.choice(["full_attention", "sliding_attention"]) if window else "full_attention"
+             for _ in range(layers)]
+    return {
+        "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": layers,
+        "hidden_size": rng.choice([20, 36, 50, 64, 72, 100, 104, 129, 200, 264, 520, 1032]),
+        "num_attention_heads": g * nkv, "num_key_value_heads": nkv, "head_dim": d,
+        "intermediate_size": rng.choice([8, 24, 50, 100, 136, 200, 301, 512, 1000]),
+        "vocab_size": rng.choice([17, 100, 333, 512, 1001, 4097]),
+        "rope_theta": rng.choice([1e4, 1e6, 500.0]), "rms_norm_eps": rng.choice([1e-6, 1e-5, 1e-3]),
+        "tie_word_embeddings": rng.choice([True, False]), "max_position_embeddings": 1024,
+        "sliding_window": window if "sliding_attention" in types else None, "layer_types": types,
+    }
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6, 7, 8])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_random_configurations(seed, dtype):
+    """Unequal batches (slots used again) and a tail decoded one by one, for
+    configurations drawn at random from a fixed seed, against the plain
+    implementation.  The 32-bit bound is a little above the tiny models' (head
+    sizes up to 256 and widths up to 1032 make the reductions longer)."""
+    import shutil
+    import tempfile
+
+    import plain_model
+    from reflex_b200.weights import write_random_model
+
+    cfg = _random_config(seed)
+    folder = tempfile.mkdtemp(prefix="rfx_rand_")
+    try:
+        write_random_model(cfg, seed, folder, stored(dtype))
+        eng = helpers.make_engine(folder, dtype, max_tokens=4096)
+        pcfg, w = plain_model.read_model(folder)
+        V = cfg["vocab_size"]
+        reqs = [helpers.random_tokens(n, V, n + seed) for n in (2, 100, 64, 37)]
+        bound = 5e-6 if dtype == "float32" else BF16_TOL
+        got = helpers.run_batches(eng, reqs, 3, [1, 200, 7])
+        for r, g in zip(reqs, got):
+            assert helpers.rel_err(g, plain_model.forward(pcfg, w, r)) < bound, cfg
+        tail = helpers.run_tail_one_by_one(eng, reqs[1], 32)
+        assert helpers.rel_err(tail, plain_model.forward(pcfg, w, reqs[1])) < bound, cfg
+        assert eng.cache.slots.held_count == 0
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)

@@ -101,6 +101,34 @@ template <> __device__ __forceinline__ void st<__nv_bfloat16>(__nv_bfloat16* p, 
     p[i] = __float2bfloat16_rn(v);
 }
 
+// four (two) neighbouring results in one access; the address is a multiple of
+// their size by the callers' conditions
+__device__ __forceinline__ void store4(float* p, const float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float4 v) {
+    uint2 u;
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    u.x = *reinterpret_cast<uint32_t*>(&lo);
+    u.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+__device__ __forceinline__ void store2(float* p, float a, float b) {
+    *reinterpret_cast<float2*>(p) = make_float2(a, b);
+}
+__device__ __forceinline__ void store2(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+// silu(g) * u as the reference writes it (src/kernels_cuda/silu_and_mul.cu:7-23).
+__device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+// The same for a result that is rounded to bfloat16 anyway: the fast exponential
+// and division are a few units in the last place of 32 bits off, far below that
+// rounding; their limits at large |g| are the function's own (0 and g).
+template <typename TO>
+__device__ __forceinline__ float silu_mul_for(float g, float u) {
+    if constexpr (sizeof(TO) == 2) return __fdividef(g, 1.0f + __expf(-g)) * u;
+    else return silu_mul(g, u);
+}
+
 // Sum over the 32 lanes in a fixed butterfly order; every lane gets the total.
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -85,10 +85,8 @@ __global__ void rmsnorm_kernel(const float* x, const TD* __restrict__ delta,
         for (int c = threadIdx.x; c < H / 4; c += blockDim.x) {
             const float4 t = reinterpret_cast<const float4*>(row_buf)[c];
             const float4 ww = reinterpret_cast<const float4*>(w)[c];
-            st<TO>(orow, 4 * c, (t.x * r) * (w_offset + ww.x));
-            st<TO>(orow, 4 * c + 1, (t.y * r) * (w_offset + ww.y));
-            st<TO>(orow, 4 * c + 2, (t.z * r) * (w_offset + ww.z));
-            st<TO>(orow, 4 * c + 3, (t.w * r) * (w_offset + ww.w));
+            store4(orow + 4 * c, make_float4((t.x * r) * (w_offset + ww.x), (t.y * r) * (w_offset + ww.y),
+                                             (t.z * r) * (w_offset + ww.z), (t.w * r) * (w_offset + ww.w)));
         }
     } else {
         for (int c = threadIdx.x; c < H; c += blockDim.x)
@@ -109,54 +107,70 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
         const size_t r = i / I, c = i % I;
         const float g = ld<T>(gu, r * 2 * I + (alternating ? 2 * c : c));
         const float u = ld<T>(gu, r * 2 * I + (alternating ? 2 * c + 1 : I + c));
-        st<T>(out, i, (g / (1.0f + expf(-g))) * u);
+        st<T>(out, i, silu_mul_for<T>(g, u));
     }
 }
 
-// bfloat16, I a multiple of 8: eight outputs a thread, 16-byte loads and stores
-__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu,
-                                     __nv_bfloat16* __restrict__ out, int R, int I, int alternating) {
+// bfloat16, I a multiple of 8: eight outputs a thread and step, 16-byte loads and
+// stores, two steps' loads in flight.  With alternating pairs a row's 2I inputs
+// and I outputs are contiguous and rows follow one another, so output pack i
+// comes from input elements [16 i, 16 i + 16).
+__device__ __forceinline__ uint4 swiglu8(const uint4 a, const uint4 b, bool alternating) {
+    const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+    uint4 o;
+    __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+    if (alternating) {  // a = g0 u0 g1 u1 g2 u2 g3 u3, b = g4 u4 ...
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const float2 p0 = __bfloat1622float2(pa[2 * j]), p1 = __bfloat1622float2(pa[2 * j + 1]);
+            const float2 q0 = __bfloat1622float2(pb[2 * j]), q1 = __bfloat1622float2(pb[2 * j + 1]);
+            po[j] = __floats2bfloat162_rn(silu_mul_for<__nv_bfloat16>(p0.x, p0.y),
+                                          silu_mul_for<__nv_bfloat16>(p1.x, p1.y));
+            po[2 + j] = __floats2bfloat162_rn(silu_mul_for<__nv_bfloat16>(q0.x, q0.y),
+                                              silu_mul_for<__nv_bfloat16>(q1.x, q1.y));
+        }
+    } else {  // a = eight gates, b = their ups
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 g = __bfloat1622float2(pa[j]), up = __bfloat1622float2(pb[j]);
+            po[j] = __floats2bfloat162_rn(silu_mul_for<__nv_bfloat16>(g.x, up.x),
+                                          silu_mul_for<__nv_bfloat16>(g.y, up.y));
+        }
+    }
+    return o;
+}
+
+__global__ void __launch_bounds__(256)
+swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int R, int I,
+                     int alternating) {
     pdl_prologue();
     const size_t n8 = (size_t)R * (I / 8);
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
-         i += (size_t)gridDim.x * blockDim.x) {
-        const size_t r = i / (I / 8), c = (i % (I / 8)) * 8;
-        const __nv_bfloat16* row = gu + r * 2 * I;
-        float g[8], u[8];
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    const unsigned i8 = (unsigned)(I / 8);
+    auto sources = [&](size_t i, const uint4*& a, const uint4*& b) {
         if (alternating) {
-            const uint4 a = *reinterpret_cast<const uint4*>(row + 2 * c);
-            const uint4 b = *reinterpret_cast<const uint4*>(row + 2 * c + 8);
-            const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
-            const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 fa = __bfloat1622float2(pa[j]), fb = __bfloat1622float2(pb[j]);
-                g[j] = fa.x;
-                u[j] = fa.y;
-                g[4 + j] = fb.x;
-                u[4 + j] = fb.y;
-            }
+            a = reinterpret_cast<const uint4*>(gu + 16 * i);
+            b = a + 1;
         } else {
-            const uint4 a = *reinterpret_cast<const uint4*>(row + c);
-            const uint4 b = *reinterpret_cast<const uint4*>(row + I + c);
-            const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
-            const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 fa = __bfloat1622float2(pa[j]), fb = __bfloat1622float2(pb[j]);
-                g[2 * j] = fa.x;
-                g[2 * j + 1] = fa.y;
-                u[2 * j] = fb.x;
-                u[2 * j + 1] = fb.y;
-            }
+            const size_t r = i / i8, c = (i - r * i8) * 8;
+            a = reinterpret_cast<const uint4*>(gu + r * 2 * I + c);
+            b = reinterpret_cast<const uint4*>(gu + r * 2 * I + I + c);
         }
-        uint4 o;
-        __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-            po[j] = __floats2bfloat162_rn((g[2 * j] / (1.0f + expf(-g[2 * j]))) * u[2 * j],
-                                          (g[2 * j + 1] / (1.0f + expf(-g[2 * j + 1]))) * u[2 * j + 1]);
-        *reinterpret_cast<uint4*>(out + r * I + c) = o;
+    };
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + step < n8; i += 2 * step) {
+        const uint4 *a0, *b0, *a1, *b1;
+        sources(i, a0, b0);
+        sources(i + step, a1, b1);
+        const uint4 va0 = *a0, vb0 = *b0, va1 = *a1, vb1 = *b1;
+        *reinterpret_cast<uint4*>(out + 8 * i) = swiglu8(va0, vb0, alternating);
+        *reinterpret_cast<uint4*>(out + 8 * (i + step)) = swiglu8(va1, vb1, alternating);
+    }
+    if (i < n8) {
+        const uint4 *a0, *b0;
+        sources(i, a0, b0);
+        *reinterpret_cast<uint4*>(out + 8 * i) = swiglu8(*a0, *b0, alternating);
     }
 }
 
@@ -242,7 +256,7 @@ extern "C" int rfx_swiglu(const void* gate_up, void* out, int dt, int R, int I, 
     else if (dt == RFX_DT_BF16 && I % 8 == 0 &&
              ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
         int b8 = (int)((n / 8 + 255) / 256);
-        if (b8 > 148 * 16) b8 = 148 * 16;
+        if (b8 > 148 * 8) b8 = 148 * 8;
         RFX_LAUNCH(swiglu_bf16x8_kernel, b8, 256, 0, s, (const __nv_bfloat16*)gate_up,
                    (__nv_bfloat16*)out, R, I, alternating);
     } else if (dt == RFX_DT_BF16)

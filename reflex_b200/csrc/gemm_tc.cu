@@ -87,32 +87,11 @@ struct Fuse {
 // up_j) and y[r, j] = silu(gate_j) * up_j, so the SwiGLU activation costs no
 // launch and no round trip of the [R, 2I] intermediate
 // (src/kernels_cuda/silu_and_mul.cu:7-23 is the reference's separate kernel).
-__device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
-// The same for a result that is rounded to bfloat16 anyway: the fast exponential
-// and division are a few units in the last place of 32 bits off, far below that
-// rounding; their limits at large |g| are the function's own (0 and g).
-template <typename TO>
-__device__ __forceinline__ float silu_mul_for(float g, float u) {
-    if constexpr (sizeof(TO) == 2) return __fdividef(g, 1.0f + __expf(-g)) * u;
-    else return silu_mul(g, u);
-}
+using rfx::silu_mul;
+using rfx::silu_mul_for;
 
-// four (two) neighbouring results in one access; the address is a multiple of
-// their size by the callers' conditions
-__device__ __forceinline__ void store4(float* p, const float4 v) { *reinterpret_cast<float4*>(p) = v; }
-__device__ __forceinline__ void store4(__nv_bfloat16* p, const float4 v) {
-    uint2 u;
-    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
-    u.x = *reinterpret_cast<uint32_t*>(&lo);
-    u.y = *reinterpret_cast<uint32_t*>(&hi);
-    *reinterpret_cast<uint2*>(p) = u;
-}
-__device__ __forceinline__ void store2(float* p, float a, float b) {
-    *reinterpret_cast<float2*>(p) = make_float2(a, b);
-}
-__device__ __forceinline__ void store2(__nv_bfloat16* p, float a, float b) {
-    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
-}
+using rfx::store2;
+using rfx::store4;
 
 template <int BN, typename TO, int EPI, bool PRO>
 __global__ void __launch_bounds__(THREADS)

@@ -25,15 +25,213 @@ struct alignas(sizeof(T) * N <= 16 ? sizeof(T) * N : 16) Pack {
     T a[N];
 };
 
-// PER: elements of a head vector per lane, head_dim <= 32 * PER.
-// VEC: head_dim == 32 * PER and a lane holds PER neighbouring elements, moved
-// with one wide access; a rotary pair (e, e + rd/2) then lies in two lanes at
-// the same place of their packs and is exchanged by a shuffle (rd/2 a multiple
-// of PER).  What a lane needs for every head of the row (its norm weights, its
-// sines and cosines, the row's place in the cache) is fetched once per block.
-// Otherwise lane l holds elements l, l + 32, ... and the pair is exchanged
-// through shared memory.
-template <typename TI, typename TO, int PER, bool VEC>
+// Unpacking and packing a lane's elements; 16-bit floats are converted in pairs.
+template <typename T, int N>
+__device__ __forceinline__ void unpack(const Pack<T, N>& p, float (&v)[N]) {
+    if constexpr (sizeof(T) == 2) {
+#pragma unroll
+        for (int i = 0; i < N; i += 2) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&p.a[i]));
+            v[i] = f.x;
+            v[i + 1] = f.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) v[i] = p.a[i];
+    }
+}
+template <typename T, int N>
+__device__ __forceinline__ void pack(const float (&v)[N], Pack<T, N>& p) {
+    if constexpr (sizeof(T) == 2) {
+#pragma unroll
+        for (int i = 0; i < N; i += 2)
+            *reinterpret_cast<__nv_bfloat162*>(&p.a[i]) = __floats2bfloat162_rn(v[i], v[i + 1]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) p.a[i] = v[i];
+    }
+}
+
+// The wide form, for head sizes that are a power of two.  A head vector lies in
+// LPH neighbouring lanes, PER neighbouring elements each (head_dim = LPH * PER),
+// moved with one wide access; a warp takes 32 / LPH heads of one kind (query, key
+// or value) at a time, a "unit".  A rotary pair (e, e + rd/2) lies in two lanes of
+// the head's group at the same place of their packs and is exchanged by a shuffle
+// (rd/2 a multiple of PER).  What a lane needs for every head of the row (its norm
+// weights, its sines and cosines, the row's place in the cache) is fetched once
+// per block.  The mean is taken by a multiplication with 1/head_dim, which for a
+// power of two gives the quotient's bits.
+template <typename TI, typename TO, int PER, int LPH>
+__global__ void __launch_bounds__(256, 4)
+qkv_post_wide_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restrict__ q_w,
+                     const float* __restrict__ k_w, float eps, float w_offset,
+                     const float* __restrict__ rope_denom, int rotary_dim,
+                     const int* __restrict__ row_pos, const int* __restrict__ row_slot,
+                     TO* __restrict__ q_out, TO* __restrict__ k_pages, TO* __restrict__ v_pages,
+                     PagedKV cache, int nq, int nkv_in, int dry_pass) {
+    extern __shared__ float smem[];  // cos[half], sin[half]
+    pdl_launch_dependents();
+    constexpr int D = PER * LPH;
+    constexpr int HPW = 32 / LPH;  // heads a warp takes at a time
+    constexpr int CH = 3;          // units whose loads are in flight together
+    constexpr float inv_d = 1.0f / (float)D;
+    const int r = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int half = rotary_dim / 2;
+    const bool rotate = rope_denom != nullptr && half > 0;
+    const int sub = lane / LPH;          // which of the unit's heads
+    const int e0 = (lane % LPH) * PER;   // this lane's first element of the head
+    const bool turns = rotate && e0 < rotary_dim;  // a pack lies on one side of the rotation
+    const bool low = e0 < half;
+    const int hl = half / PER;  // lanes in half a rotation
+    const int partner = turns ? (low ? lane + hl : lane - hl) : lane;
+    // units: the query heads in groups of HPW, then the key heads, then the value heads
+    const int uq = (nq + HPW - 1) / HPW, ukv = (nkv_in + HPW - 1) / HPW;
+    const int units = uq + 2 * ukv;
+    const int stride = gridDim.y * nwarps;
+    const int first = blockIdx.y * nwarps + warp;
+
+    // what a lane needs for every head of the row, filled in by `prepare`
+    float sn[PER], cs[PER], wq[PER];  // (the few key heads fetch their weights when they come)
+    size_t kv0 = 0;
+    const size_t kv_head_stride = (size_t)cache.page_size * D;
+
+    // The rotation of the row's position, once for all heads of the block, the
+    // norm weights and the row's place in the cache.  Positions are the step's
+    // inputs, so none of this waits for the preceding kernel.
+    auto prepare = [&]() {
+        const int pos = row_pos[r];
+        const int slot = row_slot[r];
+        float* cs_tab = smem;
+        float* sn_tab = cs_tab + half;
+        if (rotate) {
+            for (int i = threadIdx.x; i < half; i += blockDim.x) {
+                const float theta = (float)pos / rope_denom[i];
+                sincosf(theta, &sn_tab[i], &cs_tab[i]);
+            }
+        }
+        // head 0's place; the other heads lie a tile apart
+        kv0 = nkv_in > 0 ? kv_offset(cache, slot, pos, 0) : 0;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) sn[i] = cs[i] = wq[i] = 0.0f;
+        if (q_w) unpack(*reinterpret_cast<const Pack<float, PER>*>(q_w + e0), wq);
+#pragma unroll
+        for (int i = 0; i < PER; ++i) wq[i] += w_offset;
+        __syncthreads();
+        if (turns) {
+            unpack(*reinterpret_cast<const Pack<float, PER>*>(sn_tab + (low ? e0 : e0 - half)), sn);
+            unpack(*reinterpret_cast<const Pack<float, PER>*>(cs_tab + (low ? e0 : e0 - half)), cs);
+        }
+        if (low) {  // the lower half subtracts the partner's product: the sign goes into the sine
+#pragma unroll
+            for (int i = 0; i < PER; ++i) sn[i] = -sn[i];
+        }
+    };
+
+    // kind of unit u (the same for the whole warp) and this lane's head in it
+    auto unit_kind = [&](int u) { return u < uq ? 0 : (u < uq + ukv ? 1 : 2); };
+    // the loads of up to CH units, from `src_row` (the row of qkv, or the dry source)
+    auto fetch = [&](int u0, Pack<TI, PER> (&in)[CH], int (&head)[CH], bool dry, const TI* dry_src) {
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            const int u = u0 + c * stride;
+            head[c] = -1;  // nothing for this lane
+            if (u < units && !(dry && c > 0)) {
+                const int k = unit_kind(u);
+                const int h = (k == 0 ? u : (k == 1 ? u - uq : u - uq - ukv)) * HPW + sub;
+                if (h < (k == 0 ? nq : nkv_in)) {
+                    head[c] = h;
+                    const int hh = k == 0 ? h : (k == 1 ? nq + h : nq + nkv_in + h);
+                    const TI* src = dry ? dry_src : qkv + (size_t)r * row_stride + (size_t)hh * D;
+                    in[c] = *reinterpret_cast<const Pack<TI, PER>*>(src + e0);
+                }
+            }
+        }
+    };
+    auto finish = [&](int u0, const Pack<TI, PER> (&in)[CH], const int (&head)[CH], bool dry) {
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            const int u = u0 + c * stride;
+            if (u >= units || (dry && c > 0)) break;
+            const int k = unit_kind(u);
+            float v[PER];
+            if (head[c] >= 0) {
+                unpack(in[c], v);
+            } else {
+#pragma unroll
+                for (int i = 0; i < PER; ++i) v[i] = 0.0f;
+            }
+            if (k < 2) {
+                if (k == 0 ? q_w != nullptr : k_w != nullptr) {
+                    float ss = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < PER; ++i) ss = fmaf(v[i], v[i], ss);
+#pragma unroll
+                    for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                    const float rinv = 1.0f / sqrtf(ss * inv_d + eps);
+                    if (k == 0) {
+#pragma unroll
+                        for (int i = 0; i < PER; ++i) v[i] = (v[i] * rinv) * wq[i];
+                    } else {
+                        float wk[PER];
+                        unpack(*reinterpret_cast<const Pack<float, PER>*>(k_w + e0), wk);
+#pragma unroll
+                        for (int i = 0; i < PER; ++i) v[i] = (v[i] * rinv) * (w_offset + wk[i]);
+                    }
+                }
+                if (rotate) {
+#pragma unroll
+                    for (int i = 0; i < PER; ++i) {
+                        const float other = __shfl_sync(0xffffffffu, v[i], partner);
+                        // low: v cos - other sin;  high: other sin + v cos
+                        if (turns) v[i] = fmaf(other, sn[i], v[i] * cs[i]);
+                    }
+                }
+            }
+            if (head[c] >= 0 && !dry) {
+                TO* dst = (k == 0 ? q_out + ((size_t)r * nq + head[c]) * D
+                                  : (k == 1 ? k_pages : v_pages) + kv0 + (size_t)head[c] * kv_head_stride) + e0;
+                Pack<TO, PER> o;
+                pack(v, o);
+                *reinterpret_cast<Pack<TO, PER>*>(dst) = o;
+            }
+        }
+    };
+
+    Pack<TI, PER> in[CH];
+    int head[CH];
+    int u0 = first;
+    const TI* dry_src = reinterpret_cast<const TI*>(q_w ? q_w : k_w);
+    if (dry_src && dry_pass) {
+        // Decode-sized launches: the row's tables first, then a dry pass before the
+        // wait on the preceding kernel.  It takes a norm weight vector for its input
+        // (never the other kernel's output), does one unit and stores nothing; it
+        // brings the instructions into the cache.
+        prepare();
+        if (u0 < units) {
+            fetch(u0, in, head, true, dry_src);
+            finish(u0, in, head, true);
+        }
+        pdl_wait();
+    } else {
+        // Many rows: the row's first loads are issued before its tables are made.
+        pdl_wait();
+        if (u0 < units) fetch(u0, in, head, false, nullptr);
+        prepare();
+        if (u0 < units) finish(u0, in, head, false);
+        u0 += stride * CH;
+    }
+#pragma unroll 1
+    for (; u0 < units; u0 += stride * CH) {
+        fetch(u0, in, head, false, nullptr);
+        finish(u0, in, head, false);
+    }
+}
+
+// The general form.  PER: elements of a head vector per lane, head_dim <= 32 * PER;
+// lane l holds elements l, l + 32, ... and a rotary pair is exchanged through
+// shared memory.  One warp per (row, head).
+template <typename TI, typename TO, int PER>
 __global__ void __launch_bounds__(256)
 qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restrict__ q_w,
                 const float* __restrict__ k_w, float eps, float w_offset,
@@ -83,71 +281,6 @@ qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restr
     for (int pass = (dry_src && dry_pass) ? 0 : 1; pass < 2; ++pass) {
         const bool dry = pass == 0;
         if (!dry) pdl_wait();
-        if constexpr (VEC) {
-            // this lane's share of what every head of the row needs
-            const int e0 = lane * PER;
-            const bool turns = rotate && e0 < rotary_dim;  // a pack lies on one side of the rotation
-            const bool low = e0 < half;
-            const int hl = half / PER;  // lanes in half a rotation
-            const int partner = (low ? lane + hl : lane - hl) & 31;
-            Pack<float, PER> sn, cs, wq, wk;
-#pragma unroll
-            for (int i = 0; i < PER; ++i) sn.a[i] = cs.a[i] = wq.a[i] = wk.a[i] = 0.0f;
-            if (turns) {
-                sn = *reinterpret_cast<const Pack<float, PER>*>(sn_tab + (low ? e0 : e0 - half));
-                cs = *reinterpret_cast<const Pack<float, PER>*>(cs_tab + (low ? e0 : e0 - half));
-            }
-            if (q_w) wq = *reinterpret_cast<const Pack<float, PER>*>(q_w + e0);
-            if (k_w) wk = *reinterpret_cast<const Pack<float, PER>*>(k_w + e0);
-            // three heads at a time: their loads first, so that the latencies
-            // overlap, then the arithmetic
-            constexpr int CH = 3;
-            for (int hh0 = blockIdx.y * nwarps + warp; hh0 < total; hh0 += stride * CH) {
-                Pack<TI, PER> in[CH];
-#pragma unroll
-                for (int c = 0; c < CH; ++c) {
-                    const int hh = hh0 + c * stride;
-                    if (hh < total && !(dry && c > 0)) {
-                        const TI* src = dry ? dry_src : qkv + (size_t)r * row_stride + (size_t)hh * d;
-                        in[c] = *reinterpret_cast<const Pack<TI, PER>*>(src + e0);
-                    }
-                }
-#pragma unroll
-                for (int c = 0; c < CH; ++c) {
-                    const int hh = hh0 + c * stride;
-                    if (hh >= total || (dry && c > 0)) break;
-                    const bool is_q = hh < nq, is_k = !is_q && hh < nq + nkv_in;
-                    float v[PER];
-#pragma unroll
-                    for (int i = 0; i < PER; ++i) v[i] = ld<TI>(in[c].a, i);
-                    if (is_q || is_k) {
-                        if (is_q ? q_w != nullptr : k_w != nullptr) {
-                            float ss = 0.0f;
-#pragma unroll
-                            for (int i = 0; i < PER; ++i) ss = fmaf(v[i], v[i], ss);
-                            const float rinv = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);
-#pragma unroll
-                            for (int i = 0; i < PER; ++i)
-                                v[i] = (v[i] * rinv) * (w_offset + (is_q ? wq.a[i] : wk.a[i]));
-                        }
-                        if (rotate) {
-#pragma unroll
-                            for (int i = 0; i < PER; ++i) {
-                                const float other = __shfl_sync(0xffffffffu, v[i], partner);
-                                if (turns)
-                                    v[i] = low ? v[i] * cs.a[i] - other * sn.a[i] : other * sn.a[i] + v[i] * cs.a[i];
-                            }
-                        }
-                    }
-                    Pack<TO, PER> o;
-#pragma unroll
-                    for (int i = 0; i < PER; ++i) st<TO>(o.a, i, v[i]);
-                    if (!dry) *reinterpret_cast<Pack<TO, PER>*>(destination(hh) + e0) = o;
-                }
-                if (dry) break;
-            }
-            continue;  // the next pass
-        }
         // one warp per (row, head): blockIdx.y walks the heads in groups of nwarps
         for (int hh = blockIdx.y * nwarps + warp; hh < total; hh += stride) {
             if (dry && hh >= stride) break;
@@ -221,50 +354,82 @@ extern "C" int rfx_qkv_post(const void* qkv, int in_dt, int row_stride, const fl
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return RFX_ERR_BAD_ARG;
     if (nkv_in != 0 && nkv_in != nkv) return RFX_ERR_BAD_ARG;
     PagedKV cache{page_table, max_pages, page_size, nkv, head_dim};
-    const int threads = 256;  // eight heads at a time
+    const int threads = 256;
+    const int warps = threads / 32;
     cudaStream_t s = (cudaStream_t)stream;
     // Few rows (decode): a row's heads spread over several blocks, with a dry
     // pass.  Many rows (prefill): one block a row, and no dry pass (the code is
     // warm after the first blocks).
     const bool many = R >= 256;
-    int head_blocks = many ? 1 : (nq + 2 * nkv_in + threads / 32 - 1) / (threads / 32);
-    const size_t smem = ((size_t)(threads / 32) * head_dim + rotary_dim) * sizeof(float);
-    dim3 grid(R, head_blocks < 65535 ? head_blocks : 65535);
     const int dry_pass = many ? 0 : 1;
-    // the wide-access form: a whole head in 32 lanes' packs, pairs a whole number of lanes apart
-    const int per = head_dim / 32;
+    const int in_size = in_dt == RFX_DT_F32 ? 4 : 2;
+    // the wide form: a power of two of elements, 16 bytes of the input a lane where 32 lanes reach
+    const bool pow2 = head_dim >= 16 && (head_dim & (head_dim - 1)) == 0;
+    int per = 16 / in_size;
+    if (pow2 && head_dim / per > 32) per = head_dim / 32;
+    const int lph = pow2 ? head_dim / per : 0;
     const uintptr_t ptrs = reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
                            reinterpret_cast<uintptr_t>(k_pages) | reinterpret_cast<uintptr_t>(v_pages) |
                            reinterpret_cast<uintptr_t>(q_w) | reinterpret_cast<uintptr_t>(k_w);
-    const bool vec = head_dim % 32 == 0 && (per == 1 || per == 2 || per == 4 || per == 8 || per == 16) &&
-                     (rope_denom == nullptr || rotary_dim == 0 || (rotary_dim / 2) % per == 0) &&
-                     row_stride % per == 0 && (ptrs & 15) == 0;
-#define RFX_POST_P(TI, TO, P)                                                                      \
-    do {                                                                                           \
-        if (vec)                                                                                   \
-            RFX_LAUNCH((qkv_post_kernel<TI, TO, P, true>), grid, threads, smem, s, (const TI*)qkv, \
-                       row_stride, q_w, k_w, eps, w_offset, rope_denom, rotary_dim, row_pos,       \
-                       row_slot, (TO*)q_out, (TO*)k_pages, (TO*)v_pages, cache, nq, nkv_in,          \
-                       dry_pass);                                                          \
-        else                                                                                       \
-            RFX_LAUNCH((qkv_post_kernel<TI, TO, P, false>), grid, threads, smem, s, (const TI*)qkv, \
-                       row_stride, q_w, k_w, eps, w_offset, rope_denom, rotary_dim, row_pos,       \
-                       row_slot, (TO*)q_out, (TO*)k_pages, (TO*)v_pages, cache, nq, nkv_in,          \
-                       dry_pass);                                                          \
+    const bool wide = pow2 && (rope_denom == nullptr || rotary_dim == 0 || (rotary_dim / 2) % per == 0) &&
+                      row_stride % per == 0 && (ptrs & 15) == 0;
+#define RFX_POST_ARGS(TI, TO)                                                                       \
+    (const TI*)qkv, row_stride, q_w, k_w, eps, w_offset, rope_denom, rotary_dim, row_pos, row_slot, \
+        (TO*)q_out, (TO*)k_pages, (TO*)v_pages, cache, nq, nkv_in, dry_pass
+    if (wide) {
+        const int hpw = 32 / lph;
+        const int units = (nq + hpw - 1) / hpw + 2 * ((nkv_in + hpw - 1) / hpw);
+        const int unit_blocks = many ? 1 : (units + warps - 1) / warps;
+        dim3 grid(R, unit_blocks < 65535 ? unit_blocks : 65535);
+        const size_t smem = (size_t)rotary_dim * sizeof(float);
+#define RFX_WIDE(TI, TO, P, L)                                                                    \
+    RFX_LAUNCH((qkv_post_wide_kernel<TI, TO, P, L>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO))
+#define RFX_WIDE_32(TI, TO)  /* 32-bit input: 4 elements are 16 bytes */   \
+    do {                                                                  \
+        if (per == 4 && lph == 4) RFX_WIDE(TI, TO, 4, 4);                 \
+        else if (per == 4 && lph == 8) RFX_WIDE(TI, TO, 4, 8);            \
+        else if (per == 4 && lph == 16) RFX_WIDE(TI, TO, 4, 16);          \
+        else if (per == 4 && lph == 32) RFX_WIDE(TI, TO, 4, 32);          \
+        else if (per == 8 && lph == 32) RFX_WIDE(TI, TO, 8, 32);          \
+        else if (per == 16 && lph == 32) RFX_WIDE(TI, TO, 16, 32);        \
+        else return RFX_ERR_UNSUPPORTED;                                  \
     } while (0)
-#define RFX_POST(TI, TO)                                  \
-    do {                                                  \
-        if (head_dim <= 32) RFX_POST_P(TI, TO, 1);        \
-        else if (head_dim <= 64) RFX_POST_P(TI, TO, 2);   \
-        else if (head_dim <= 128) RFX_POST_P(TI, TO, 4);  \
-        else if (head_dim <= 256) RFX_POST_P(TI, TO, 8);  \
-        else RFX_POST_P(TI, TO, 16);                      \
+#define RFX_WIDE_16(TI, TO)  /* 16-bit input: 8 elements are 16 bytes */   \
+    do {                                                                  \
+        if (per == 8 && lph == 2) RFX_WIDE(TI, TO, 8, 2);                 \
+        else if (per == 8 && lph == 4) RFX_WIDE(TI, TO, 8, 4);            \
+        else if (per == 8 && lph == 8) RFX_WIDE(TI, TO, 8, 8);            \
+        else if (per == 8 && lph == 16) RFX_WIDE(TI, TO, 8, 16);          \
+        else if (per == 8 && lph == 32) RFX_WIDE(TI, TO, 8, 32);          \
+        else if (per == 16 && lph == 32) RFX_WIDE(TI, TO, 16, 32);        \
+        else return RFX_ERR_UNSUPPORTED;                                  \
+    } while (0)
+        if (in_dt == RFX_DT_F32 && out_dt == RFX_DT_F32) RFX_WIDE_32(float, float);
+        else if (in_dt == RFX_DT_F32 && out_dt == RFX_DT_BF16) RFX_WIDE_32(float, __nv_bfloat16);
+        else if (in_dt == RFX_DT_BF16 && out_dt == RFX_DT_BF16) RFX_WIDE_16(__nv_bfloat16, __nv_bfloat16);
+        else return RFX_ERR_BAD_ARG;
+#undef RFX_WIDE_32
+#undef RFX_WIDE_16
+#undef RFX_WIDE
+        return 0;
+    }
+    // the general form: a warp per head, eight heads at a time
+    const int head_blocks = many ? 1 : (nq + 2 * nkv_in + warps - 1) / warps;
+    const size_t smem = ((size_t)warps * head_dim + rotary_dim) * sizeof(float);
+    dim3 grid(R, head_blocks < 65535 ? head_blocks : 65535);
+#define RFX_POST(TI, TO)                                                                              \
+    do {                                                                                              \
+        if (head_dim <= 32) RFX_LAUNCH((qkv_post_kernel<TI, TO, 1>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO));        \
+        else if (head_dim <= 64) RFX_LAUNCH((qkv_post_kernel<TI, TO, 2>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO));   \
+        else if (head_dim <= 128) RFX_LAUNCH((qkv_post_kernel<TI, TO, 4>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO));  \
+        else if (head_dim <= 256) RFX_LAUNCH((qkv_post_kernel<TI, TO, 8>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO));  \
+        else RFX_LAUNCH((qkv_post_kernel<TI, TO, 16>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO));                      \
     } while (0)
     if (in_dt == RFX_DT_F32 && out_dt == RFX_DT_F32) RFX_POST(float, float);
     else if (in_dt == RFX_DT_F32 && out_dt == RFX_DT_BF16) RFX_POST(float, __nv_bfloat16);
     else if (in_dt == RFX_DT_BF16 && out_dt == RFX_DT_BF16) RFX_POST(__nv_bfloat16, __nv_bfloat16);
     else return RFX_ERR_BAD_ARG;
 #undef RFX_POST
-#undef RFX_POST_P
+#undef RFX_POST_ARGS
     return 0;
 }

@@ -56,6 +56,26 @@ def test_rmsnorm_with_add_gather_and_offset(R, H, out_dtype):
     assert torch.equal(xd.cpu(), x)
 
 
+@pytest.mark.parametrize("R,H", [(256, 64), (300, 100), (700, 4096), (1500, 5120), (257, 8200)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_of_many_rows(R, H, out_dtype):
+    """Many whole rows: the same bits as a gather of every row, and the plain norm."""
+    g = torch.Generator().manual_seed(R + H)
+    x = torch.randn(R, H, generator=g) * 3
+    x[R // 2] *= 50.0  # a row of another scale among its neighbours
+    w = 1 + 0.1 * torch.randn(H, generator=g)
+    eps = 1e-6
+    xd, wd = x.to(DEV), w.to(DEV)
+    out = ops().rmsnorm(xd, wd, eps, out_dtype, weight_offset=0.5)
+    every = torch.arange(R, dtype=torch.int32, device=DEV)
+    one_by_one = ops().rmsnorm(xd, wd, eps, out_dtype, rows=every, weight_offset=0.5)
+    assert torch.equal(out, one_by_one)
+    tol = 2e-6 if out_dtype == torch.float32 else 5e-3
+    ref = pm.rms_norm(x.double().numpy(), 0.5 + w.double().numpy(), eps)
+    for r in (0, R // 2, R - 1):
+        assert relerr(out[r], ref[r]) < tol
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_swiglu_embed_add(dtype):
     g = torch.Generator().manual_seed(1)

@@ -94,7 +94,12 @@ def load_model(model_dir: str, dtype: torch.dtype = torch.bfloat16, device="cuda
     try:
         check_names_and_shapes(spec, ckpt)
         model = CausalLM(spec, dtype, device)
-        model.bind(read_tensors(spec, ckpt))
+        tensors = read_tensors(spec, ckpt)
+        if torch.device(device).type == "cuda":
+            from .upload import upload_all
+
+            tensors = upload_all(tensors, device)  # through pinned staging, element types kept
+        model.bind(tensors)
     finally:
         ckpt.close()
     return model

@@ -36,7 +36,7 @@ from .sampling.params import SamplingParams  # noqa: E402,F401
 
 
 def __getattr__(name):
-    if name in ("Model", "System1Response", "System1CandidateResult"):
+    if name in ("Model", "EngineOptions", "System1Response", "System1CandidateResult", "resolve_weights"):
         from . import api
 
         return getattr(api, name)

@@ -23,6 +23,40 @@ _DTYPES = {"bf16": torch.bfloat16, "bfloat16": torch.bfloat16, "f32": torch.floa
            "float32": torch.float32, "fp32": torch.float32}
 
 
+def resolve_weights(flag: Optional[str] = None, default: str = "bf16") -> str:
+    """The weights option: `flag` if given, else the environment's
+    `REFLEX_WEIGHTS` if set and not empty, else `default`
+    (src/model/loading.rs:44-62; `check` passes "f32" as its default)."""
+    import os
+
+    if flag is not None:
+        if flag not in _DTYPES:
+            raise InvalidInput(f"weights must be one of {sorted(_DTYPES)}, got {flag!r}")
+        return flag
+    env = os.environ.get("REFLEX_WEIGHTS", "")
+    if env:
+        if env not in _DTYPES:
+            raise InvalidInput(f"REFLEX_WEIGHTS: weights must be one of {sorted(_DTYPES)}, got {env!r}")
+        return env
+    return default
+
+
+@dataclass
+class EngineOptions:
+    """What is fixed when a model is loaded (the reference's `LoadOptions`,
+    src/model/loading.rs:91-98, and its environment switches read once at load).
+    `weights` None: `REFLEX_WEIGHTS`, else bfloat16.  The cache's element type
+    follows the weights' (32-bit with "f32").  `max_tokens` sizes the cache
+    (tokens held by all live sequences, each rounded up to a page);
+    `max_batch` is the most sequences the generation loop runs together."""
+
+    weights: Optional[str] = None
+    device: str = "cuda:0"
+    max_tokens: int = 16384
+    max_batch: int = 64
+    use_graphs: bool = True
+
+
 @dataclass
 class System1CandidateResult:
     token_ids: List[int]
@@ -77,15 +111,24 @@ class Model:
         self.decode_ahead = True
 
     @classmethod
-    def load(cls, model_dir: str, weights: str = "bf16", device: str = "cuda:0", **kw) -> "Model":
+    def load(cls, model_dir: str, weights: Optional[str] = None, device: Optional[str] = None,
+             options: Optional[EngineOptions] = None, **kw) -> "Model":
         """`weights`: "bf16" (serving precision) or "f32" (everything in true
         32-bit), the role of the reference's `--weights f16|f32`
-        (src/model/loading.rs:44-62)."""
+        (src/model/loading.rs:44-62); None: `REFLEX_WEIGHTS`, else bfloat16.
+        `options` gives the same and the cache's size as one object; arguments
+        given beside it win."""
         from .weights.loader import load_model
 
-        if weights not in _DTYPES:
-            raise InvalidInput(f"weights must be one of {sorted(_DTYPES)}, got {weights!r}")
-        return cls(load_model(model_dir, _DTYPES[weights], device), **kw)
+        o = options or EngineOptions()
+        weights = resolve_weights(weights if weights is not None else o.weights)
+        device = device if device is not None else o.device
+        sizes = {"max_tokens": o.max_tokens, "max_batch": o.max_batch, "use_graphs": o.use_graphs}
+        unknown = set(kw) - set(sizes)
+        if unknown:
+            raise InvalidInput(f"unknown load options: {sorted(unknown)}")
+        sizes.update(kw)
+        return cls(load_model(model_dir, _DTYPES[weights], device), **sizes)
 
     @property
     def weights_dtype(self) -> str:

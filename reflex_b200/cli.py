@@ -74,6 +74,16 @@ class Args:
             fail(f"{flag} must be a number, got {self.values[flag]!r}")
 
 
+def resolve_weights(flag: Optional[str], default: str = "bf16") -> str:
+    from .api import resolve_weights as resolve
+    from .errors import InvalidInput
+
+    try:
+        return resolve(flag, default)
+    except InvalidInput as e:
+        fail(str(e))
+
+
 def _load(path: str, weights: str, **kw):
     from .api import Model
 
@@ -100,7 +110,7 @@ def cmd_generate(argv: List[str], t0: float) -> int:
         temperature=a.num("--temperature", float, 0.0), top_k=a.num("--top-k", int, None),
         top_p=a.num("--top-p", float, None), seed=a.num("--seed", int, None),
         stop_token_ids=tuple(parse_ids(a.values.get("--stop-ids", ""))))
-    model, load_ms = _load(path, a.values.get("--weights", "bf16"))
+    model, load_ms = _load(path, resolve_weights(a.values.get("--weights")))
     first = {}
     t_gen = time.perf_counter()
 
@@ -134,7 +144,7 @@ def cmd_system1(argv: List[str], t0: float) -> int:
     cands = [parse_ids(c) for c in a.multi.get("--candidate", [])]
     if not cands:
         fail("system1 requires at least one --candidate")
-    model, load_ms = _load(a.positional[0], a.values.get("--weights", "bf16"))
+    model, load_ms = _load(a.positional[0], resolve_weights(a.values.get("--weights")))
     resp = model.system1_evaluate(parse_ids(a.positional[1]), cands, a.num("--temperature", float, 1.0))
     total_ms = (time.perf_counter() - t0) * 1000.0
     for idx, (r, p) in enumerate(zip(resp.results, resp.probabilities)):
@@ -165,7 +175,7 @@ def cmd_check(argv: List[str], t0: float) -> int:
     a = Args(argv, {"--max-tokens", "--reference", "--tolerance", "--weights"}, set())
     if len(a.positional) < 2:
         fail(USAGE)
-    model, _ = _load(a.positional[0], a.values.get("--weights", "f32"))
+    model, _ = _load(a.positional[0], resolve_weights(a.values.get("--weights"), default="f32"))
     prompt = parse_ids(a.positional[1])
     n = a.num("--max-tokens", int, 16)
     logits = model.forward_prompt(prompt)[-1].double()
@@ -200,7 +210,7 @@ def cmd_bench(argv: List[str], t0: float) -> int:
     a = Args(argv, {"--warmup", "--iters", "--weights"}, set())
     if not a.positional:
         fail(USAGE)
-    model, load_ms = _load(a.positional[0], a.values.get("--weights", "bf16"))
+    model, load_ms = _load(a.positional[0], resolve_weights(a.values.get("--weights")))
     warmup, iters = a.num("--warmup", int, 2), a.num("--iters", int, 5)
     V = model.spec.vocab_size
     g = torch.Generator().manual_seed(0)

@@ -143,3 +143,29 @@ def test_run_time_switches_are_validated():
                                   "import reflex_b200.ops as o; o.decode_splits(1, 8, 8, 4)"],
                                  cwd=root, env=env, capture_output=True, text=True)
         assert res.returncode != 0 and "InvalidInput" in res.stderr and name in res.stderr, res.stderr
+
+
+def test_weights_option_flag_then_environment_then_default(monkeypatch):
+    """src/model/loading.rs:44-62: the flag wins, then REFLEX_WEIGHTS when set
+    and not empty, then the caller's default; a bad value names its source."""
+    from reflex_b200.api import EngineOptions, resolve_weights
+    from reflex_b200.errors import InvalidInput
+
+    monkeypatch.delenv("REFLEX_WEIGHTS", raising=False)
+    assert resolve_weights() == "bf16"
+    assert resolve_weights(default="f32") == "f32"
+    assert resolve_weights("f32") == "f32"
+    monkeypatch.setenv("REFLEX_WEIGHTS", "f32")
+    assert resolve_weights() == "f32"
+    assert resolve_weights("bf16") == "bf16"
+    monkeypatch.setenv("REFLEX_WEIGHTS", "")
+    assert resolve_weights() == "bf16"
+    monkeypatch.setenv("REFLEX_WEIGHTS", "f8")
+    with pytest.raises(InvalidInput) as e:
+        resolve_weights()
+    assert "REFLEX_WEIGHTS" in str(e.value)
+    assert resolve_weights("f32") == "f32"  # a flag is not affected by a bad environment
+    with pytest.raises(InvalidInput):
+        resolve_weights("f16")
+    o = EngineOptions()
+    assert (o.weights, o.max_tokens, o.max_batch, o.use_graphs) == (None, 16384, 64, True)

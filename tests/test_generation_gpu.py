@@ -55,6 +55,25 @@ def test_greedy_generation_of_an_unequal_batch(name, weights):
     assert one == got[1][:3]  # alone or in a batch: the same tokens
 
 
+def test_load_options_as_one_object_and_from_the_environment(monkeypatch):
+    import reflex_b200
+    from reflex_b200 import EngineOptions, InvalidInput
+
+    folder = helpers.model_folder("A", 7, "float32")
+    prompt = helpers.random_tokens(9, ALL["A"]["vocab_size"], 3)
+    want, _ = plain_generate(folder, prompt, 4, lambda l, s: pm.argmax_last(l))
+    model = reflex_b200.Model.load(folder, options=EngineOptions(weights="f32", max_tokens=256, max_batch=2,
+                                                                 use_graphs=False))
+    assert model.weights_dtype == "f32" and model.max_batch == 2
+    assert model.generate(prompt, 4) == want
+    # an argument beside the options wins; the environment fills in when neither names the weights
+    assert reflex_b200.Model.load(folder, weights="bf16", options=EngineOptions(weights="f32")).weights_dtype == "bf16"
+    monkeypatch.setenv("REFLEX_WEIGHTS", "f32")
+    assert reflex_b200.Model.load(folder, max_tokens=256).weights_dtype == "f32"
+    with pytest.raises(InvalidInput):
+        reflex_b200.Model.load(folder, max_slots=3)
+
+
 def test_sampled_generation_follows_the_plain_sampler_with_the_same_uniforms():
     import reflex_b200
     from reflex_b200.sampling import uniform

@@ -84,7 +84,10 @@ int main(int argc, char** argv) {
 
 
 def main() -> int:
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        print("usage: make_elementwise_golden.py <checkout of the reference>", file=sys.stderr)
+        return 2
+    ref = sys.argv[1]
     kdir = os.path.join(ref, "src", "kernels_cuda")
     tmp = tempfile.mkdtemp()
     src = os.path.join(tmp, "shim.cpp")

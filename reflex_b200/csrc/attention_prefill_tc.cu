@@ -45,6 +45,14 @@ __device__ __forceinline__ void trace_mark(int which) {
     g_trace[(size_t)cta * 32 + which] = t;
 }
 
+// a raw value (cycles spent in a wait, summed) instead of a timestamp
+__device__ __forceinline__ void trace_value(int which, long long v) {
+    if (g_trace == nullptr) return;
+    const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    if (cta >= g_trace_ctas) return;
+    g_trace[(size_t)cta * 32 + which] = (unsigned long long)v;
+}
+
 using namespace sm100;
 using rfx::PagedKV;
 
@@ -196,14 +204,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         if (elect_one()) {
             constexpr uint32_t idesc_s = umma_idesc_bf16(ROWS, PAGE);  // S: N = 64 keys
             constexpr uint32_t idesc_o = idesc_b_mn(ROWS, D);          // O: N = D, V is MN-major
+            const bool tracing = g_trace != nullptr;
+            long long wait_k = 0, wait_p = 0, wait_v = 0, c0 = 0;
             bool ok = mbar_wait(&q_full, 0);
             if (!ok) { atomicExch(err, 13); abort_flag = 1; }
             auto pv = [&](int i) -> bool {
                 const int b = i & 1, s = i % KV_STAGES;
                 const uint32_t ph2 = (i >> 1) & 1, phs = (i / KV_STAGES) & 1;
                 // P_i is delivered after any rescaling of O that page i asked for
+                if (tracing) c0 = clock64();
                 if (!mbar_wait(&p_full[b], ph2)) { atomicExch(err, 14); return false; }
+                if (tracing) { const long long c1 = clock64(); wait_p += c1 - c0; c0 = c1; }
                 if (!mbar_wait(&v_full[s], phs)) { atomicExch(err, 15); return false; }
+                if (tracing) wait_v += clock64() - c0;
                 tc_fence_after_sync();
                 const uint32_t va = smem_u32(v_ring + s * KV_BYTES);
 #pragma unroll
@@ -221,7 +234,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                 const uint32_t phs = (j / KV_STAGES) & 1;
                 // S_j reuses the columns of S_{j-2} and P_{j-2}: PV_{j-2} was issued
                 // before this and the tensor core runs MMAs in issue order
+                if (tracing) c0 = clock64();
                 if (!mbar_wait(&k_full[s], phs)) { atomicExch(err, 18); ok = false; break; }
+                if (tracing) wait_k += clock64() - c0;
                 tc_fence_after_sync();
                 const uint32_t qa = smem_u32(q_tile), ka = smem_u32(k_ring + s * KV_BYTES);
 #pragma unroll
@@ -238,6 +253,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             }
             if (ok && n_pages > 0) ok = pv(n_pages - 1);
             if (!ok) abort_flag = 1;
+            if (tracing) {
+                trace_value(8, wait_k);
+                trace_value(9, wait_p);
+                trace_value(10, wait_v);
+            }
         }
         __syncwarp();
     } else {
@@ -253,11 +273,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         constexpr float RAISE = 8.0f;  // raise the reference maximum only past 2^8
         float m = -INFINITY, l = 0.0f;
         bool ok = true;
+        const bool tracing = g_trace != nullptr && t == 0;
+        long long wait_s = 0, c0 = 0;
 
         for (int j = 0; j < n_pages && ok; ++j) {
             const int b = j & 1;
             const uint32_t ph2 = (j >> 1) & 1;
+            if (tracing) c0 = clock64();
             if (!mbar_wait(&s_full[b], ph2)) { atomicExch(err, 22); ok = false; break; }
+            if (tracing) wait_s += clock64() - c0;
             tc_fence_after_sync();
             if (t == 0 && j == 0) trace_mark(2);
             uint32_t sr[PAGE];
@@ -352,6 +376,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             if (lane == 0) mbar_arrive(&p_full[b]);
         }
         if (t == 0) trace_mark(3);
+        if (tracing) trace_value(11, wait_s);
         if (ok && n_pages > 0) {
             if (!mbar_wait(&o_full, (uint32_t)((n_pages - 1) & 1))) { atomicExch(err, 25); ok = false; }
         }

@@ -592,13 +592,28 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None,
     return out
 
 
+def sample_work_bytes(B: int, V: int) -> int:
+    """Bytes of working memory `sample` needs for B rows of V entries."""
+    return int(native.lib().rfx_sample_work_bytes(int(B), int(V)))
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
            top_k: Optional[torch.Tensor] = None, top_p: Optional[torch.Tensor] = None,
-           scratch: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+           scratch: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+           work: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token a row: temperature softmax, optional top-k and top-p cuts, and an
+    inverse-CDF draw with the row's uniform number.  `scratch` (float32 [B, V])
+    and `work` (uint8, `sample_work_bytes(B, V)`) may be given to spare the
+    allocations of a call a step."""
     B, V = logits.shape
     _chk(logits, "logits", torch.float32)
     if scratch is None:
         scratch = torch.empty((B, V), dtype=torch.float32, device=logits.device)
+    need = sample_work_bytes(B, V)
+    if work is None:
+        work = torch.empty((need,), dtype=torch.uint8, device=logits.device)
+    elif work.numel() < need or work.dtype != torch.uint8:
+        raise InvalidInput(f"sample: work must hold {need} bytes")
     if out is None:
         out = torch.empty((B,), dtype=torch.int32, device=logits.device)
     _chk(out, "out", torch.int32)
@@ -606,6 +621,6 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
         logits.data_ptr(), V, B, V, _chk(temperature, "temperature", torch.float32),
         _chk(top_k, "top_k", torch.int32), _chk(top_p, "top_p", torch.float32),
         _chk(uniform, "uniform", torch.float32), _chk(scratch, "scratch", torch.float32),
-        out.data_ptr(), _stream())
+        _chk(work, "work", torch.uint8), out.data_ptr(), _stream())
     native.check(st, "sample")
     return out

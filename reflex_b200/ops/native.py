@@ -53,7 +53,7 @@ _SIGNATURES = {
     "rfx_wait_probe": [c_longlong, c_void_p, c_void_p],
     "rfx_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "rfx_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                   c_void_p, c_void_p, c_void_p],
+                   c_void_p, c_void_p, c_void_p, c_void_p],
 }
 
 
@@ -80,6 +80,8 @@ def lib() -> ctypes.CDLL:
             fn.restype = c_int
         handle.rfx_gemm_bf16_tc_max_parts.argtypes = [c_int]
         handle.rfx_gemm_bf16_tc_max_parts.restype = c_int
+        handle.rfx_sample_work_bytes.argtypes = [c_int, c_int]
+        handle.rfx_sample_work_bytes.restype = c_longlong
         handle.rfx_error_string.argtypes = [c_int]
         handle.rfx_error_string.restype = ctypes.c_char_p
         _lib = handle

@@ -54,6 +54,8 @@ class Sampler:
         self.seed = params.seed if params.seed is not None else fresh_seed()
         self._const = {}
         self._scratch = None
+        self._work = None
+        self._uniforms = {}
 
     def _constants(self, n: int):
         if n not in self._const:
@@ -80,6 +82,25 @@ class Sampler:
                                 torch.cuda.Event())
         return ring["slots"][i]
 
+    def _upload_uniforms(self, values: List[float]) -> torch.Tensor:
+        """The step's uniform numbers on the device, through pinned buffers that
+        take turns (a pick may still be in flight when the next is prepared)."""
+        n = len(values)
+        ring = self._uniforms.setdefault(n, {"next": 0, "slots": [None] * self.RING})
+        i = ring["next"]
+        ring["next"] = (i + 1) % self.RING
+        if ring["slots"][i] is None:
+            ring["slots"][i] = (torch.empty((n,), dtype=torch.float32, pin_memory=True),
+                                torch.empty((n,), dtype=torch.float32, device=self.device),
+                                torch.cuda.Event())
+        host, dev, copied = ring["slots"][i]
+        copied.synchronize()  # the copy that last read this pinned buffer is done
+        for j, v in enumerate(values):
+            host[j] = v
+        dev.copy_(host, non_blocking=True)
+        copied.record()
+        return dev
+
     def pick_async(self, logits: torch.Tensor, requests: Sequence[int], steps: Sequence[int]) -> PendingIds:
         """As `pick`, without waiting: the ids stay on the device for the next
         step and travel to the host behind an event."""
@@ -90,12 +111,12 @@ class Sampler:
         if self.params.is_greedy():
             ops.argmax(logits, out=dev, scratch=scratch)
         else:
-            u = torch.tensor([uniform(self.seed, r, s) for r, s in zip(requests, steps)],
-                             dtype=torch.float32).to(self.device)
+            u = self._upload_uniforms([uniform(self.seed, r, s) for r, s in zip(requests, steps)])
             t, k, tp = self._constants(n)
             if self._scratch is None or self._scratch.shape[0] < n or self._scratch.shape[1] != V:
                 self._scratch = torch.empty((n, V), dtype=torch.float32, device=self.device)
-            ops.sample(logits, t, u, top_k=k, top_p=tp, scratch=self._scratch[:n], out=dev)
+                self._work = torch.empty((ops.sample_work_bytes(n, V),), dtype=torch.uint8, device=self.device)
+            ops.sample(logits, t, u, top_k=k, top_p=tp, scratch=self._scratch[:n], out=dev, work=self._work)
         host.copy_(dev, non_blocking=True)
         event.record()
         return PendingIds(dev, host, event)

@@ -512,6 +512,58 @@ def test_sampling_matches_the_plain_sampler_given_the_same_uniforms(V, top_k, to
         assert got == [int(torch.nonzero(r == r.max())[0]) for r in logits]  # the most probable, lowest index
 
 
+@pytest.mark.parametrize("B,V", [(450, 151936), (3, 17), (40, 4097), (700, 1000)])
+def test_sampling_with_a_cut_of_its_own_in_every_row(B, V):
+    """Rows of one call differ in temperature, top-k and top-p (some have none),
+    rows are many enough (450 of 151,936) that the vocabulary is cut into larger chunks, a row
+    has equal logits at its cut (the lowest indices stay) and one has entries
+    of probability zero."""
+    g = torch.Generator().manual_seed(B * 7 + V)
+    logits = torch.randn(B, V, generator=g) * 3
+    ks = [0, 1, 5, 50, V, V + 3, 0, 0]
+    ps = [1.0, 1.0, 1.0, 0.9, 0.5, 0.0, 0.3, 0.97]
+    ts = [0.8, 0.3, 1.0, 2.5]
+    top_k = [ks[b % len(ks)] for b in range(B)]
+    top_p = [ps[(b // 2) % len(ps)] for b in range(B)]
+    temp = [ts[b % len(ts)] for b in range(B)]
+    if V >= 16:
+        logits[0, 3:12] = logits[0].max() + 0.5      # nine equal at the top
+        top_k[0], top_p[0] = 5, 1.0                    # the cut falls among them
+        logits[1, ::2] = float("-inf")                 # probability zero
+        top_k[1], top_p[1] = 0, 1.0
+    u = torch.rand(B, generator=g)
+    u[0] = 0.99999994
+    got = ops().sample(logits.to(DEV), torch.tensor(temp, device=DEV), u.to(DEV),
+                       top_k=torch.tensor(top_k, dtype=torch.int32, device=DEV),
+                       top_p=torch.tensor(top_p, device=DEV)).tolist()
+    for b in (range(B) if B * V < 10_000_000 else list(range(16)) + list(range(16, B, 29))):
+        k = top_k[b] if 0 < top_k[b] < V else None
+        tp = top_p[b] if top_p[b] < 1.0 else None
+        row = logits[b].numpy()
+        want = pm.sample_token(row, temp[b], float(u[b]), k, tp)
+        if got[b] == want:
+            continue
+        # sums taken in another order round differently: only where the draw lies within
+        # rounding of a boundary of the walk may the neighbouring kept entry come out
+        p = np.exp((row.astype(np.float64) - float(row.max())) / temp[b])
+        order = np.lexsort((np.arange(V), -p))
+        n_keep = k or V
+        if tp is not None:
+            cum = np.cumsum(p[order] / p.sum())
+            n_p = int(np.searchsorted(cum, tp, side="left")) + 1
+            assert abs(cum[n_p - 1] - tp) > 1e-6, "the cut itself lies within rounding: choose another seed"
+            n_keep = min(n_keep, max(1, n_p))
+        kept = np.sort(order[:n_keep])
+        assert got[b] in kept, (b, got[b], want)
+        cum = np.cumsum(p[kept])
+        draw = float(u[b]) * cum[-1]
+        i_w, i_g = int(np.searchsorted(kept, want)), int(np.searchsorted(kept, got[b]))
+        assert abs(i_w - i_g) == 1 and abs(cum[min(i_w, i_g)] - draw) < 1e-5 * cum[-1], (b, got[b], want)
+    if V >= 16:
+        assert got[0] in range(3, 8)   # of the nine equal entries the five lowest indices are kept
+        assert got[1] % 2 == 1
+
+
 def test_sampling_distribution():
     V, n = 50, 4000
     g = torch.Generator().manual_seed(9)

@@ -340,8 +340,6 @@ template <int PASS>  // 1 or 2: decide on pass PASS - 1, histogram of pass PASS
 __global__ void __launch_bounds__(STHREADS)
 sample_select_kernel(int V, const int* __restrict__ top_k, const float* __restrict__ top_p,
                      const float* __restrict__ probs, SampleWork w, int B, int chunk) {
-    __shared__ int hn[NBINS];
-    __shared__ unsigned int hm_lo[NBINS], hm_hi[NBINS];
     __shared__ int sh_i[17];
     __shared__ unsigned long long sh_m[STHREADS / 32];
     __shared__ SampleRow sh_row;
@@ -363,12 +361,23 @@ sample_select_kernel(int V, const int* __restrict__ top_k, const float* __restri
     // every block of the row reaches the same state; the row's last block records it
     // for the kernels that follow
     if (c == (int)gridDim.x - 1 && threadIdx.x == 0) w.rows[(size_t)(PASS - 1) * B + b] = st;
+    // Only the entries of the chosen bin count now, a few hundred of a row: they go
+    // straight into the row's histogram (integer additions: any order, the same result).
     const unsigned int mask = PASS == 1 ? (0x7ffu << 20) : ((0x7ffu << 20) | (0x7ffu << 9));
     const int lo = c * chunk, hi = min(V, lo + chunk);
-    __syncthreads();
-    chunk_histogram<true>(probs + (size_t)b * V, lo, hi, st.prefix, mask, pass_shift(PASS), pass_bins(PASS),
-                          hn, hm_lo, hm_hi, w.hist_n + ((size_t)PASS * B + b) * NBINS,
-                          w.hist_m + ((size_t)PASS * B + b) * NBINS);
+    const float* p = probs + (size_t)b * V;
+    int* g_n = w.hist_n + ((size_t)PASS * B + b) * NBINS;
+    unsigned long long* g_m = w.hist_m + ((size_t)PASS * B + b) * NBINS;
+    const int shift = pass_shift(PASS), bins = pass_bins(PASS);
+    for (int i = lo + threadIdx.x; i < hi; i += STHREADS) {
+        const float v = p[i];
+        const unsigned int u = __float_as_uint(v);
+        if ((u & mask) == st.prefix) {
+            const int bin = (u >> shift) & (bins - 1);
+            atomicAdd(&g_n[bin], 1);
+            atomicAdd(&g_m[bin], mass_of(v));
+        }
+    }
 }
 
 __global__ void __launch_bounds__(STHREADS)
@@ -438,19 +447,34 @@ sample_pick_kernel(int V, int C, const float* __restrict__ uniform, const float*
         ties_kept = st.ties_kept;
     }
     const double cut_v = (double)__uint_as_float(cut);
+    // the chunks' sums and tie counts, fetched by all threads (up to PICK_C chunks;
+    // beyond that thread 0 reads them from where they lie)
+    constexpr int PICK_C = 512;
+    __shared__ double s_sum[PICK_C];
+    __shared__ int s_tie[PICK_C];
+    const bool staged = C <= PICK_C;
+    if (staged) {
+        for (int c = threadIdx.x; c < C; c += STHREADS) {
+            s_sum[c] = cuts ? w.above_sum[(size_t)b * C + c] : w.csum[(size_t)b * C + c];
+            s_tie[c] = cuts ? w.tie_cnt[(size_t)b * C + c] : 0;
+        }
+        __syncthreads();
+    }
+    auto chunk_sum = [&](int c) {
+        return staged ? s_sum[c] : (cuts ? w.above_sum[(size_t)b * C + c] : w.csum[(size_t)b * C + c]);
+    };
+    auto chunk_ties = [&](int c) { return staged ? s_tie[c] : (cuts ? w.tie_cnt[(size_t)b * C + c] : 0); };
     // thread 0: the kept sum of every chunk, in chunk order, and the chunk of the draw
     if (threadIdx.x == 0) {
         double renorm = 0.0;
         int seen = 0;
         for (int c = 0; c < C; ++c) {
-            double s;
+            double s = chunk_sum(c);
             if (cuts) {
-                const int nt = w.tie_cnt[(size_t)b * C + c];
+                const int nt = chunk_ties(c);
                 const int kept = max(0, min(nt, ties_kept - seen));
                 seen += nt;
-                s = w.above_sum[(size_t)b * C + c] + (double)kept * cut_v;
-            } else {
-                s = w.csum[(size_t)b * C + c];
+                s += (double)kept * cut_v;
             }
             renorm += s;
         }
@@ -460,14 +484,12 @@ sample_pick_kernel(int V, int C, const float* __restrict__ uniform, const float*
         double last_acc = 0.0;
         seen = 0;
         for (int c = 0; c < C; ++c) {
-            double s;
+            double s = chunk_sum(c);
             int nt = 0;
             if (cuts) {
-                nt = w.tie_cnt[(size_t)b * C + c];
+                nt = chunk_ties(c);
                 const int kept = max(0, min(nt, ties_kept - seen));
-                s = w.above_sum[(size_t)b * C + c] + (double)kept * cut_v;
-            } else {
-                s = w.csum[(size_t)b * C + c];
+                s += (double)kept * cut_v;
             }
             if (s > 0.0) {
                 last = c;

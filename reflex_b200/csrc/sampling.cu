@@ -12,9 +12,9 @@
 //    vocabulary) sum to >= top_p; ties at a cut are kept lowest index first.
 //    The draw walks the kept entries in index order: the token is the first
 //    whose running sum reaches u * (sum of kept p).
-//    Both cuts are found by a radix select over the bit patterns of p (p >= 0,
-//    so the patterns order like the values), four 8-bit digits, histograms of
-//    counts and of mass in shared memory.  `probs` is scratch of B*V floats.
+//    The cut is one radix select over the bit patterns of p for both rules
+//    (below); `probs` is scratch of B*V floats and `work` holds the chunk sums
+//    and histograms.
 #include "common.cuh"
 
 namespace {

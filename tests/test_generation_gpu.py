@@ -216,3 +216,19 @@ def test_trace_run_replays_steps_and_writes_logits(dtype, tmp_path):
         assert np.abs(x[1] - rb[5 + i]).max() < tol * scale
     assert not os.path.exists(os.path.join(out_dir, "5.f32"))  # nothing was wanted
     assert np.abs(load(6, 1)[0] - rc[39]).max() < tol * scale
+
+
+def test_diagnostics_print_a_decode_steps_timeline():
+    """The kernels' own time stamps, read back for a tiny model: one line per
+    product of the captured step, in launch order, each later than the last."""
+    import io
+
+    from reflex_b200 import diagnostics
+    from tiny_configs import TINY_B
+
+    out = io.StringIO()
+    diagnostics.decode_step(batch=2, layers=2, prompt=8, config=dict(TINY_B), out=out)
+    lines = [l.split() for l in out.getvalue().splitlines()[2:]]
+    assert [l[0] for l in lines] == ["qkv", "o", "gate_up", "down"] * 2 + ["head"]
+    left = [float(l[-2]) if len(l) > 11 else float(l[-1]) for l in lines]  # released -> left, us
+    assert all(0.0 < v < 1000.0 for v in left)

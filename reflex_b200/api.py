@@ -177,12 +177,23 @@ class Model:
             raise InvalidInput("system1 needs at least one candidate")
         if len(prompt) == 0:
             raise InvalidInput("prompt is empty")
-        for c in candidates:
+        V = self.spec.vocab_size
+        for ci, c in enumerate(candidates):
             if len(c) == 0:
                 raise InvalidInput("a candidate has no tokens")
+            for t in c:  # every id, the last one too: it indexes the head, it is never embedded
+                if not (0 <= int(t) < V):
+                    raise InvalidInput(f"candidate {ci}: token id {t} is outside the vocabulary [0, {V})")
         eng = self.engine
-        seqs = [eng.open() for _ in candidates]
+        if len(candidates) > eng.cache.slots.free_count:
+            from .errors import OutOfMemory
+
+            raise OutOfMemory(f"system1 needs a cache slot per candidate: {len(candidates)} candidates, "
+                              f"{eng.cache.slots.free_count} slots free")
+        seqs: List[int] = []
         try:
+            for _ in candidates:
+                seqs.append(eng.open())
             P = len(prompt)
             entries = []
             for s, c in zip(seqs, candidates):

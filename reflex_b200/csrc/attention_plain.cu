@@ -10,7 +10,14 @@
 // m' = max(m, s), l = l e^(m-m') + e^(s-m'), acc = acc e^(m-m') + e^(s-m') V_j;
 // out = acc / l   (src/kernels_cuda/attention_online.cuh:64-102; the window
 // rule is src/model/config.rs:1184-1185: i - j < window).
+//
+// Orders, which a host mirror repeats bit for bit: the dot product as a fused
+// multiply-add chain per lane over elements lane, lane + 32, ..., then the
+// lanes' butterfly, then times scale; l = fma(l, corr, p);
+// acc = fma(acc, corr, p * v) with the product rounded first; the exponential
+// is `exact_expf`.
 #include "common.cuh"
+#include "exact_math.cuh"
 #include "paged.cuh"
 
 namespace {
@@ -56,13 +63,13 @@ attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
         }
         const float s = warp_sum(dot) * scale;
         const float m_new = fmaxf(m, s);
-        const float corr = expf(m - m_new);  // 0 at the first key (m = -inf)
-        const float p = expf(s - m_new);
+        const float corr = exact_expf(m - m_new);  // 0 at the first key (m = -inf)
+        const float p = exact_expf(s - m_new);
         l = fmaf(l, corr, p);
 #pragma unroll
         for (int i = 0; i < MAX_PER_LANE; ++i) {
             const int e = i * 32 + lane;
-            if (e < d) acc[i] = fmaf(acc[i], corr, p * ld<T>(vp, e));
+            if (e < d) acc[i] = fmaf(acc[i], corr, __fmul_rn(p, ld<T>(vp, e)));
         }
         m = m_new;
     }

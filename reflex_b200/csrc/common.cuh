@@ -9,6 +9,8 @@
 
 #include <utility>
 
+#include "exact_math.cuh"
+
 #define RFX_DT_F32 0
 #define RFX_DT_BF16 1
 
@@ -119,7 +121,8 @@ __device__ __forceinline__ void store2(__nv_bfloat16* p, float a, float b) {
 }
 
 // silu(g) * u as the reference writes it (src/kernels_cuda/silu_and_mul.cu:7-23).
-__device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+// The exponential is `exact_expf`, so a host program can repeat the bits.
+__device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + exact_expf(-g))) * u; }
 // The same for a result that is rounded to bfloat16 anyway: the fast exponential
 // and division are a few units in the last place of 32 bits off, far below that
 // rounding; their limits at large |g| are the function's own (0 and g).

@@ -9,10 +9,24 @@
 // Rotary, half-split pairs (i, i + rd/2) for i < rd/2
 // (src/kernels_cuda/rope.cu:9-37):  theta = (float)pos / denom[i] with
 // denom[i] = base^(2i/rd);  (a, b) <- (a cos - b sin, a sin + b cos).
-// Elements >= rd stay.  v is stored as projected.  All arithmetic is 32-bit;
-// the angle is a 32-bit division followed by sincosf with full range reduction.
+// With consecutive pairing the pairs are (2i, 2i + 1) instead
+// (src/model/config.rs:15-28).  cos and sin are multiplied by `magnitude` (1 for
+// the plain encoding; a frequency-scaled encoding's attention factor,
+// src/model/kernels.rs:3086-3129).  Elements >= rd stay.  v is stored as
+// projected.  All arithmetic is 32-bit; the angle is a 32-bit division, its sine
+// and cosine come from `exact_sincosf`, whose bits a host program can repeat.
+//
+// Orders of the 32-bit form (32-bit in, 32-bit out: always the general kernel),
+// which a host mirror repeats: a head's sum of squares as a fused multiply-add
+// chain per lane over elements lane, lane + 32, ..., then the lanes' butterfly;
+// y = (x * r) * (offset + w); the rotation as fma(partner, -+sin, x * cos) with
+// the product x * cos rounded first.
 #include "common.cuh"
+#include "exact_math.cuh"
 #include "paged.cuh"
+
+#define RFX_PAIR_HALF 0
+#define RFX_PAIR_CONSECUTIVE 1
 
 namespace {
 
@@ -68,7 +82,7 @@ qkv_post_wide_kernel(const TI* __restrict__ qkv, int row_stride, const float* __
                      const float* __restrict__ rope_denom, int rotary_dim,
                      const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                      TO* __restrict__ q_out, TO* __restrict__ k_pages, TO* __restrict__ v_pages,
-                     PagedKV cache, int nq, int nkv_in, int dry_pass) {
+                     PagedKV cache, int nq, int nkv_in, int dry_pass, float magnitude) {
     extern __shared__ float smem[];  // cos[half], sin[half]
     pdl_launch_dependents();
     constexpr int D = PER * LPH;
@@ -107,7 +121,10 @@ qkv_post_wide_kernel(const TI* __restrict__ qkv, int row_stride, const float* __
         if (rotate) {
             for (int i = threadIdx.x; i < half; i += blockDim.x) {
                 const float theta = (float)pos / rope_denom[i];
-                sincosf(theta, &sn_tab[i], &cs_tab[i]);
+                float sv, cv;
+                exact_sincosf(theta, &sv, &cv);
+                sn_tab[i] = sv * magnitude;
+                cs_tab[i] = cv * magnitude;
             }
         }
         // head 0's place; the other heads lie a tile apart
@@ -238,7 +255,7 @@ qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restr
                 const float* __restrict__ rope_denom, int rotary_dim,
                 const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                 TO* __restrict__ q_out, TO* __restrict__ k_pages, TO* __restrict__ v_pages,
-                PagedKV cache, int nq, int nkv_in, int dry_pass) {
+                PagedKV cache, int nq, int nkv_in, int dry_pass, int pairing, float magnitude) {
     extern __shared__ float smem[];  // [warps][head_dim], then cos[half], sin[half]
     pdl_launch_dependents();
     const int d = cache.head_dim;
@@ -257,7 +274,10 @@ qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restr
     if (rotate) {
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
             const float theta = (float)pos / rope_denom[i];
-            sincosf(theta, &sn_tab[i], &cs_tab[i]);
+            float sv, cv;
+            exact_sincosf(theta, &sv, &cv);
+            sn_tab[i] = sv * magnitude;
+            cs_tab[i] = cv * magnitude;
         }
     }
     // where this row's key and value heads go: head 0's place, the others a tile apart
@@ -330,10 +350,20 @@ qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restr
                 if (e >= d) break;
                 float o = v[i];
                 if (e < rotary_dim) {
-                    const int fi = e < half ? e : e - half;
+                    // the pair's first element takes -sin, its second +sin
+                    int fi, other;
+                    bool first_of_pair;
+                    if (pairing == RFX_PAIR_CONSECUTIVE) {
+                        fi = e >> 1;
+                        first_of_pair = (e & 1) == 0;
+                        other = e ^ 1;
+                    } else {
+                        first_of_pair = e < half;
+                        fi = first_of_pair ? e : e - half;
+                        other = first_of_pair ? e + half : e - half;
+                    }
                     const float sn = sn_tab[fi], cs = cs_tab[fi];
-                    if (e < half) o = v[i] * cs - buf[e + half] * sn;
-                    else o = buf[e - half] * sn + v[i] * cs;
+                    o = fmaf(buf[other], first_of_pair ? -sn : sn, __fmul_rn(v[i], cs));
                 }
                 if (!dry) st<TO>(dst, e, o);
             }
@@ -348,8 +378,9 @@ extern "C" int rfx_qkv_post(const void* qkv, int in_dt, int row_stride, const fl
                             int rotary_dim, const int* row_pos, const int* row_slot, void* q_out,
                             void* k_pages, void* v_pages, int out_dt, const int* page_table,
                             int max_pages, int page_size, int R, int nq, int nkv_in, int nkv,
-                            int head_dim, void* stream) {
+                            int head_dim, int pairing, float magnitude, void* stream) {
     if (R <= 0) return 0;
+    if (pairing != RFX_PAIR_HALF && pairing != RFX_PAIR_CONSECUTIVE) return RFX_ERR_BAD_ARG;
     if (head_dim <= 0 || head_dim > 32 * MAX_PER_LANE) return RFX_ERR_UNSUPPORTED;
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return RFX_ERR_BAD_ARG;
     if (nkv_in != 0 && nkv_in != nkv) return RFX_ERR_BAD_ARG;
@@ -371,8 +402,11 @@ extern "C" int rfx_qkv_post(const void* qkv, int in_dt, int row_stride, const fl
     const uintptr_t ptrs = reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
                            reinterpret_cast<uintptr_t>(k_pages) | reinterpret_cast<uintptr_t>(v_pages) |
                            reinterpret_cast<uintptr_t>(q_w) | reinterpret_cast<uintptr_t>(k_w);
-    const bool wide = pow2 && (rope_denom == nullptr || rotary_dim == 0 || (rotary_dim / 2) % per == 0) &&
-                      row_stride % per == 0 && (ptrs & 15) == 0;
+    // (the 32-bit form keeps to the general kernel's one order; so does consecutive pairing)
+    const bool rotates = rope_denom != nullptr && rotary_dim > 0;
+    const bool wide = pow2 && (!rotates || ((rotary_dim / 2) % per == 0 && pairing == RFX_PAIR_HALF)) &&
+                      row_stride % per == 0 && (ptrs & 15) == 0 &&
+                      !(in_dt == RFX_DT_F32 && out_dt == RFX_DT_F32);
 #define RFX_POST_ARGS(TI, TO)                                                                       \
     (const TI*)qkv, row_stride, q_w, k_w, eps, w_offset, rope_denom, rotary_dim, row_pos, row_slot, \
         (TO*)q_out, (TO*)k_pages, (TO*)v_pages, cache, nq, nkv_in, dry_pass
@@ -383,7 +417,7 @@ extern "C" int rfx_qkv_post(const void* qkv, int in_dt, int row_stride, const fl
         dim3 grid(R, unit_blocks < 65535 ? unit_blocks : 65535);
         const size_t smem = (size_t)rotary_dim * sizeof(float);
 #define RFX_WIDE(TI, TO, P, L)                                                                    \
-    RFX_LAUNCH((qkv_post_wide_kernel<TI, TO, P, L>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO))
+    RFX_LAUNCH((qkv_post_wide_kernel<TI, TO, P, L>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO), magnitude)
 #define RFX_WIDE_32(TI, TO)  /* 32-bit input: 4 elements are 16 bytes */   \
     do {                                                                  \
         if (per == 4 && lph == 4) RFX_WIDE(TI, TO, 4, 4);                 \
@@ -404,8 +438,7 @@ extern "C" int rfx_qkv_post(const void* qkv, int in_dt, int row_stride, const fl
         else if (per == 16 && lph == 32) RFX_WIDE(TI, TO, 16, 32);        \
         else return RFX_ERR_UNSUPPORTED;                                  \
     } while (0)
-        if (in_dt == RFX_DT_F32 && out_dt == RFX_DT_F32) RFX_WIDE_32(float, float);
-        else if (in_dt == RFX_DT_F32 && out_dt == RFX_DT_BF16) RFX_WIDE_32(float, __nv_bfloat16);
+        if (in_dt == RFX_DT_F32 && out_dt == RFX_DT_BF16) RFX_WIDE_32(float, __nv_bfloat16);
         else if (in_dt == RFX_DT_BF16 && out_dt == RFX_DT_BF16) RFX_WIDE_16(__nv_bfloat16, __nv_bfloat16);
         else return RFX_ERR_BAD_ARG;
 #undef RFX_WIDE_32
@@ -419,11 +452,11 @@ extern "C" int rfx_qkv_post(const void* qkv, int in_dt, int row_stride, const fl
     dim3 grid(R, head_blocks < 65535 ? head_blocks : 65535);
 #define RFX_POST(TI, TO)                                                                              \
     do {                                                                                              \
-        if (head_dim <= 32) RFX_LAUNCH((qkv_post_kernel<TI, TO, 1>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO));        \
-        else if (head_dim <= 64) RFX_LAUNCH((qkv_post_kernel<TI, TO, 2>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO));   \
-        else if (head_dim <= 128) RFX_LAUNCH((qkv_post_kernel<TI, TO, 4>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO));  \
-        else if (head_dim <= 256) RFX_LAUNCH((qkv_post_kernel<TI, TO, 8>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO));  \
-        else RFX_LAUNCH((qkv_post_kernel<TI, TO, 16>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO));                      \
+        if (head_dim <= 32) RFX_LAUNCH((qkv_post_kernel<TI, TO, 1>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO), pairing, magnitude);        \
+        else if (head_dim <= 64) RFX_LAUNCH((qkv_post_kernel<TI, TO, 2>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO), pairing, magnitude);   \
+        else if (head_dim <= 128) RFX_LAUNCH((qkv_post_kernel<TI, TO, 4>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO), pairing, magnitude);  \
+        else if (head_dim <= 256) RFX_LAUNCH((qkv_post_kernel<TI, TO, 8>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO), pairing, magnitude);  \
+        else RFX_LAUNCH((qkv_post_kernel<TI, TO, 16>), grid, threads, smem, s, RFX_POST_ARGS(TI, TO), pairing, magnitude);                      \
     } while (0)
     if (in_dt == RFX_DT_F32 && out_dt == RFX_DT_F32) RFX_POST(float, float);
     else if (in_dt == RFX_DT_F32 && out_dt == RFX_DT_BF16) RFX_POST(float, __nv_bfloat16);

@@ -87,8 +87,10 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int,
     for batch in plan_batches([len(p) for p in prompts], max_new_tokens, engine.cache.max_tokens, max_batch):
         stats.batches += 1
         live = list(batch)
-        seqs = {i: engine.open() for i in live}
+        seqs = {}
         try:
+            for i in live:  # inside the try: a slot taken before an open() fails is given back
+                seqs[i] = engine.open()
             entries = [(seqs[i], list(prompts[i]), [len(prompts[i]) - 1]) for i in live]
             stats.prefill_tokens += sum(len(prompts[i]) for i in live)
             if ahead:

@@ -44,6 +44,14 @@ BLOCK_NAMES = (
 )
 
 
+def attention_scale(head_dim: int) -> float:
+    """1 / sqrtf((float) head_dim), both steps in 32-bit as the reference computes
+    it (src/model/kernels.rs:3385-3398), so that the kernels get the same bits."""
+    import numpy as np
+
+    return float(np.float32(1.0) / np.sqrt(np.float32(head_dim)))
+
+
 def build_qwen3_spec(cfg: Qwen3Config) -> ModelSpec:
     eps = cfg.rms_norm_eps
     head_norm = NormSpec("rmsnorm", cfg.head_dim, eps)
@@ -59,7 +67,7 @@ def build_qwen3_spec(cfg: Qwen3Config) -> ModelSpec:
             num_heads=cfg.num_attention_heads,
             num_kv_heads=cfg.num_key_value_heads,
             head_dim=cfg.head_dim,
-            scale=1.0 / math.sqrt(float(cfg.head_dim)),
+            scale=attention_scale(cfg.head_dim),
             window=window,
             qk_norm=head_norm,
             position=rope,

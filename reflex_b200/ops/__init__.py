@@ -346,11 +346,23 @@ def linear_swiglu(x: torch.Tensor, weight_pairs: torch.Tensor) -> torch.Tensor:
 
 # ----------------------------------------------------------------- attention
 def qkv_post(qkv: torch.Tensor, q_weight, k_weight, eps: float, weight_offset: float,
-             rope_denom, rotary_dim: int, row_pos: torch.Tensor, row_slot: torch.Tensor,
+             rotation, row_pos: torch.Tensor, row_slot: torch.Tensor,
              k_pages, v_pages, page_table: torch.Tensor, page_size: int, nq: int, nkv: int,
              head_dim: int, writes_cache: bool, out_dtype: torch.dtype) -> torch.Tensor:
-    """Per-head q/k norm, rotary encoding, q out, k and v into the cache."""
+    """Per-head q/k norm, rotary encoding, q out, k and v into the cache.
+    `rotation`: a `parts.Rotation` (denominators, rotary_dim, pairing,
+    magnitude) or None for no rotary encoding."""
+    from ..parts.registry import PAIRINGS
+
     R = qkv.shape[0]
+    rope_denom, rotary_dim, pairing, magnitude = None, 0, 0, 1.0
+    if rotation is not None:
+        if rotation.pairing not in PAIRINGS:
+            raise InvalidInput(f"qkv_post: pairing must be one of {sorted(PAIRINGS)}, got {rotation.pairing!r}")
+        rope_denom, rotary_dim = rotation.denominators, int(rotation.rotary_dim)
+        pairing, magnitude = PAIRINGS[rotation.pairing], float(rotation.magnitude)
+        if rope_denom is not None and rope_denom.numel() != rotary_dim // 2:
+            raise InvalidInput("qkv_post: one denominator per rotary pair is needed")
     nkv_in = nkv if writes_cache else 0
     if qkv.shape[1] != (nq + 2 * nkv_in) * head_dim:
         raise InvalidInput("qkv_post: qkv width does not match the head counts")
@@ -362,7 +374,7 @@ def qkv_post(qkv: torch.Tensor, q_weight, k_weight, eps: float, weight_offset: f
         _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32),
         q.data_ptr(), _chk(k_pages, "k_pages"), _chk(v_pages, "v_pages"), dt_code(out_dtype),
         _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size, R, nq, nkv_in,
-        nkv, head_dim, _stream())
+        nkv, head_dim, pairing, magnitude, _stream())
     native.check(st, f"qkv_post (head_dim={head_dim})")
     return q
 
@@ -455,61 +467,6 @@ def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_sl
 
 
 CLUSTER_MERGE = _env_flag("REFLEX_B200_CLUSTER_MERGE", True)
-
-
-def fused_decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int) -> int:
-    """Ranks of the fused decode kernel's cluster over the key range: the same
-    estimate as `decode_splits`, with a cluster barrier (about 1 us) in place of
-    the combine kernel, and at most 8 ranks."""
-    forced = _env_int("REFLEX_B200_DECODE_SPLITS", 0, 0, 64)  # tuning aid
-    if forced > 0:
-        return max(s for s in (1, 2, 4, 8) if s <= forced)
-    ctas = n_rows * nkv * ((nq // nkv + 7) // 8)
-    best, best_cost = 1, None
-    for s in (1, 2, 4, 8):
-        if s > max(1, max_pages):
-            break
-        waves = max(1.0, ctas * s / (2.0 * SM_COUNT))
-        cost = 4.0 + -(-max_pages // s) * 0.8 * waves + (1.0 if s > 1 else 0.0)
-        if best_cost is None or cost < best_cost - 1e-9:
-            best, best_cost = s, cost
-    return best
-
-
-# The one-launch form of a decode step's attention (`attention_decode_fused`) is
-# opt-in: measured on a B200 at Qwen3-8B sizes it is level with the separate
-# kernels at batch 8 (3.42 against 3.40 ms a step) and behind them at batch 32
-# and 64, because its larger CTAs become resident later behind the product
-# kernel before them, which costs more than the launches it saves.
-FUSE_DECODE_ATTENTION = _env_flag("REFLEX_B200_FUSE_ATTENTION", False)
-
-
-def attention_decode_fused(qkv: torch.Tensor, q_weight, k_weight, eps: float, weight_offset: float,
-                           rope_denom, rotary_dim: int, k_pages, v_pages, page_table, page_size: int,
-                           row_pos, row_slot, nq: int, nkv: int, head_dim: int, writes_cache: bool,
-                           window, scale: float, n_splits: int = 1) -> torch.Tensor:
-    """Decode rows (one query position each) from the float32 q/k/v product to
-    the attention output in one launch: per-head norms, rotation, the new key
-    and value into the bfloat16 cache, attention, the splits merged inside a
-    thread-block cluster.  Returns bfloat16 [R, nq * head_dim]."""
-    R = qkv.shape[0]
-    _chk(qkv, "qkv", torch.float32)
-    nkv_in = nkv if writes_cache else 0
-    if qkv.shape[1] != (nq + 2 * nkv_in) * head_dim:
-        raise InvalidInput("attention_decode_fused: qkv width does not match the head counts")
-    if head_dim % 16 or not (16 <= head_dim <= 256):
-        raise InvalidInput(f"attention_decode_fused takes head_dim in steps of 16 up to 256, got {head_dim}")
-    out = torch.empty((R, nq * head_dim), dtype=torch.bfloat16, device=qkv.device)
-    st = native.lib().rfx_attention_decode_fused(
-        qkv.data_ptr(), qkv.shape[1], nkv_in, _chk(q_weight, "q_norm", torch.float32),
-        _chk(k_weight, "k_norm", torch.float32), float(eps), float(weight_offset),
-        _chk(rope_denom, "rope_denom", torch.float32), int(rotary_dim),
-        _chk(k_pages, "k_pages", torch.bfloat16), _chk(v_pages, "v_pages", torch.bfloat16),
-        _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
-        _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32), out.data_ptr(),
-        R, nq, nkv, head_dim, int(n_splits), int(window or 0), float(scale), _stream())
-    native.check(st, f"attention_decode_fused (head_dim={head_dim}, splits={n_splits})")
-    return out
 
 
 def attention_prefill(q, k_pages, v_pages, page_table, page_size, seq_slot, seq_start, seq_new,

@@ -4,6 +4,7 @@ from .registry import (  # noqa: F401
     MIXERS,
     NORMS,
     POSITIONS,
+    Rotation,
     TensorInfo,
     register_block,
     register_feed_forward,

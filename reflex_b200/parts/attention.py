@@ -90,28 +90,16 @@ class GQAttention:
         w = self.qkv if ctx.writes_cache else self.q_only
         qkv = ops.linear(x, w, out_dtype=torch.float32 if x.shape[0] <= ops.GEMV_MAX_ROWS else None)
         ops.prof_mark("qkv_gemm")
-        denom, rotary_dim = (None, 0) if self.position is None else self.position.rotation()
+        rotation = None if self.position is None else self.position.rotation()
         norm = s.qk_norm
-        if (ops.FUSE_DECODE_ATTENTION and batch.is_decode and qkv.dtype == torch.float32
-                and self.dtype == torch.bfloat16 and s.head_dim % 16 == 0 and s.head_dim <= 256):
-            # one token a sequence: norms, rotation, cache write, attention and
-            # the merge of the key splits are one kernel
-            pages = -(-min(batch.max_context, s.window or batch.max_context) // kv.page_size) + (1 if s.window else 0)
-            attn = ops.attention_decode_fused(
-                qkv, self.q_norm, self.k_norm, norm.eps if norm else 0.0,
-                norm.weight_offset if norm else 0.0, denom, rotary_dim, kv.k_pages, kv.v_pages,
-                kv.page_table, kv.page_size, batch.row_pos, batch.row_slot, s.num_heads, s.num_kv_heads,
-                s.head_dim, ctx.writes_cache, s.window, s.scale,
-                n_splits=ops.fused_decode_splits(qkv.shape[0], s.num_heads, s.num_kv_heads, pages))
-        else:
-            q = ops.qkv_post(
-                qkv, self.q_norm, self.k_norm, norm.eps if norm else 0.0,
-                norm.weight_offset if norm else 0.0, denom, rotary_dim, batch.row_pos, batch.row_slot,
-                kv.k_pages, kv.v_pages, kv.page_table, kv.page_size, s.num_heads, s.num_kv_heads,
-                s.head_dim, ctx.writes_cache, self.dtype)
-            ops.prof_mark("norm_rope")
-            attn = ops.attention(q, kv.k_pages, kv.v_pages, kv.page_table, kv.page_size, batch,
-                                 s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale)
+        q = ops.qkv_post(
+            qkv, self.q_norm, self.k_norm, norm.eps if norm else 0.0,
+            norm.weight_offset if norm else 0.0, rotation, batch.row_pos, batch.row_slot,
+            kv.k_pages, kv.v_pages, kv.page_table, kv.page_size, s.num_heads, s.num_kv_heads,
+            s.head_dim, ctx.writes_cache, self.dtype)
+        ops.prof_mark("norm_rope")
+        attn = ops.attention(q, kv.k_pages, kv.v_pages, kv.page_table, kv.page_size, batch,
+                             s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale)
         ops.prof_mark("attn")
         if residual is not None:
             fused = ops.linear_residual(attn, self.o, residual[0], residual[1])

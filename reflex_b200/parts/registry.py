@@ -13,7 +13,7 @@ Interfaces (duck-typed; `spec` is the part's record from `config.spec`):
     bind(tensors: {role: Tensor})                takes ownership of its weights
 
   norm            __call__(residual_f32, delta=None, rows=None, update=True) -> normed
-  position        rotation() -> (denominators_f32 | None, rotary_dim)
+  position        rotation() -> Rotation (below) | None
   mixer           cache_spec() -> KVSpec | StateSpec | None
                   forward(x, ctx) -> delta [rows, hidden]
   feed-forward    forward(x) -> delta [rows, hidden]
@@ -36,6 +36,28 @@ class TensorInfo:
     # "norm":   a norm's weight, kept 32-bit, drawn 1 + U(-0.1, 0.1)
     role: str
     optional: bool = False
+
+
+@dataclass(frozen=True)
+class Rotation:
+    """What a rotary position encoding hands to the mixer that applies it.
+
+    A head vector's first `rotary_dim` elements are rotated in pairs; pair i
+    turns by the angle position / denominators[i] (32-bit division), and the
+    cosine and sine are multiplied by `magnitude` (1.0: a pure rotation; a
+    frequency-scaled encoding's attention factor otherwise,
+    src/model/kernels.rs:3086-3129).  `pairing` says which elements form pair i:
+    "half" (i, i + rotary_dim / 2) or "consecutive" (2i, 2i + 1)
+    (src/model/config.rs:15-28).  Variants that differ in their frequencies
+    differ only in the table."""
+
+    denominators: "object"  # float32 tensor [rotary_dim / 2] on the device
+    rotary_dim: int
+    pairing: str = "half"
+    magnitude: float = 1.0
+
+
+PAIRINGS = {"half": 0, "consecutive": 1}
 
 
 class _Registry:

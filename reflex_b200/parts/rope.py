@@ -5,18 +5,21 @@ For a head vector t[0..d) and i < rd/2:  theta = (float)pos / base^(2i/rd);
 elements >= rd stay (src/kernels_cuda/rope.cu:9-37).  The part owns the table
 of denominators base^(2i/rd), made once on the host in double precision and
 rounded to 32-bit; the angle itself is computed per element in 32-bit inside
-the fused kernel that the attention part launches.
+the fused kernel that the attention part launches.  Pairing and magnitude go
+to that kernel as parameters (`Rotation`), so an encoding with consecutive
+pairs or a scaled magnitude is another position part, not another kernel.
 """
 
 from __future__ import annotations
 
+import math
 from typing import Dict, Optional, Tuple
 
 import torch
 
 from ..config.spec import PositionSpec
 from ..errors import InvalidInput
-from .registry import TensorInfo, register_position
+from .registry import Rotation, TensorInfo, register_position
 
 
 @register_position("rope_neox")
@@ -28,9 +31,9 @@ class RotaryNeox:
             )
         self.spec = spec
         half = spec.rotary_dim // 2
-        exponents = torch.arange(half, dtype=torch.float64) * 2.0 / float(spec.rotary_dim)
-        denom = torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64), exponents)
-        self.denominators = denom.to(torch.float32).to(device)
+        # the C library's pow in double, element by element, then one rounding to 32-bit
+        denom = [math.pow(float(spec.theta), 2.0 * i / float(spec.rotary_dim)) for i in range(half)]
+        self.denominators = torch.tensor(denom, dtype=torch.float64).to(torch.float32).to(device)
 
     @classmethod
     def tensor_specs(cls, spec: PositionSpec) -> Dict[str, TensorInfo]:
@@ -39,5 +42,5 @@ class RotaryNeox:
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         pass
 
-    def rotation(self) -> Tuple[Optional[torch.Tensor], int]:
-        return self.denominators, self.spec.rotary_dim
+    def rotation(self) -> Rotation:
+        return Rotation(self.denominators, self.spec.rotary_dim, "half", 1.0)

@@ -99,6 +99,56 @@ def test_unequal_batches_early_ends_slot_reuse(name, dtype):
     assert all(g.pool.held_count == 0 for g in eng.cache.kv_groups)
 
 
+def mirror_logits(folder, tokens, **kw):
+    import fp32_mirror
+    import plain_model
+
+    cfg, w = plain_model.read_model(folder)
+    return fp32_mirror.forward(cfg, w, tokens, **kw)
+
+
+@pytest.mark.parametrize("name", list(ALL))
+def test_float32_logits_equal_the_host_mirror_bit_for_bit(name):
+    """The true 32-bit path against a host program that repeats its kernels'
+    arithmetic operation by operation (tests/fp32_mirror.py): the same bits at
+    every position, for each request whole, with its last 32 tokens one by one,
+    and in unequal batches whose slots are used again.  A tolerance would not see
+    a last-bit dependence on the batch that two cuttings happen to share; this
+    does.  The mirror with one reduction order changed (the norm's sum of squares
+    in plain index order) no longer matches, so the comparison is that sharp."""
+    V = ALL[name]["vocab_size"]
+    flat = helpers.model_folder(name, 7, "float32")
+    eng = helpers.make_engine(flat, "float32", max_tokens=1024)
+    for n, seed in ((100, 3), (33, 4), (1, 5)):
+        toks = helpers.random_tokens(n, V, seed)
+        ref = mirror_logits(flat, toks)
+        assert np.array_equal(helpers.run_whole(eng, toks), ref), "whole"
+        assert np.array_equal(helpers.run_tail_one_by_one(eng, toks, 32), ref), "last 32 one by one"
+        if n == 100:
+            assert not np.array_equal(mirror_logits(flat, toks, norm_order=1), ref)
+    sharp = sharp_folder(name, 7, "float32")
+    eng = helpers.make_engine(sharp, "float32", max_tokens=64 * 8, max_slots=3)
+    lengths = (5, 17, 32, 1, 70, 129, 64, 2, 65)
+    reqs = [helpers.random_tokens(n, V, 100 + n) for n in lengths]
+    got = helpers.run_batches(eng, reqs, 3, [5, 17, 20, 1, 64])
+    for r, g in zip(reqs, got):
+        assert np.array_equal(g, mirror_logits(sharp, r)), f"batched, length {len(r)}"
+    assert eng.cache.slots.held_count == 0
+
+
+def test_float32_long_decoding_equals_the_host_mirror():
+    """300 tokens one by one on the model with sliding layers: page edges, the
+    window's edge and pages given back under way, bit for bit."""
+    V = ALL["C"]["vocab_size"]
+    folder = sharp_folder("C", 11, "float32")
+    eng = helpers.make_engine(folder, "float32", max_tokens=512)
+    toks = helpers.random_tokens(300, V, 5)
+    got = helpers.run_tail_one_by_one(eng, toks, tail=299)
+    ref = mirror_logits(folder, toks)
+    bad = np.nonzero((got != ref).any(axis=1))[0]
+    assert bad.size == 0, f"first differing position {int(bad[0])}"
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_over_page_and_window_edges(dtype):
     """300 tokens one by one on the model with sliding layers (window 37):
@@ -230,6 +280,10 @@ def test_one_layer_at_the_benchmark_models_widths(dtype):
         got = helpers.run_batches(eng, reqs, 3, [4, 20, 8])
         for r, g in zip(reqs, got):
             assert helpers.rel_err(g, plain_model.forward(pcfg, w, r)) < bound
+        if dtype == "float32":
+            import fp32_mirror
+
+            assert np.array_equal(got[0], fp32_mirror.forward(pcfg, w, reqs[0]))
         assert eng.cache.slots.held_count == 0
     finally:
         shutil.rmtree(folder, ignore_errors=True)
@@ -288,6 +342,11 @@ def test_random_configurations(seed, dtype):
             assert helpers.rel_err(g, plain_model.forward(pcfg, w, r)) < bound, cfg
         tail = helpers.run_tail_one_by_one(eng, reqs[1], 32)
         assert helpers.rel_err(tail, plain_model.forward(pcfg, w, reqs[1])) < bound, cfg
+        if dtype == "float32":
+            import fp32_mirror
+
+            for r, g in zip(reqs, got):
+                assert np.array_equal(g, fp32_mirror.forward(pcfg, w, r)), cfg
         assert eng.cache.slots.held_count == 0
     finally:
         shutil.rmtree(folder, ignore_errors=True)

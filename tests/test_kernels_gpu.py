@@ -219,7 +219,9 @@ def test_qkv_post_norm_rope_cache(nq, nkv, d, rd, theta, dtype):
     k_pages = torch.full((n_pages, nkv, 64, d), 7.0, dtype=dtype, device=DEV)
     v_pages = torch.full((n_pages, nkv, 64, d), 7.0, dtype=dtype, device=DEV)
     denom = torch.pow(torch.tensor(theta, dtype=torch.float64), torch.arange(rd // 2, dtype=torch.float64) * 2 / rd)
-    q = ops().qkv_post(qkv.to(DEV), qw.to(DEV), kw.to(DEV), eps, 0.0, denom.float().to(DEV), rd,
+    from reflex_b200.parts import Rotation
+
+    q = ops().qkv_post(qkv.to(DEV), qw.to(DEV), kw.to(DEV), eps, 0.0, Rotation(denom.float().to(DEV), rd),
                        torch.tensor(positions, dtype=torch.int32, device=DEV),
                        torch.tensor(slots, dtype=torch.int32, device=DEV), k_pages, v_pages, table.to(DEV), 64,
                        nq, nkv, d, True, dtype)
@@ -364,75 +366,6 @@ def test_attention_decode_splits(nq, nkv, d, ctxs, window, splits):
         finally:
             o.CLUSTER_MERGE = True
         assert torch.equal(out.view(torch.int16), two.view(torch.int16))
-
-
-FUSED_CASES = [
-    # nq, nkv, d, rotary, contexts, window, splits, this run writes the cache
-    (4, 2, 16, 16, [1, 17, 64, 65], None, 1, True),
-    (6, 1, 32, 32, [100, 129], None, 2, True),
-    (3, 1, 48, 32, [300, 38, 37], 37, 4, True),
-    (32, 8, 128, 128, [640] * 4, None, 4, True),
-    (32, 8, 128, 128, [1, 63, 64, 4000], None, 8, True),
-    (32, 8, 128, 128, [520] * 8, None, 1, True),
-    (40, 2, 256, 64, [999], None, 4, True),
-    (7, 7, 80, 80, [255, 256], 100, 2, True),
-    (20, 1, 64, 64, [130, 64], None, 2, True),
-    (6, 2, 64, 64, [129, 5], None, 2, False),
-]
-
-
-@pytest.mark.parametrize("nq,nkv,d,rd,ctxs,window,splits,writes", FUSED_CASES)
-def test_fused_decode_attention_equals_the_separate_kernels(nq, nkv, d, rd, ctxs, window, splits, writes):
-    """From the q/k/v product's rows to the attention output in one launch:
-    the same bits as qkv_post followed by attention_decode with as many
-    splits, the same cache afterwards, and both right against the plain
-    formulas.  The row's own key and value are NaN in the cache beforehand
-    when the run writes them: the kernel must not read them from there."""
-    g = torch.Generator().manual_seed(nq * 7 + d)
-    slots, table, kp, vp, ks, vs = _paged(ctxs, nkv, d, torch.bfloat16, g)
-    R = len(ctxs)
-    theta, eps = 1e4, 1e-6
-    nkv_in = nkv if writes else 0
-    qkv = torch.randn(R, (nq + 2 * nkv_in) * d, generator=g) * 1.5
-    qw = 1 + 0.1 * torch.randn(d, generator=g)
-    kw = 1 + 0.1 * torch.randn(d, generator=g)
-    denom = torch.pow(torch.tensor(theta, dtype=torch.float64), torch.arange(rd // 2, dtype=torch.float64) * 2 / rd)
-    pos = [c - 1 for c in ctxs]
-    if writes:
-        for i, p in enumerate(pos):
-            page = int(table[slots[i], p // 64])
-            kp[page, :, p % 64] = float("nan")
-            vp[page, :, p % 64] = float("nan")
-    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
-    row_pos, row_slot = i32(pos), i32(slots)
-    common = (qw.to(DEV), kw.to(DEV), eps, 0.0, denom.float().to(DEV), rd)
-    # the separate kernels
-    kp1, vp1 = kp.to(DEV), vp.to(DEV)
-    q1 = ops().qkv_post(qkv.to(DEV), *common, row_pos, row_slot, kp1, vp1, table.to(DEV), 64, nq, nkv, d,
-                        writes, torch.bfloat16)
-    out1 = ops().attention_decode(q1, kp1, vp1, table.to(DEV), 64, row_pos, row_slot, nq, nkv, d, window,
-                                  d ** -0.5, n_splits=splits)
-    # the one kernel
-    kp2, vp2 = kp.to(DEV), vp.to(DEV)
-    out2 = ops().attention_decode_fused(qkv.to(DEV), *common, kp2, vp2, table.to(DEV), 64, row_pos, row_slot,
-                                        nq, nkv, d, writes, window, d ** -0.5, n_splits=splits)
-    assert not bool(torch.isnan(out2.float()).any())
-    assert torch.equal(out1.view(torch.int16), out2.view(torch.int16))
-    assert torch.equal(kp1.view(torch.int16), kp2.view(torch.int16))
-    assert torch.equal(vp1.view(torch.int16), vp2.view(torch.int16))
-    # against the plain formulas
-    x = qkv.double().numpy()
-    parr = np.array(pos)
-    qr = pm.rope_neox(pm.rms_norm(x[:, : nq * d].reshape(R, nq, d), qw.double().numpy(), eps), parr, theta, rd)
-    if writes:
-        kr = pm.rope_neox(pm.rms_norm(x[:, nq * d:(nq + nkv) * d].reshape(R, nkv, d), kw.double().numpy(), eps),
-                          parr, theta, rd)
-        vr = x[:, (nq + nkv) * d:].reshape(R, nkv, d)
-        for i, p in enumerate(pos):
-            ks[i][p] = torch.from_numpy(kr[i]).float()
-            vs[i][p] = torch.from_numpy(vr[i]).float()
-    ref = _ref_rows(torch.from_numpy(qr).float(), ks, vs, [(p, 1) for p in pos], d ** -0.5, window, torch.bfloat16)
-    assert relerr(out2.reshape(R, nq, d), ref) < 1e-2
 
 
 @pytest.mark.parametrize("kernel", ["plain_f32", "plain_bf16", "prefill_bf16", "prefill_tc_bf16", "decode_bf16"])
@@ -602,3 +535,101 @@ def test_a_bounded_wait_that_runs_out_is_reported_and_the_device_stays_usable():
     got = helpers.run_whole(engine, tokens)
     engine.check_errors()
     assert helpers.rel_err(got, helpers.plain_logits(helpers.model_folder("A", 7, "bfloat16"), tokens)) < 1.5e-2
+
+
+# ------------------------------------------ the 32-bit kernels, bit for bit
+def _bits_equal(got: torch.Tensor, ref: np.ndarray) -> bool:
+    return np.array_equal(got.float().cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("R,H", [(1, 64), (3, 100), (5, 4096), (300, 72), (2, 8200)])
+def test_f32_rmsnorm_equals_the_host_mirror(R, H):
+    import fp32_mirror as mir
+
+    g = torch.Generator().manual_seed(H)
+    x, d = torch.randn(R, H, generator=g) * 3, torch.randn(R, H, generator=g)
+    w = 1 + 0.1 * torch.randn(H, generator=g)
+    xd = x.to(DEV).clone()
+    out = ops().rmsnorm(xd, w.to(DEV), 1e-5, torch.float32, delta=d.to(DEV), weight_offset=1.0)
+    ref, t = mir.rms_norm(x.numpy(), w.numpy(), 1e-5, delta=d.numpy(), w_offset=1.0)
+    assert _bits_equal(out, ref) and _bits_equal(xd, t)
+
+
+@pytest.mark.parametrize("R,N,K", [(1, 7, 5), (65, 130, 257), (3, 1000, 96)])
+def test_f32_product_and_swiglu_equal_the_host_mirror(R, N, K):
+    import fp32_mirror as mir
+
+    g = torch.Generator().manual_seed(N)
+    x, W = torch.randn(R, K, generator=g), torch.randn(N, K, generator=g)
+    assert _bits_equal(ops().linear(x.to(DEV), W.to(DEV)), mir.linear(x.numpy(), W.numpy()))
+    gu = torch.randn(R, 2 * N, generator=g) * 8
+    gu[0, :4] = torch.tensor([100.0, -100.0, 0.0, -0.0])
+    got = ops().swiglu(gu.to(DEV))
+    assert _bits_equal(got, mir.swiglu_act(gu[:, :N].numpy(), gu[:, N:].numpy()))
+
+
+@pytest.mark.parametrize("nq,nkv,d,rd,pairing,magnitude", [
+    (4, 2, 16, 16, "half", 1.0), (6, 1, 32, 32, "half", 1.0), (3, 1, 48, 32, "half", 1.0),
+    (32, 8, 128, 128, "half", 1.0), (5, 5, 80, 80, "consecutive", 1.0), (4, 2, 64, 32, "consecutive", 1.25),
+    (2, 1, 256, 256, "half", 0.75)])
+def test_f32_qkv_post_equals_the_host_mirror_with_every_pairing(nq, nkv, d, rd, pairing, magnitude):
+    """Norm, rotation (both pairings, a magnitude other than 1) and the cache
+    write of the 32-bit form, bit for bit; and the bfloat16 form of the same
+    call within its rounding of it."""
+    import fp32_mirror as mir
+    from reflex_b200.parts import Rotation
+
+    g = torch.Generator().manual_seed(nq * 13 + d)
+    positions = [0, 1, 63, 64, 200, 3000, 40959]
+    R = len(positions)
+    qkv = torch.randn(R, (nq + 2 * nkv) * d, generator=g) * 2
+    qw, kw = 1 + 0.1 * torch.randn(d, generator=g), 1 + 0.1 * torch.randn(d, generator=g)
+    denom = mir.rope_denominators(1e6, rd)
+    pos_pages = 40960 // 64
+    table = torch.arange(pos_pages, dtype=torch.int32).reshape(1, pos_pages) % 8
+    # every used page index maps to its own page
+    for i, p in enumerate(sorted({p // 64 for p in positions})):
+        table[0, p] = i
+    rot = Rotation(torch.from_numpy(denom).to(DEV), rd, pairing, magnitude)
+    pair = 1 if pairing == "consecutive" else 0
+    x = qkv.numpy()
+    qr = mir.head_norm_rope(x[:, : nq * d].reshape(R, nq, d), qw.numpy(), 1e-6, denom, rd, positions, pair, magnitude)
+    kr = mir.head_norm_rope(x[:, nq * d:(nq + nkv) * d].reshape(R, nkv, d), kw.numpy(), 1e-6, denom, rd, positions,
+                            pair, magnitude)
+    for dtype in (torch.float32, torch.bfloat16):
+        kp = torch.zeros((8, nkv, 64, d), dtype=dtype, device=DEV)
+        vp = torch.zeros((8, nkv, 64, d), dtype=dtype, device=DEV)
+        q = ops().qkv_post(qkv.to(DEV), qw.to(DEV), kw.to(DEV), 1e-6, 0.0, rot,
+                           torch.tensor(positions, dtype=torch.int32, device=DEV),
+                           torch.zeros(R, dtype=torch.int32, device=DEV), kp, vp, table.to(DEV), 64, nq, nkv, d,
+                           True, dtype)
+        kgot = torch.stack([kp[int(table[0, p // 64]), :, p % 64] for p in positions])
+        vgot = torch.stack([vp[int(table[0, p // 64]), :, p % 64] for p in positions])
+        if dtype == torch.float32:
+            assert _bits_equal(q.reshape(R, nq, d), qr) and _bits_equal(kgot, kr)
+            assert _bits_equal(vgot, x[:, (nq + nkv) * d:].reshape(R, nkv, d))
+        else:
+            assert relerr(q.reshape(R, nq, d), qr.astype(np.float64)) < 8e-3
+            assert relerr(kgot, kr.astype(np.float64)) < 8e-3
+    # the rotation is what the formulas say: against the plain model where it has the pairing
+    if pairing == "half" and magnitude == 1.0:
+        ref = pm.rope_neox(pm.rms_norm(x[:, : nq * d].reshape(R, nq, d).astype(np.float64), qw.double().numpy(), 1e-6),
+                           np.array(positions), 1e6, rd)
+        assert np.abs(qr - ref).max() < 2e-2  # the 32-bit angle at position 40959
+        assert np.abs(qr[:4] - ref[:4]).max() < 2e-5
+
+
+@pytest.mark.parametrize("nq,nkv,d,T,window", [(4, 2, 16, 70, None), (6, 1, 32, 129, None), (3, 1, 48, 100, 37),
+                                                (8, 2, 128, 66, 5), (2, 1, 80, 33, None)])
+def test_f32_attention_equals_the_host_mirror(nq, nkv, d, T, window):
+    import fp32_mirror as mir
+
+    g = torch.Generator().manual_seed(nq * 31 + d)
+    slots, table, kp, vp, ks, vs = _paged([T], nkv, d, torch.float32, g)
+    q = torch.randn(T, nq, d, generator=g) * 3
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(d)))
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    out = ops().attention_plain(q.reshape(T, nq * d).to(DEV), kp.to(DEV), vp.to(DEV), table.to(DEV), 64,
+                                i32(list(range(T))), i32([slots[0]] * T), nq, nkv, d, window, scale)
+    ref = mir.attention(q.numpy(), ks[0].numpy(), vs[0].numpy(), scale, window)
+    assert _bits_equal(out.reshape(T, nq, d), ref)

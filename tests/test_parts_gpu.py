@@ -47,8 +47,9 @@ def test_norm_rope_and_mlp_parts():
         assert relerr(got, ref) < tol
 
     rope = POSITIONS.get("rope_neox")(PositionSpec("rope_neox", head_dim=48, rotary_dim=32, theta=5e4), torch.float32, DEV)
-    denom, rd = rope.rotation()
-    assert rd == 32 and denom.dtype == torch.float32
+    rot = rope.rotation()
+    denom, rd = rot.denominators, rot.rotary_dim
+    assert rd == 32 and denom.dtype == torch.float32 and rot.pairing == "half" and rot.magnitude == 1.0
     want = np.power(5e4, np.arange(16) * 2.0 / 32)
     np.testing.assert_allclose(denom.cpu().numpy(), want, rtol=1e-7)
 
@@ -276,7 +277,9 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding():
             pass
 
         def rotation(self):
-            return self.denominators, self.spec.rotary_dim
+            from reflex_b200.parts import Rotation
+
+            return Rotation(self.denominators, self.spec.rotary_dim)
 
     H, V, nq, nkv, d, I, E = 48, 101, 3, 1, 32, 40, 3
     theta, factor, window, eps = 1e4, 4.0, 9, 1e-5

@@ -104,6 +104,66 @@ def test_formulas_match_the_reference_sources():
         np.testing.assert_allclose(got.reshape(-1), np.array(case["y"]), rtol=0, atol=case["atol"])
     s = g["silu_and_mul"]
     gate, up = np.array(s["gate"]), np.array(s["up"])
-    np.testing.assert_allclose((gate / (1.0 + np.exp(-gate))) * up, np.array(s["y"]), rtol=2e-6, atol=1e-7)
+    # through the function the engine is held to: with x = [gate, up] and selector
+    # matrices, pm.swiglu's products hand it exactly these gates and ups
+    n = len(gate)
+    eye, zero = np.eye(n), np.zeros((n, n))
+    x = np.concatenate([gate, up])[None, :]
+    got = pm.swiglu(x, np.hstack([eye, zero]), np.hstack([zero, eye]), eye)[0]
+    np.testing.assert_allclose(got, np.array(s["y"]), rtol=2e-6, atol=1e-7)
     a = g["add"]
     np.testing.assert_allclose(np.array(a["a"]) + np.array(a["b"]), np.array(a["y"]), rtol=1e-7)
+
+
+# ----------------------------------------------------------- the 32-bit mirror
+def test_mirror_exponential_and_sine_cosine_are_accurate():
+    """The mirror's own exp and sin/cos (IEEE operations only) against NumPy in
+    double: a few units in the last place at most, over the ranges the model
+    uses (softmax and SiLU arguments; angles up to a long context's position)."""
+    import fp32_mirror as mir
+
+    rng = np.random.default_rng(0)
+    xs = np.concatenate([rng.uniform(-90, 88.7, 4000), rng.uniform(-1, 1, 2000), [0.0, -0.0, 88.7, -87.3, -103.0]])
+    for x in xs.astype(np.float32):
+        got, ref = mir.exp(float(x)), math.exp(float(x))
+        assert abs(got - ref) <= 3 * np.spacing(np.float32(ref)), (x, got, ref)
+    assert mir.exp(float("-inf")) == 0.0 and mir.exp(-200.0) == 0.0 and mir.exp(100.0) == float("inf")
+    assert math.isnan(mir.exp(float("nan")))
+    assert 0.0 < mir.exp(-100.0) < 1e-43  # a subnormal result
+    for t in np.concatenate([rng.uniform(-10, 10, 2000), rng.uniform(0, 1e5, 3000), [0.0, 40959.0, 1.0e7]]).astype(np.float32):
+        s, c = mir.sincos(float(t))
+        assert abs(s - math.sin(float(t))) <= 6.1e-8 and abs(c - math.cos(float(t))) <= 6.1e-8, t
+
+
+def test_mirror_agrees_with_the_plain_model_and_sees_a_changed_order():
+    """The mirror follows the same formulas as the float64 plain model (so it is
+    within 32-bit rounding of it), and a change of one reduction order (the
+    norm's sum of squares in plain index order) changes its bits: a bit-for-bit
+    comparison with it therefore sees such a change in a kernel."""
+    import fp32_mirror as mir
+    import helpers
+
+    for name in ("A", "B"):
+        folder = helpers.model_folder(name, 7, "float32")
+        cfg, w = pm.read_model(folder)
+        toks = helpers.random_tokens(40, cfg["vocab_size"], 1)
+        ref = pm.forward(cfg, w, toks)
+        got = mir.forward(cfg, w, toks)
+        assert got.dtype == np.float32 and got.shape == ref.shape
+        assert helpers.rel_err(got, ref) < 3e-6
+        other = mir.forward(cfg, w, toks, norm_order=1)
+        assert helpers.rel_err(other, ref) < 3e-6
+        assert not np.array_equal(got, other)
+    # each part alone against its plain form
+    rng = np.random.default_rng(3)
+    T, nq, nkv, d = 9, 6, 2, 48
+    q, k, v = (rng.normal(size=(T, n, d)).astype(np.float32) for n in (nq, nkv, nkv))
+    a = mir.attention(q, k, v, 0.2, 4)
+    np.testing.assert_allclose(a, pm.causal_attention(q.astype(np.float64), k.astype(np.float64), v.astype(np.float64), 0.2, 4),
+                               rtol=2e-5, atol=2e-6)
+    wn = (1 + 0.1 * rng.normal(size=d)).astype(np.float32)
+    pos = np.array([0, 1, 5, 63, 64, 200, 999, 4095, 40000])
+    got = mir.head_norm_rope(q, wn, 1e-6, mir.rope_denominators(1e4, 32), 32, pos)
+    ref = pm.rope_neox(pm.rms_norm(q.astype(np.float64), wn.astype(np.float64), 1e-6), pos, 1e4, 32)
+    np.testing.assert_allclose(got, ref, rtol=0, atol=5e-3)  # the 32-bit angle is off by up to pos * 2^-24
+    np.testing.assert_allclose(got[:3], ref[:3], rtol=0, atol=2e-6)  # positions 0, 1, 5

@@ -180,7 +180,7 @@ def main() -> int:
         scratch = torch.empty((batch * 128,), dtype=torch.float32, device="cuda:0")
         ops.argmax(logits, out=ids[0], scratch=scratch)
         for i in range(warmup):
-            logits = eng.step_decode(seqs, ids[i % 2])
+            logits = eng.step_decode(seqs, ids[i % 2], borrow=True)
             ops.argmax(logits, out=ids[(i + 1) % 2], scratch=scratch)
         launches0 = ops.launch_count()
         ctx0 = eng.length(seqs[0])
@@ -189,7 +189,7 @@ def main() -> int:
         t0 = sampler.mark() if sampler else 0
         start.record()
         for i in range(warmup, warmup + steps):
-            logits = eng.step_decode(seqs, ids[i % 2])
+            logits = eng.step_decode(seqs, ids[i % 2], borrow=True)
             ops.argmax(logits, out=ids[(i + 1) % 2], scratch=scratch)
         end.record()
         torch.cuda.synchronize()

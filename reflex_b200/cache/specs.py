@@ -15,6 +15,14 @@ class KVSpec:
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    # size of a value vector when it differs from a key vector's (a compressed
+    # latent cache; the reference's attention parameters carry separate K and V
+    # strides for it, src/kernels_cuda/attention_online.cu:22-23); None: head_dim
+    v_head_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)

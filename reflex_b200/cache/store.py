@@ -40,7 +40,7 @@ class KVView:
     """What a kernel needs to read and write one cache entry."""
 
     k_pages: torch.Tensor  # [pages, kv heads, PAGE_TOKENS, head_dim]
-    v_pages: torch.Tensor
+    v_pages: torch.Tensor  # [pages, kv heads, PAGE_TOKENS, value_dim]
     page_table: torch.Tensor  # int32 [slots, pages per sequence]
     page_size: int
     spec: KVSpec
@@ -56,10 +56,11 @@ class KVGroup:
         self.pages_per_seq = pages_per_seq
         self.pool = IdPool(n_pages, "page")
         shape = (len(self.entries), n_pages, spec.n_kv_heads, PAGE_TOKENS, spec.head_dim)
+        v_shape = shape[:-1] + (spec.value_dim,)
         self.device = device
         if device is not None:
             self.k = torch.empty(shape, dtype=dtype, device=device)
-            self.v = torch.empty(shape, dtype=dtype, device=device)
+            self.v = torch.empty(v_shape, dtype=dtype, device=device)
             self.table_dev = torch.zeros((max_slots, pages_per_seq), dtype=torch.int32, device=device)
         else:  # bookkeeping only (host tests)
             self.k = self.v = self.table_dev = None
@@ -150,8 +151,25 @@ class StateGroup:
             self.data[:, slot].zero_()
 
     def view(self, entry: int) -> torch.Tensor:
-        """[slots, *shape]; a mixer indexes it by a sequence's slot."""
+        """[slots, *shape]; a mixer indexes it by a sequence's slot: on the host
+        (`batch.slots`), or with the step's device-side indices
+        (`batch.seq_slot`, `batch.row_slot`; `index_select` / `index_copy_`), which
+        keeps its launches free of host values so that they can be captured."""
         return self.data[self.index[entry]]
+
+    def snapshot(self, slots: Sequence[int]):
+        """The state of the given slots, copied aside before a step runs: fixed-size
+        state is overwritten in place and cannot be rewound any other way
+        (src/model/mod.rs:1026-1030)."""
+        if self.data is None:
+            return None
+        idx = torch.tensor(list(slots), dtype=torch.int64, device=self.data.device)
+        return idx, self.data.index_select(1, idx)
+
+    def restore(self, saved) -> None:
+        if saved is not None:
+            idx, data = saved
+            self.data.index_copy_(1, idx, data)
 
 
 class Cache:
@@ -246,6 +264,18 @@ class Cache:
                 g.grow(slot, self.lengths[slot] + n_new)
         for g in self.kv_groups:
             g.flush()
+
+    def snapshot_state(self, slots: Sequence[int]):
+        """What `restore_state` needs to put the slots' fixed-size state back as it
+        is now; None when the model keeps no such state (then nothing is copied)."""
+        if not self.state_groups:
+            return None
+        return [g.snapshot(slots) for g in self.state_groups]
+
+    def restore_state(self, saved) -> None:
+        if saved is not None:
+            for g, s in zip(self.state_groups, saved):
+                g.restore(s)
 
     def commit(self, growth: Sequence[Tuple[int, int]]) -> None:
         for slot, n_new in growth:

@@ -85,6 +85,12 @@ class LayerSpec:
     mixer_norm: NormSpec
     feed_forward_norm: NormSpec
     names: Tuple[Tuple[str, str], ...] = ()
+    # further norms of the arrangement, by role (sandwich norms after the mixer and
+    # after the feed-forward, before the residual add: src/model/dense.rs:72-83,
+    # 928-930), and any other option of it: a block registered outside the
+    # framework reads them, the framework only carries them
+    extra_norms: Tuple[Tuple[str, NormSpec], ...] = ()
+    params: Tuple[Tuple[str, Any], ...] = ()
 
 
 @dataclass(frozen=True)

@@ -56,6 +56,18 @@ inline bool pdl_enabled() {
     return v != 0;
 }
 
+// Streaming multiprocessors of the current device, asked once (148 on a B200).
+inline int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
 // Launch with the library's attributes; cluster_z > 1 asks for a thread-block
 // cluster of (1, 1, cluster_z).
 template <typename... KArgs, typename... Args>

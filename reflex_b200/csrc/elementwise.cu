@@ -249,14 +249,14 @@ extern "C" int rfx_swiglu(const void* gate_up, void* out, int dt, int R, int I, 
     cudaStream_t s = (cudaStream_t)stream;
     const size_t n = (size_t)R * I;
     int blocks = (int)((n + 255) / 256);
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > sm_count() * 16) blocks = sm_count() * 16;
     if (dt == RFX_DT_F32)
         RFX_LAUNCH(swiglu_kernel<float>, blocks, 256, 0, s, (const float*)gate_up, (float*)out, R, I,
                    alternating);
     else if (dt == RFX_DT_BF16 && I % 8 == 0 &&
              ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
         int b8 = (int)((n / 8 + 255) / 256);
-        if (b8 > 148 * 8) b8 = 148 * 8;
+        if (b8 > sm_count() * 8) b8 = sm_count() * 8;
         RFX_LAUNCH(swiglu_bf16x8_kernel, b8, 256, 0, s, (const __nv_bfloat16*)gate_up,
                    (__nv_bfloat16*)out, R, I, alternating);
     } else if (dt == RFX_DT_BF16)
@@ -271,7 +271,7 @@ extern "C" int rfx_add(float* a, const void* b, int b_dt, long long n, void* str
     if (n <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     int blocks = (int)((n + 255) / 256);
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > sm_count() * 16) blocks = sm_count() * 16;
     if (b_dt == RFX_DT_F32)
         RFX_LAUNCH(add_kernel<float>, blocks, 256, 0, s, a, (const float*)b, (size_t)n);
     else if (b_dt == RFX_DT_BF16)

@@ -626,22 +626,24 @@ const CUtensorMap* cached_map(const void* base, int rows, int cols, int box_rows
     return &cache.emplace(key, m).first->second;
 }
 
-int sm_count() {
-    static int n = 0;
-    if (!n) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        if (n <= 0) n = 148;
-    }
-    return n;
-}
+using rfx::sm_count;
 
 int g_trace_next = 0;  // launch counter: the trace record a launch writes
 
 int env_int(const char* name, int dflt) {
     const char* e = getenv(name);
     return e ? atoi(e) : dflt;
+}
+
+// Tuning aids, read from the environment once, at the first product.
+struct Knobs {
+    int cps, even, smem_kb, stages, smem_cap_kb, l2pf_mb;
+};
+const Knobs& knobs() {
+    static const Knobs k = {env_int("REFLEX_B200_GEMM_CPS", 0),      env_int("REFLEX_B200_GEMM_EVEN", 1),
+                            env_int("REFLEX_B200_GEMM_SMEM_KB", 110), env_int("REFLEX_B200_GEMM_STAGES", 0),
+                            env_int("REFLEX_B200_GEMM_SMEM_CAP_KB", 112), env_int("REFLEX_B200_GEMM_L2PF_MB", 0)};
+    return k;
 }
 
 // How a product is cut into CTAs.  Streaming weights at HBM speed needs every SM
@@ -657,7 +659,7 @@ struct Cut {
 Cut choose_cut(int N, int r_tiles, int num_kb, int ks_req) {
     if (ks_req > 0) return Cut{BM, (N + BM - 1) / BM, ks_req};
     const int sms = sm_count();
-    const int cps_first = env_int("REFLEX_B200_GEMM_CPS", 0);  // tuning aid: CTAs per SM to try first
+    const int cps_first = knobs().cps;  // tuning aid: CTAs per SM to try first
     for (int pass = 0; pass < 2 && cps_first > 0; ++pass) {
         const int c = cps_first ? (pass == 0 ? cps_first : 3 - cps_first) : (pass == 0 ? 1 : 2);
         if (c < 1 || c > 2) continue;
@@ -680,7 +682,7 @@ Cut choose_cut(int N, int r_tiles, int num_kb, int ks_req) {
     const int tiles = (N + BM - 1) / BM;
     // Between one and two 128-row tiles per SM the SMs that get two CTAs finish
     // late while the rest idle: cut lower tiles instead, two per SM, equal work.
-    if (r_tiles == 1 && tiles > sms && tiles < 2 * sms && env_int("REFLEX_B200_GEMM_EVEN", 1)) {
+    if (r_tiles == 1 && tiles > sms && tiles < 2 * sms && knobs().even) {
         int bm = (N + 2 * sms - 1) / (2 * sms);
         bm = (bm + 1) & ~1;
         if (bm >= 32 && bm <= BM) return Cut{bm, (N + bm - 1) / bm, 1};
@@ -710,15 +712,15 @@ int launch(const void* x, const void* W, void* y, int R, int N, int K, int kspli
     // A ring of about 72 KB: three CTAs fit an SM, so the kernels that follow
     // (launched early, see common.cuh) are resident and prefetch their weights
     // while this one runs; a deeper ring measured slower for that reason.
-    int stages = (env_int("REFLEX_B200_GEMM_SMEM_KB", 110) * 1024) / S::STAGE_BYTES;
+    int stages = (knobs().smem_kb * 1024) / S::STAGE_BYTES;
     if (stages < 3) stages = 3;
-    const int st_env = env_int("REFLEX_B200_GEMM_STAGES", 0);  // tuning aid
+    const int st_env = knobs().stages;  // tuning aid
     if (st_env >= 2) stages = st_env;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 2) stages = 2;
     // after the stages, the tile that receives the cluster's partial rows
     constexpr int RECV_BYTES = BN * BM * 4;
-    const int cap = env_int("REFLEX_B200_GEMM_SMEM_CAP_KB", 112) * 1024;  // tuning aid
+    const int cap = knobs().smem_cap_kb * 1024;  // tuning aid
     while (stages > 3 && stages * S::STAGE_BYTES + RECV_BYTES > cap) --stages;
     if (stages * S::STAGE_BYTES < BN * BM * 4) return RFX_ERR_UNSUPPORTED;  // the squares of EPI 2
     if (n_part_out) *n_part_out = cut.tiles * ks;
@@ -728,7 +730,7 @@ int launch(const void* x, const void* W, void* y, int R, int N, int K, int kspli
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     // L2 prefetch before the dependency wait: up to a budget for the whole grid
-    const long long budget = (long long)env_int("REFLEX_B200_GEMM_L2PF_MB", 0) << 20;
+    const long long budget = (long long)knobs().l2pf_mb << 20;
     const long long ctas = (long long)cut.tiles * r_tiles * ks;
     int l2_ahead = (int)(budget / (ctas * cut.bm * BK * 2));
     if (r_tiles > 1) l2_ahead = 0;  // prefill-sized calls are not bandwidth-bound
@@ -815,7 +817,9 @@ extern "C" int rfx_gemm_bf16_tc_residual(const void* x, const void* W, float* h,
 }
 
 // An upper bound of the partials a residual product of N weight rows writes per row.
-extern "C" int rfx_gemm_bf16_tc_max_parts(int N) { return ((N + 31) / 32) * 8 + 8 * 148 * 2; }
+extern "C" int rfx_gemm_bf16_tc_max_parts(int N) { return ((N + 31) / 32) * 8 + 8 * sm_count() * 2; }
+
+extern "C" int rfx_sm_count() { return sm_count(); }
 
 // Tuning aid: give the product kernel a device buffer of launches * ctas records of
 // four 64-bit timestamps; the next launch writes record 0.  Null turns it off.

@@ -66,8 +66,10 @@ def decode_step(batch: int, layers: int, prompt: int, config: Dict, out=sys.stdo
     lib.rfx_gemm_trace.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
     n_launch, n_cta = 4 * layers + 1, 1200
     buf = torch.zeros((n_launch * n_cta * 8,), dtype=torch.int64, device="cuda:0")
+    from .engine.graphs import DecodeGraph
+
     for i in range(6):
-        if i == 2:  # this call captures the step's graph: its launches get trace ids from 0
+        if i == DecodeGraph.WARMUP:  # this call captures the step's graph: its launches get trace ids from 0
             lib.rfx_gemm_trace(buf.data_ptr(), n_launch, n_cta)
         logits = eng.step([(s, [t], [0]) for s, t in zip(seqs, ids)])
         ids = ops.argmax(logits).tolist()

@@ -84,6 +84,9 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int,
     max_batch = max(1, min(max_batch, engine.cache.max_slots))
     check_errors = getattr(engine, "check_errors", lambda: None)
     ahead = pick_async is not None and hasattr(engine, "step_decode")
+    # the loop picks from a step's logits before it runs the next step, so it can
+    # do without the copy that makes logits outlive later steps
+    kw = {"borrow": True} if getattr(engine, "lends_logits", False) else {}
     for batch in plan_batches([len(p) for p in prompts], max_new_tokens, engine.cache.max_tokens, max_batch):
         stats.batches += 1
         live = list(batch)
@@ -95,11 +98,11 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int,
             stats.prefill_tokens += sum(len(prompts[i]) for i in live)
             if ahead:
                 _decode_ahead(engine, entries, live, seqs, outputs, max_new_tokens, stops, pick_async,
-                              on_token, stats, check_errors)
+                              on_token, stats, check_errors, kw)
                 continue
             first = True
             while live:
-                logits = engine.step(entries)
+                logits = engine.step(entries, **kw)
                 ids = pick(logits, live, [len(outputs[i]) for i in live])
                 if first or stats.decode_steps % 64 == 0:
                     check_errors()  # the picked ids are on the host: the device has been waited for
@@ -127,7 +130,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int,
 
 
 def _decode_ahead(engine, entries, live, seqs, outputs, max_new_tokens, stops, pick_async, on_token,
-                  stats, check_errors) -> None:
+                  stats, check_errors, kw) -> None:
     """One batch, the device kept one step ahead of the host.
 
     The ids a step picks stay on the device and feed the next step at once; the
@@ -137,7 +140,7 @@ def _decode_ahead(engine, entries, live, seqs, outputs, max_new_tokens, stops, p
     slot is given back only after the step has finished with its pages.
     Requests that end by count are known in time and never ride along.  The
     tokens returned are the same as the loop that waits for every step gives."""
-    logits = engine.step(entries)
+    logits = engine.step(entries, **kw)
     pending = pick_async(logits, live, [len(outputs[i]) for i in live])
     ended: set = set()  # picked a stop token; their row may still be in flight
     first = True
@@ -152,7 +155,7 @@ def _decode_ahead(engine, entries, live, seqs, outputs, max_new_tokens, stops, p
             else:
                 at = {i: r for r, i in enumerate(live)}
                 tokens_dev = pending.dev[[at[i] for i in goes_on]]
-            logits = engine.step_decode([seqs[i] for i in goes_on], tokens_dev)
+            logits = engine.step_decode([seqs[i] for i in goes_on], tokens_dev, **kw)
             next_pending = pick_async(logits, goes_on, [len(outputs[i]) + 1 for i in goes_on])
         ids = pending.wait()  # the step that picked them is over: the rows it carried are free
         if first or stats.decode_steps % 64 == 0:

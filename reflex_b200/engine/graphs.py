@@ -2,10 +2,19 @@
 
 A decode step is a fixed set of launches whose sizes depend only on the number
 of sequences; positions, slots and tokens are read from device memory.  So one
-graph per batch size is captured at its first use and replayed afterwards with
-new contents copied into the same descriptor buffer.  (The reference's attempt
-failed because positions were kernel arguments that changed each step:
-docs/design/decode-speed.md:189-207.)
+graph per (batch size, context bucket) is captured at its first use and
+replayed afterwards with new contents copied into the same descriptor buffer.
+(The reference's attempt failed because positions were kernel arguments that
+changed each step: docs/design/decode-speed.md:189-207.)
+
+All graphs of an engine allocate from one memory pool: only one of them runs at
+a time, so they share their intermediate buffers and a batch that shrinks
+through many sizes does not grow the device memory with every size.  Their
+results therefore live in shared storage too, and `run` hands out a copy unless
+the caller asks to borrow the graph's own buffer.  Only the engine's very first
+decode step runs eagerly (it sizes the lazily made buffers); every later
+(size, bucket) captures at its first use.  The engine keeps at most
+`Engine.max_graphs` graphs and drops the least recently used.
 """
 
 from __future__ import annotations
@@ -16,7 +25,7 @@ from .batch import layout, make_batch
 
 
 class DecodeGraph:
-    WARMUP = 2
+    WARMUP = 1  # eager decode steps per engine before the first capture
 
     def __init__(self, engine, n_seqs: int, context_hint: int):
         self.engine = engine
@@ -31,10 +40,12 @@ class DecodeGraph:
         self.calls = 0
         self.kernels = 0
 
-    def run(self, tokens, slots, starts, want, tokens_dev=None) -> torch.Tensor:
+    def run(self, tokens, slots, starts, want, tokens_dev=None, borrow: bool = False) -> torch.Tensor:
         """`tokens_dev` (int32 [n] on the device), when given, takes the place of
         the host `tokens`: it is copied over the descriptor's token field on the
-        stream, after the descriptor itself."""
+        stream, after the descriptor itself.  The logits are a copy of the
+        graph's result; with `borrow` they are the graph's own buffer, valid
+        only until the engine's next step."""
         eng = self.engine
         batch = make_batch(tokens, slots, starts, want, eng.device, buffer=self.buffer, staging=eng.staging)
         if tokens_dev is not None:
@@ -43,9 +54,8 @@ class DecodeGraph:
         if self.graph is None:
             # the first decode steps of a batch size run eagerly: they size every
             # lazily allocated buffer; later graphs of that size capture at once
-            done = eng._eager_decodes.get(self.n, 0)
-            if done < self.WARMUP:
-                eng._eager_decodes[self.n] = done + 1
+            if eng._eager_decodes < self.WARMUP:
+                eng._eager_decodes += 1
                 return eng.model.forward(batch, eng.cache)
             # capture: the eager call above has already sized every lazy buffer
             torch.cuda.synchronize()
@@ -53,9 +63,9 @@ class DecodeGraph:
             from .. import ops
 
             before = ops.launch_count()
-            with torch.cuda.graph(g):
+            with torch.cuda.graph(g, pool=eng.graph_pool()):
                 self.logits = eng.model.forward(batch, eng.cache)
             self.kernels = ops.launch_count() - before  # this library's kernels in the graph
             self.graph = g
         self.graph.replay()
-        return self.logits
+        return self.logits if borrow else self.logits.clone()

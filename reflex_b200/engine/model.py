@@ -54,7 +54,18 @@ class CausalLM:
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, dtype, self.device)
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
-        self.err_flag = torch.zeros((1,), dtype=torch.int32, device=self.device)
+
+    @property
+    def capturable(self) -> bool:
+        """True when every layer and the final norm declare `capturable = True`:
+        their launches take positions, slots and lengths from device memory
+        (`StepBatch`'s device fields) and nothing forces the host to wait, so a
+        decode step can be captured once and replayed.  A part that walks host
+        lists, or synchronises (a `.nonzero()`, an `.item()`), leaves the
+        attribute out or sets it False, and the engine then runs every step
+        eagerly."""
+        return (all(bool(getattr(l, "capturable", False)) for l in self.layers)
+                and bool(getattr(self.final_norm, "capturable", False)))
 
     # --- weights ----------------------------------------------------------
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -88,13 +99,16 @@ class CausalLM:
     # --- forward ----------------------------------------------------------
     def hidden_states(self, batch, cache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         ops.prof_mark("start")
-        h = ops.embed(self.embedding, batch.tokens, self.spec.embedding_scale, self.err_flag)
+        # a token id outside the vocabulary (possible only for ids fed from the device)
+        # gives a zero row and sets the device's error word, which `check_errors` reads
+        h = ops.embed(self.embedding, batch.tokens, self.spec.embedding_scale,
+                      ops.device_error_word(self.device))
         ops.prof_mark("embed")
         pending = None
         order = self.spec.run_order
         for i, run in enumerate(order):
             # the norm that will consume this run's result: the next run's first norm, or the final one
-            next_norm = (getattr(self.layers[order[i + 1].layer], "mixer_norm", None)
+            next_norm = (getattr(self.layers[order[i + 1].layer], "fusable_first_norm", None)
                          if i + 1 < len(order) else self.final_norm)
             ctx = RunContext(batch=batch, writes_cache=run.writes_cache, entry=run.cache)
             kind = cache.has(run.cache)
@@ -103,7 +117,7 @@ class CausalLM:
             elif kind == "state":
                 ctx.state = cache.state(run.cache)
             layer = self.layers[run.layer]
-            if hasattr(layer, "mixer_norm"):
+            if hasattr(layer, "fusable_first_norm"):
                 h, pending = layer.forward(h, pending, ctx, next_norm=next_norm)
             else:
                 h, pending = layer.forward(h, pending, ctx)

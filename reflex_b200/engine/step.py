@@ -4,8 +4,10 @@
 (a whole prompt, a chunk of one, or a single decoded token) and the places
 among them whose logits are wanted.  It runs exactly those tokens as one packed
 batch against the cache that earlier steps left, writes their keys and values,
-and returns float32 logits [wanted, vocab].  There is no padding: a row's
-result depends only on its own sequence.  The reference has the two special
+and returns float32 logits [wanted, vocab] that belong to the caller (a later
+step never overwrites them; `borrow=True` spares the copy of a replayed decode
+step's logits, which are then valid only until the next step).  There is no
+padding: a row's result depends only on its own sequence.  The reference has the two special
 cases, a whole-prompt prefill of one sequence and a one-token step
 (src/model/dense.rs:1930-1985, src/model/decode_step.rs:139-329); batches and
 mixed steps are this library's own.
@@ -32,16 +34,24 @@ def ops_profile_on() -> bool:
 
 
 class Engine:
+    lends_logits = True  # `step(..., borrow=True)` is understood
+
     def __init__(self, model: CausalLM, max_tokens: int, max_slots: Optional[int] = None,
-                 use_graphs: bool = True):
+                 use_graphs: bool = True, max_graphs: int = 48):
         self.model = model
         self.device = model.device
         self.cache = Cache(model.cache_entry_specs(), max_tokens, model.spec.max_positions,
                            model.dtype, model.device, max_slots=max_slots)
         self.vocab_size = model.spec.vocab_size
-        self.use_graphs = use_graphs and model.dtype == torch.bfloat16
-        self._graphs: Dict[Tuple[int, int], "object"] = {}
-        self._eager_decodes: Dict[int, int] = {}  # eager decode steps run so far, per batch size
+        # decode steps are captured into CUDA graphs when every part of the model
+        # says that its launches may be (`CausalLM.capturable`) and the path is
+        # the serving one; the 32-bit path always runs eagerly
+        self.use_graphs = bool(use_graphs and model.dtype == torch.bfloat16 and model.capturable
+                               and torch.device(self.device).type == "cuda")
+        self.max_graphs = max(1, int(max_graphs))
+        self._graphs: Dict[Tuple[int, int], "object"] = {}  # insertion order = least recently used first
+        self._graph_pool = None
+        self._eager_decodes = 0  # eager decode steps run so far
         self.steps_run = 0
         self.staging = Staging(self.device) if torch.device(self.device).type == "cuda" else None
 
@@ -65,6 +75,12 @@ class Engine:
 
         ops.check_device_errors(self.device)
 
+    def graph_pool(self):
+        """The one memory pool all of this engine's decode graphs allocate from."""
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        return self._graph_pool
+
     # --- the step -------------------------------------------------------------
     def _check(self, entries: Sequence[StepEntry]) -> None:
         if not entries:
@@ -85,7 +101,7 @@ class Engine:
                     raise InvalidInput(
                         f"sequence {seq}: wanted place {w} is outside this step's {len(tokens)} tokens")
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], borrow: bool = False) -> torch.Tensor:
         self._check(entries)
         cache = self.cache
         slots = [int(e[0]) for e in entries]
@@ -95,10 +111,12 @@ class Engine:
         growth = [(s, len(t)) for s, t in zip(slots, tokens)]
         before = [[g.end[s] for s in slots] for g in cache.kv_groups]
         cache.reserve(growth)
+        saved_state = cache.snapshot_state(slots)
         try:
             n_want = sum(len(w) for w in want)
-            if self.use_graphs and all(len(t) == 1 for t in tokens) and n_want == len(tokens):
-                logits = self._decode_graphed(tokens, slots, starts, want)
+            # the captured step has one token and one wanted row, that token's, per sequence
+            if self.use_graphs and all(len(t) == 1 for t in tokens) and all(w == [0] for w in want):
+                logits = self._decode_graphed(tokens, slots, starts, want, borrow=borrow)
             else:
                 batch = make_batch(tokens, slots, starts, want, self.device, staging=self.staging)
                 if n_want:
@@ -107,9 +125,11 @@ class Engine:
                     self.model.hidden_states(batch, cache)
                     logits = torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         except Exception:
+            # the cache as it was: pages given back, fixed-size state put back
             for g, ends in zip(cache.kv_groups, before):
                 for s, e in zip(slots, ends):
                     g.shrink_to(s, e)
+            cache.restore_state(saved_state)
             raise
         cache.commit(growth)
         self.steps_run += 1
@@ -119,13 +139,15 @@ class Engine:
             ops.prof_report(f"{self.steps_run - 1}:rows={sum(len(t) for t in tokens)}")
         return logits
 
-    def step_decode(self, seqs: Sequence[int], tokens_dev: torch.Tensor) -> torch.Tensor:
+    def step_decode(self, seqs: Sequence[int], tokens_dev: torch.Tensor, borrow: bool = False) -> torch.Tensor:
         """One decode step whose tokens are already on the device: sequence
         `seqs[i]` goes on by token `tokens_dev[i]` (int32), and the logits of
         every row come back, float32 [len(seqs), vocab].  Nothing waits for the
         host, so a caller can enqueue the step while it is still reading the
         ids that feed it (the generation loop does).  The ids must be valid
-        token ids: ids picked from this model's logits are."""
+        token ids: ids picked from this model's logits are (an id outside the
+        vocabulary gives a zero embedding row and is reported by
+        `check_errors`).  `borrow` as in `step`."""
         n = len(seqs)
         if n == 0:
             raise InvalidInput("a step needs at least one sequence")
@@ -141,24 +163,27 @@ class Engine:
         growth = [(s, 1) for s in slots]
         before = [[g.end[s] for s in slots] for g in cache.kv_groups]
         cache.reserve(growth)
+        saved_state = cache.snapshot_state(slots)
         try:
             if self.use_graphs:
-                logits = self._decode_graphed(tokens, slots, starts, want, tokens_dev=tokens_dev)
+                logits = self._decode_graphed(tokens, slots, starts, want, tokens_dev=tokens_dev, borrow=borrow)
             else:
                 batch = make_batch(tokens, slots, starts, want, self.device, staging=self.staging)
                 batch.tokens.copy_(tokens_dev)
                 logits = self.model.forward(batch, cache)
         except Exception:
+            # the cache as it was: pages given back, fixed-size state put back
             for g, ends in zip(cache.kv_groups, before):
                 for s, e in zip(slots, ends):
                     g.shrink_to(s, e)
+            cache.restore_state(saved_state)
             raise
         cache.commit(growth)
         self.steps_run += 1
         return logits
 
     # --- decode steps as CUDA graphs -----------------------------------------
-    def _decode_graphed(self, tokens, slots, starts, want, tokens_dev=None) -> torch.Tensor:
+    def _decode_graphed(self, tokens, slots, starts, want, tokens_dev=None, borrow=False) -> torch.Tensor:
         from .graphs import DecodeGraph
 
         n = len(tokens)
@@ -167,11 +192,13 @@ class Engine:
         # (batch size, context bucket)
         bucket = decode_context_bucket(max(starts) + 1, PAGE_TOKENS)
         key = (n, bucket)
-        g = self._graphs.get(key)
+        g = self._graphs.pop(key, None)
         if g is None:
             g = DecodeGraph(self, n, bucket)
-            self._graphs[key] = g
-        return g.run(tokens, slots, starts, want, tokens_dev=tokens_dev)
+            while len(self._graphs) >= self.max_graphs:
+                self._graphs.pop(next(iter(self._graphs)))  # the least recently used
+        self._graphs[key] = g  # most recently used last
+        return g.run(tokens, slots, starts, want, tokens_dev=tokens_dev, borrow=borrow)
 
     def launches_per_decode_step(self, n_seqs: int) -> int:
         """This library's kernels in one decode step of `n_seqs` sequences

@@ -190,7 +190,8 @@ def check_device_errors(device="cuda:0") -> None:
     code = int(device_error_word(device).item())
     if code:
         device_error_word(device).zero_()
-        raise CudaError(f"a kernel gave up a bounded wait (code {code}); its results are not valid")
+        raise CudaError(f"a kernel reported an error (code {code}: a bounded wait that ran out, or a token "
+                        f"id outside the vocabulary); the step's results are not valid")
 
 
 def wait_probe(limit_ns: int, device="cuda:0") -> None:
@@ -406,7 +407,15 @@ def gemv_simple(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = 
     return y
 
 
-SM_COUNT = 148
+_SM_COUNT = 0
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device, asked once."""
+    global _SM_COUNT
+    if not _SM_COUNT:
+        _SM_COUNT = int(native.lib().rfx_sm_count())
+    return _SM_COUNT
 
 
 def decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int = 64) -> int:
@@ -426,7 +435,7 @@ def decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int = 64) -> int:
     for s in (1, 2, 4, 8, 16, 32, 64):
         if s > max(1, max_pages):
             break
-        waves = -(-ctas * s // (2 * SM_COUNT))
+        waves = -(-ctas * s // (2 * sm_count()))
         merge = 0.0 if s == 1 else (2.0 + 0.1 * s if s <= 8 else 3.0 + 0.25 * s)
         cost = 4.0 + (-(-max_pages // s) * 0.8 + 1.5) * waves + merge
         if best_cost is None or cost < best_cost - 1e-9:

@@ -77,6 +77,8 @@ def lib() -> ctypes.CDLL:
             fn.restype = c_int
         handle.rfx_gemm_bf16_tc_max_parts.argtypes = [c_int]
         handle.rfx_gemm_bf16_tc_max_parts.restype = c_int
+        handle.rfx_sm_count.argtypes = []
+        handle.rfx_sm_count.restype = c_int
         handle.rfx_sample_work_bytes.argtypes = [c_int, c_int]
         handle.rfx_sample_work_bytes.restype = c_longlong
         handle.rfx_error_string.argtypes = [c_int]

@@ -77,6 +77,13 @@ class GQAttention:
             self.k_norm = tensors["k_norm"].to(device=self.device, dtype=torch.float32).contiguous()
 
     supports_fused_residual = True
+    accepts_normed_input = True  # its first product finishes a norm that the product before began
+
+    @property
+    def capturable(self) -> bool:
+        """Positions, slots and the page table are read from device memory, so a
+        decode step's launches may be captured, if the position part's may."""
+        return self.position is None or bool(getattr(self.position, "capturable", False))
 
     def forward(self, x, ctx, residual=None):
         """x: normed rows (or rows awaiting their norm factor, `ops.NormedInput`).

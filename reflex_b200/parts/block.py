@@ -27,6 +27,19 @@ class PreNormBlock:
         self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, dtype, device)
         self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, dtype, device)
 
+    @property
+    def fusable_first_norm(self):
+        """The norm this layer starts with, if the product before it may begin it
+        (the mixer then gets rows that await their norm factor, an
+        `ops.NormedInput`, which only a mixer that says so accepts); else None."""
+        return self.mixer_norm if getattr(self.mixer, "accepts_normed_input", False) else None
+
+    @property
+    def capturable(self) -> bool:
+        """Whether every part of the layer allows its launches to be captured."""
+        return all(bool(getattr(p, "capturable", False))
+                   for p in (self.mixer_norm, self.feed_forward_norm, self.mixer, self.feed_forward))
+
     @classmethod
     def tensor_names(cls, spec: LayerSpec) -> Dict[str, Tuple[str, str, TensorInfo]]:
         """full tensor name -> (part, role, info) for every tensor of the layer."""
@@ -68,7 +81,8 @@ class PreNormBlock:
             x = self.mixer_norm(hidden, delta=pending)
             ops.prof_mark("norm")
         if getattr(self.mixer, "supports_fused_residual", False):
-            a = self.mixer.forward(x, ctx, residual=(hidden, self.feed_forward_norm))
+            ffn_norm = self.feed_forward_norm if getattr(self.feed_forward, "accepts_normed_input", False) else None
+            a = self.mixer.forward(x, ctx, residual=(hidden, ffn_norm))
         else:
             a = self.mixer.forward(x, ctx)
         if isinstance(a, ops.NormedInput):

@@ -21,6 +21,8 @@ from .registry import TensorInfo, register_feed_forward
 
 @register_feed_forward("swiglu")
 class SwiGLU:
+    capturable = True  # launches read nothing from the host: may be captured into a CUDA graph
+
     def __init__(self, spec: FeedForwardSpec, dtype: torch.dtype, device):
         self.spec = spec
         self.dtype = dtype
@@ -46,6 +48,7 @@ class SwiGLU:
         self.down = dev(tensors["down_proj"]).contiguous()
 
     supports_fused_residual = True
+    accepts_normed_input = True  # its first product finishes a norm that the product before began
 
     def forward(self, x, residual=None):
         """With `residual` = (hidden, next norm) the down projection may add itself

@@ -19,6 +19,8 @@ from .registry import TensorInfo, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm:
+    capturable = True  # launches read nothing from the host: may be captured into a CUDA graph
+
     def __init__(self, spec: NormSpec, dtype: torch.dtype, device):
         self.spec = spec
         self.dtype = dtype

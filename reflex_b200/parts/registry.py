@@ -11,6 +11,11 @@ Interfaces (duck-typed; `spec` is the part's record from `config.spec`):
     tensor_specs(spec) -> {role: TensorInfo}     classmethod; what it loads
     __init__(spec, dtype, device)
     bind(tensors: {role: Tensor})                takes ownership of its weights
+    capturable = True                            optional: its launches take everything that
+                                                 changes from step to step out of device memory
+                                                 and never wait for the host, so a decode step
+                                                 may be captured into a CUDA graph; absent or
+                                                 False: the engine runs every step eagerly
 
   norm            __call__(residual_f32, delta=None, rows=None, update=True) -> normed
   position        rotation() -> Rotation (below) | None

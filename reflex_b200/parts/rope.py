@@ -24,6 +24,8 @@ from .registry import Rotation, TensorInfo, register_position
 
 @register_position("rope_neox")
 class RotaryNeox:
+    capturable = True
+
     def __init__(self, spec: PositionSpec, dtype: torch.dtype, device):
         if spec.rotary_dim % 2 or not (0 < spec.rotary_dim <= spec.head_dim):
             raise InvalidInput(

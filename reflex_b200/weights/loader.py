@@ -23,7 +23,7 @@ import torch
 from ..config.qwen3 import read_config_json
 from ..config.registry import spec_from_config_dict
 from ..config.spec import ModelSpec
-from ..errors import CheckpointError
+from ..errors import CheckpointError, InvalidInput
 from .safetensors_io import Checkpoint
 
 
@@ -82,7 +82,36 @@ def read_tensors(spec: ModelSpec, ckpt) -> Dict[str, torch.Tensor]:
 def load_spec(model_dir: str) -> Tuple[object, ModelSpec]:
     from .. import models  # noqa: F401  (registers the architectures)
 
-    return spec_from_config_dict(read_config_json(model_dir))
+    typed, spec = spec_from_config_dict(read_config_json(model_dir))
+    spec.eos_token_ids = merge_generation_config(model_dir, spec.eos_token_ids)
+    return typed, spec
+
+
+def merge_generation_config(model_dir: str, eos_ids) -> Tuple[int, ...]:
+    """End-of-sequence ids of `generation_config.json`, when the folder has one,
+    joined to config.json's (checkpoints often list further stop ids only
+    there).  The reference takes its one end-of-sequence id from the tokenizer
+    (src/sampling.rs:120-125); this library works on ids, so the model folder's
+    json files are its only source."""
+    import json
+    import os
+
+    path = os.path.join(model_dir, "generation_config.json")
+    out = [int(e) for e in eos_ids]
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                eos = json.load(f).get("eos_token_id")
+        except ValueError as e:
+            raise InvalidInput(f"{path} is not valid JSON: {e}") from None
+        if isinstance(eos, bool) or not (eos is None or isinstance(eos, (int, list, tuple))):
+            raise InvalidInput(f"{path}: eos_token_id must be an integer or a list of integers")
+        for e in ([] if eos is None else [eos] if isinstance(eos, int) else list(eos)):
+            if isinstance(e, bool) or not isinstance(e, int) or e < 0:
+                raise InvalidInput(f"{path}: eos_token_id must hold non-negative integers, got {e!r}")
+            if e not in out:
+                out.append(e)
+    return tuple(out)
 
 
 def load_model(model_dir: str, dtype: torch.dtype = torch.bfloat16, device="cuda:0"):

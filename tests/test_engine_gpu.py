@@ -350,3 +350,99 @@ def test_random_configurations(seed, dtype):
         assert eng.cache.slots.held_count == 0
     finally:
         shutil.rmtree(folder, ignore_errors=True)
+
+
+# ----------------------------------------------- schedules around the decode graphs
+def test_logits_of_two_steps_can_be_held_together():
+    """A step's logits belong to the caller: the next replay of the same graph
+    does not overwrite them.  With `borrow=True` they are the graph's own
+    buffer and the next step does overwrite them, which is what the flag says."""
+    V = ALL["B"]["vocab_size"]
+    folder = helpers.model_folder("B", 7, "bfloat16")
+    eng = helpers.make_engine(folder, "bfloat16", max_tokens=512)
+    toks = helpers.random_tokens(40, V, 8)
+    ref = helpers.plain_logits(folder, toks)
+    s = eng.open()
+    eng.step([(s, toks[:30], [])])
+    kept = [eng.step([(s, [toks[i]], [0])]) for i in range(30, 40)]  # every step's logits held
+    assert any(g.graph is not None for g in eng._graphs.values())
+    for i, l in zip(range(30, 40), kept):
+        assert helpers.rel_err(l.float().cpu().numpy(), ref[i:i + 1]) < BF16_TOL, i
+    eng.close(s)
+    s = eng.open()
+    eng.step([(s, toks[:30], [])])
+    lent = [eng.step([(s, [toks[i]], [0])], borrow=True) for i in range(30, 34)]
+    assert lent[-1].data_ptr() == lent[-2].data_ptr()  # the same storage, as documented
+    eng.close(s)
+
+
+def test_wanted_places_other_than_one_per_token_go_the_eager_way():
+    """[[0, 0], []] for two decode sequences passes the checks and has as many
+    wanted rows as tokens, but is not the captured step's shape."""
+    V = ALL["B"]["vocab_size"]
+    folder = helpers.model_folder("B", 7, "bfloat16")
+    eng = helpers.make_engine(folder, "bfloat16", max_tokens=512)
+    a, b = helpers.random_tokens(20, V, 1), helpers.random_tokens(9, V, 2)
+    sa, sb = eng.open(), eng.open()
+    eng.step([(sa, a[:19], []), (sb, b[:8], [])])
+    out = eng.step([(sa, [a[19]], [0, 0]), (sb, [b[8]], [])]).float().cpu().numpy()
+    ref = helpers.plain_logits(folder, a)[19:20]
+    assert out.shape == (2, V)
+    assert helpers.rel_err(out[0:1], ref) < BF16_TOL and helpers.rel_err(out[1:2], ref) < BF16_TOL
+    eng.close(sa)
+    eng.close(sb)
+
+
+def test_a_batch_of_64_that_ends_one_request_at_a_time():
+    """64 requests decoded together in bfloat16 with graphs on, whose lengths
+    make them leave one after another, so the batch shrinks through every size
+    from 64 to 1.  Logits of several requests against the plain implementation;
+    the number of graphs and the device memory they take stay bounded (they
+    share one pool, and a new size captures at once instead of running eager
+    warm-up steps)."""
+    V = ALL["B"]["vocab_size"]
+    folder = helpers.model_folder("B", 7, "bfloat16")
+    eng = helpers.make_engine(folder, "bfloat16", max_tokens=64 * 64 * 2, max_graphs=40)
+    reqs = [helpers.random_tokens(3 + (i % 5) + i, V, 200 + i) for i in range(64)]  # lengths 3 .. 70, all different
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_reserved()
+    got = helpers.run_batches(eng, reqs, 64, [3])
+    grown = torch.cuda.memory_reserved() - before
+    assert eng._eager_decodes == 1
+    assert len(eng._graphs) <= 40
+    assert grown < 256 << 20, f"decode graphs took {grown >> 20} MiB"
+    for i in (0, 1, 17, 40, 63):
+        assert helpers.rel_err(got[i], helpers.plain_logits(folder, reqs[i])) < BF16_TOL, i
+    assert eng.cache.slots.held_count == 0
+
+
+@pytest.mark.parametrize("n", [65, 100, 128])
+def test_decode_batches_above_64_rows(n):
+    """More decode rows than the weight-streaming product takes: the step
+    leaves the fused path (library products, stand-alone norms) and must give
+    the same logits."""
+    V = ALL["B"]["vocab_size"]
+    folder = helpers.model_folder("B", 7, "bfloat16")
+    eng = helpers.make_engine(folder, "bfloat16", max_tokens=64 * n)
+    reqs = [helpers.random_tokens(4 + i % 7, V, 300 + i) for i in range(n)]
+    got = helpers.run_batches(eng, reqs, n, [2])
+    for i in (0, 1, n // 2, n - 1):
+        assert helpers.rel_err(got[i], helpers.plain_logits(folder, reqs[i])) < BF16_TOL, i
+
+
+def test_a_token_id_fed_from_the_device_outside_the_vocabulary_is_reported():
+    from reflex_b200 import CudaError
+
+    folder = helpers.model_folder("A", 7, "bfloat16")
+    eng = helpers.make_engine(folder, "bfloat16", max_tokens=256)
+    s = eng.open()
+    eng.step([(s, [1, 2, 3], [2])])
+    eng.check_errors()
+    bad = torch.tensor([ALL["A"]["vocab_size"] + 5], dtype=torch.int32, device="cuda:0")
+    eng.step_decode([s], bad)
+    with pytest.raises(CudaError):
+        eng.check_errors()
+    eng.check_errors()  # reported once, the device stays usable
+    out = eng.step([(s, [4], [0])])
+    assert bool(torch.isfinite(out).all())
+    eng.close(s)

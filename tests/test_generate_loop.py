@@ -204,3 +204,20 @@ def test_the_ahead_loop_returns_the_same_tokens_and_frees_everything(prompts, n,
     # a request that picked a stop token rides along for at most one more step
     assert sum(len(st) for st in plain.steps) <= sum(len(st) for st in e.steps) \
         <= sum(len(st) for st in plain.steps) + len(prompts)
+
+
+def test_slots_taken_before_an_open_fails_are_given_back():
+    """If taking a slot fails part-way through a batch's start, the slots
+    already taken go back: nothing stays held for the life of the engine."""
+    from reflex_b200 import OutOfMemory
+
+    class Stingy(FakeEngine):
+        def open(self):
+            if self.cache.slots.held_count >= 2:
+                raise OutOfMemory("no slot left (made up by the test)")
+            return super().open()
+
+    e = Stingy()
+    with pytest.raises(OutOfMemory):
+        generate(e, [[1], [2], [3]], 2, greedy)
+    assert e.cache.slots.held_count == 0

@@ -232,3 +232,25 @@ def test_diagnostics_print_a_decode_steps_timeline():
     assert [l[0] for l in lines] == ["qkv", "o", "gate_up", "down"] * 2 + ["head"]
     left = [float(l[-2]) if len(l) > 11 else float(l[-1]) for l in lines]  # released -> left, us
     assert all(0.0 < v < 1000.0 for v in left)
+
+
+def test_system1_refuses_bad_candidates_and_gives_its_slots_back():
+    """A candidate's last id never goes through the step (it only picks a
+    logit), so it is checked on the host; and more candidates than free slots
+    are refused before any slot is taken."""
+    import reflex_b200
+    from reflex_b200 import InvalidInput, OutOfMemory
+
+    folder = helpers.model_folder("A", 7, "float32")
+    model = reflex_b200.Model.load(folder, weights="f32", max_tokens=1024)
+    V = ALL["A"]["vocab_size"]
+    for bad in ([1, V], [V + 3], [2, -1]):
+        with pytest.raises(InvalidInput):
+            model.system1_evaluate([1, 2, 3], [[4, 5], bad])
+    assert model.engine.cache.slots.held_count == 0
+    small = reflex_b200.Model(model.lm, max_tokens=128)  # two pages: two slots
+    with pytest.raises(OutOfMemory):
+        small.system1_evaluate([1, 2, 3], [[4], [5], [6]])
+    assert small.engine.cache.slots.held_count == 0
+    res = model.system1_evaluate([1, 2, 3], [[4, 5], [6]])
+    assert len(res.probabilities) == 2

@@ -144,19 +144,23 @@ def test_run_order_is_data_a_layer_twice_and_a_shared_cache(dtype):
     assert helpers.rel_err(got, ref) < (2e-5 if dtype == torch.float32 else 1.5e-2)
 
 
-def test_a_toy_mixer_with_state_of_its_own():
-    """An exponential moving average over a sequence's tokens: state [hidden]
-    per sequence, fixed size, zero at the start, updated token by token.  It is
-    registered from here; config, weights, cache, step and replay take it as
-    they take attention."""
+def _toy_ema_model(dtype):
+    """Two layers of a toy mixer (an exponential moving average over a
+    sequence's tokens: state [hidden] per sequence, fixed size, zero at the
+    start, updated token by token) with the library's SwiGLU and norms."""
     from reflex_b200.cache import StateSpec
     from reflex_b200.config.spec import FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec
-    from reflex_b200.engine import CausalLM, Engine, expected_tensors
+    from reflex_b200.engine import CausalLM, expected_tensors
     from reflex_b200.parts import TensorInfo, register_mixer
     from reflex_b200.weights import random_tensors
 
     @register_mixer("toy_ema")
     class ToyEma:
+        # decode steps index the state with the step's device-side slots and never
+        # wait for the host, so they may be captured into a CUDA graph
+        capturable = True
+        fail_after_update = False  # test switch: raise once the state has been changed
+
         def __init__(self, spec, dtype, device):
             self.spec, self.dtype, self.device = spec, dtype, device
             self.decay = dict(spec.params)["decay"]
@@ -172,13 +176,23 @@ def test_a_toy_mixer_with_state_of_its_own():
             self.mix = tensors["mix"].to(self.device, torch.float32)
 
         def forward(self, x, ctx):
-            out = torch.empty((x.shape[0], self.spec.hidden_size), dtype=torch.float32, device=x.device)
             b = ctx.batch
-            for i, slot in enumerate(b.slots):  # each sequence's rows, in order
-                state = ctx.state[slot]
-                for r in range(b.row0[i], b.row0[i + 1]):
-                    state.mul_(self.decay).add_(x[r].float(), alpha=1 - self.decay)
-                    out[r] = state
+            xf = x.float()
+            if b.is_decode:
+                # one row a sequence: the state rows by the device's slot list
+                slots = b.row_slot.long()
+                state = ctx.state.index_select(0, slots) * self.decay + xf * (1 - self.decay)
+                ctx.state.index_copy_(0, slots, state)
+                out = state
+            else:
+                out = torch.empty((x.shape[0], self.spec.hidden_size), dtype=torch.float32, device=x.device)
+                for i, slot in enumerate(b.slots):  # each sequence's rows, in order
+                    state = ctx.state[slot]
+                    for r in range(b.row0[i], b.row0[i + 1]):
+                        state.mul_(self.decay).add_(xf[r], alpha=1 - self.decay)
+                        out[r] = state
+            if ToyEma.fail_after_update:
+                raise RuntimeError("toy failure after the state was updated")
             return out @ self.mix.T
 
     H, V = 40, 97
@@ -189,12 +203,9 @@ def test_a_toy_mixer_with_state_of_its_own():
     spec = ModelSpec("toy", V, H, layers, NormSpec("rmsnorm", H, 1e-5), tie_word_embeddings=True, max_positions=256,
                      embedding_name="emb", final_norm_name="fn")
     assert "blocks.1.ema.mix.weight" in expected_tensors(spec)
-    model = CausalLM(spec, torch.float32, DEV)
-    tensors = dict(random_tensors(spec, 1, torch.float32))
+    model = CausalLM(spec, dtype, DEV)
+    tensors = {k: (v.to(dtype) if v.dim() > 1 else v) for k, v in random_tensors(spec, 1, torch.float32)}
     model.bind(tensors)
-    eng = Engine(model, max_tokens=256)
-    assert len(eng.cache.state_groups) == 1 and not eng.cache.kv_groups
-
     w = {k: v.double().numpy() for k, v in tensors.items()}
 
     def plain(tokens):
@@ -211,23 +222,101 @@ def test_a_toy_mixer_with_state_of_its_own():
             h = h + pm.swiglu(x, w[p + "ff.g"], w[p + "ff.u"], w[p + "ff.d"])
         return pm.rms_norm(h, w["fn"], 1e-5) @ w["emb"].T
 
+    return model, plain, ToyEma, V
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_a_toy_mixer_with_state_of_its_own(dtype):
+    """Registered from here; config, weights, cache, step and replay take it as
+    they take attention: in 32-bit, and in bfloat16 with the defaults, where its
+    decode steps are captured into CUDA graphs (it declares `capturable` and
+    reads its slots from the step's device-side indices)."""
+    import reflex_b200
+    from reflex_b200.engine import Engine
+
+    model, plain, _, V = _toy_ema_model(dtype)
+    eng = Engine(model, max_tokens=256)
+    assert len(eng.cache.state_groups) == 1 and not eng.cache.kv_groups
+    assert eng.use_graphs == (dtype == torch.bfloat16)
+    tol = 1e-5 if dtype == torch.float32 else 1.5e-2
     reqs = [helpers.random_tokens(n, V, n) for n in (9, 3, 14, 6)]
     got = helpers.run_batches(eng, reqs, 2, [4, 3, 1])  # unequal batches, slots (and state) used again
     for r, g in zip(reqs, got):
-        assert helpers.rel_err(g, plain(r)) < 1e-5
+        assert helpers.rel_err(g, plain(r)) < tol
     assert eng.cache.slots.held_count == 0
+    if dtype == torch.bfloat16:
+        assert eng._graphs and any(g.graph is not None for g in eng._graphs.values())
+    # through the entry point, defaults: greedy ids against the plain model's
+    api = reflex_b200.Model(model, max_tokens=512)
+    prompts = [helpers.random_tokens(n, V, 50 + n) for n in (5, 11, 2)]
+    outs = api.generate(prompts, 12)
+    for p, o in zip(prompts, outs):
+        seq = list(p)
+        for tok in o:
+            logits = plain(seq)[-1]
+            best = pm.argmax_last(logits)
+            assert tok == best or logits[best] - logits[tok] <= 2 * tol * np.abs(logits).max()
+            seq.append(tok)
 
 
-def test_a_toy_routed_feed_forward_and_a_toy_position_encoding():
-    """Two more parts registered from here and chosen layer by layer: a
-    feed-forward that routes each row to its best expert of three (router in
-    32-bit), and a rotary encoding whose positions are divided by a factor.
-    Layer 0 uses both with windowed attention, layer 1 the library's own parts:
-    one model, different mixers' options and feed-forwards in different layers."""
+def test_a_failed_step_leaves_fixed_size_state_as_it_was():
+    """A mixer that fails after it has updated its state: the step raises, and
+    the sequence's state and length are what they were, so the same step run
+    again gives what an undisturbed run gives."""
+    from reflex_b200.engine import Engine
+
+    model, plain, ToyEma, V = _toy_ema_model(torch.float32)
+    eng = Engine(model, max_tokens=256)
+    toks = helpers.random_tokens(12, V, 3)
+    s = eng.open()
+    eng.step([(s, toks[:7], [])])
+    before = eng.cache.state_groups[0].data.clone()
+    ToyEma.fail_after_update = True
+    try:
+        with pytest.raises(RuntimeError):
+            eng.step([(s, toks[7:], [0])])
+    finally:
+        ToyEma.fail_after_update = False
+    assert eng.length(s) == 7 and torch.equal(eng.cache.state_groups[0].data, before)
+    out = eng.step([(s, toks[7:], list(range(5)))]).cpu().numpy()
+    eng.close(s)
+    assert helpers.rel_err(out, plain(toks)[7:]) < 1e-5
+
+
+def rope_pairs(t, positions, theta, rotary_dim, factor, magnitude):
+    """A rotary encoding with consecutive pairs (2i, 2i + 1), positions divided by
+    `factor`, cos and sin times `magnitude` (src/model/config.rs:15-28 for the
+    pairing, src/model/kernels.rs:3086-3129 for a magnitude other than 1)."""
+    half = rotary_dim // 2
+    denom = np.power(float(theta), 2.0 * np.arange(half) / rotary_dim) * factor
+    ang = np.asarray(positions, dtype=np.float64)[:, None] / denom[None, :]
+    c, s_ = (np.cos(ang) * magnitude)[:, None, :], (np.sin(ang) * magnitude)[:, None, :]
+    out = t.copy()
+    a, b = t[..., 0:rotary_dim:2], t[..., 1:rotary_dim:2]
+    out[..., 0:rotary_dim:2] = a * c - b * s_
+    out[..., 1:rotary_dim:2] = a * s_ + b * c
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_toy_parts_chosen_layer_by_layer(dtype):
+    """Parts registered from here and chosen layer by layer, in 32-bit and in
+    bfloat16 through the entry point with its defaults: a feed-forward that
+    routes each row to its best expert of three (router in 32-bit; it waits for
+    the host, so it leaves `capturable` out and the engine captures nothing); a
+    rotary encoding with consecutive pairs, divided positions and a magnitude
+    other than 1; and a block arrangement with sandwich norms (a norm after the
+    mixer and after the feed-forward, before the residual add) that reads its
+    extra norms from the layer's record.  Layer 0 uses all three with windowed
+    attention, layer 1 the library's own parts: one model, different mixers'
+    options, feed-forwards and arrangements in different layers."""
+    import reflex_b200
+    from reflex_b200 import ops
     from reflex_b200.config.spec import (FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec,
-                                         PositionSpec)
+                                         PositionSpec, names_dict)
     from reflex_b200.engine import CausalLM, Engine
-    from reflex_b200.parts import TensorInfo, register_feed_forward, register_position
+    from reflex_b200.parts import (FEED_FORWARDS, MIXERS, NORMS, Rotation, TensorInfo, register_block,
+                                   register_feed_forward, register_position)
     from reflex_b200.weights import random_tensors
 
     @register_feed_forward("toy_routed")
@@ -258,16 +347,17 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding():
                     out[rows] = torch.relu(xf[rows] @ self.w_in[e].T) @ self.w_out[e].T
             return out
 
-    @register_position("toy_rope_divided")
-    class ToyDividedRope:
-        """NeoX pairs; angle = (position / factor) / theta^(2i/d)."""
+    @register_position("toy_rope_pairs")
+    class ToyPairsRope:
+        capturable = True
 
         def __init__(self, spec, dtype, device):
             self.spec = spec
-            factor = dict(spec.params)["factor"]
+            p = dict(spec.params)
             half = spec.rotary_dim // 2
             exps = torch.arange(half, dtype=torch.float64) * 2.0 / spec.rotary_dim
-            self.denominators = (torch.pow(torch.tensor(spec.theta, dtype=torch.float64), exps) * factor).float().to(device)
+            self.denominators = (torch.pow(torch.tensor(spec.theta, dtype=torch.float64), exps) * p["factor"]).float().to(device)
+            self.magnitude = p["magnitude"]
 
         @classmethod
         def tensor_specs(cls, spec):
@@ -277,12 +367,54 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding():
             pass
 
         def rotation(self):
-            from reflex_b200.parts import Rotation
+            return Rotation(self.denominators, self.spec.rotary_dim, "consecutive", self.magnitude)
 
-            return Rotation(self.denominators, self.spec.rotary_dim)
+    @register_block("toy_sandwich")
+    class ToySandwich:
+        """h += post_mixer_norm(mixer(norm1(h))); h += post_ffn_norm(ffn(norm2(h)))."""
+
+        def __init__(self, spec, dtype, device):
+            self.spec = spec
+            mk = lambda n: NORMS.get(n.kind)(n, dtype, device)
+            self.norm1, self.norm2 = mk(spec.mixer_norm), mk(spec.feed_forward_norm)
+            self.extra = {role: mk(n) for role, n in spec.extra_norms}
+            self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, dtype, device)
+            self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, dtype, device)
+
+        @property
+        def capturable(self):
+            return all(getattr(p, "capturable", False) for p in
+                       (self.norm1, self.norm2, self.mixer, self.feed_forward, *self.extra.values()))
+
+        @classmethod
+        def tensor_names(cls, spec):
+            out, bn = {}, names_dict(spec.names)
+            for part, n in (("mixer_norm", spec.mixer_norm), ("feed_forward_norm", spec.feed_forward_norm), *spec.extra_norms):
+                out[spec.prefix + bn[part]] = (part, "weight", NORMS.get(n.kind).tensor_specs(n)["weight"])
+            for part, sp, reg in (("mixer", spec.mixer, MIXERS), ("feed_forward", spec.feed_forward, FEED_FORWARDS)):
+                nd = names_dict(sp.names)
+                for role, info in reg.get(sp.kind).tensor_specs(sp).items():
+                    out[spec.prefix + nd.get(role, role)] = (part, role, info)
+            return out
+
+        def bind(self, by_part):
+            self.norm1.bind(by_part["mixer_norm"])
+            self.norm2.bind(by_part["feed_forward_norm"])
+            for role, n in self.extra.items():
+                n.bind(by_part[role])
+            self.mixer.bind(by_part["mixer"])
+            self.feed_forward.bind(by_part["feed_forward"])
+
+        def forward(self, hidden, pending, ctx):
+            x = self.norm1(hidden, delta=pending)  # adds what the block before left, then norms
+            a = self.mixer.forward(x, ctx)
+            ops.add_(hidden, self.extra["post_mixer_norm"](a.float()))
+            x = self.norm2(hidden)
+            f = self.feed_forward.forward(x)
+            return hidden, self.extra["post_ffn_norm"](f.float())
 
     H, V, nq, nkv, d, I, E = 48, 101, 3, 1, 32, 40, 3
-    theta, factor, window, eps = 1e4, 4.0, 9, 1e-5
+    theta, factor, magnitude, window, eps = 1e4, 4.0, 1.1, 9, 1e-5
     names = (("q_proj", "att.q"), ("k_proj", "att.k"), ("v_proj", "att.v"), ("o_proj", "att.o"),
              ("q_norm", "att.qn"), ("k_norm", "att.kn"))
 
@@ -296,46 +428,71 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding():
     dense = FeedForwardSpec("swiglu", H, 56, names=(("gate_proj", "ff.g"), ("up_proj", "ff.u"), ("down_proj", "ff.d")))
     norm = NormSpec("rmsnorm", H, eps)
     lnames = (("mixer_norm", "n1"), ("feed_forward_norm", "n2"))
-    layers = [LayerSpec("prenorm", "blocks.0.", mixer("toy_rope_divided", (("factor", factor),), window), routed, norm, norm, names=lnames),
+    layers = [LayerSpec("toy_sandwich", "blocks.0.", mixer("toy_rope_pairs", (("factor", factor), ("magnitude", magnitude)), window),
+                        routed, norm, norm, names=lnames + (("post_mixer_norm", "n3"), ("post_ffn_norm", "n4")),
+                        extra_norms=(("post_mixer_norm", norm), ("post_ffn_norm", norm))),
               LayerSpec("prenorm", "blocks.1.", mixer("rope_neox", (), None), dense, norm, norm, names=lnames)]
     spec = ModelSpec("toy2", V, H, layers, norm, tie_word_embeddings=False, max_positions=256,
                      embedding_name="emb", final_norm_name="fn", head_name="head")
-    model = CausalLM(spec, torch.float32, DEV)
+    model = CausalLM(spec, dtype, DEV)
     tensors = dict(random_tensors(spec, 3, torch.float32))
-    # spread the router so that choices are clear of ties
+    # spread the router so that choices are clear of ties, also after bfloat16's rounding
     tensors["blocks.0.moe.r"] = tensors["blocks.0.moe.r"] * 50
+    tensors = {k: (v.to(dtype) if v.dim() > 1 else v) for k, v in tensors.items()}
     model.bind(tensors)
+    assert not model.capturable
     eng = Engine(model, max_tokens=512)
+    assert not eng.use_graphs
     assert len(eng.cache.kv_groups) == 2  # a windowed group and a full one, storage of their own
 
     w = {k: v.double().numpy() for k, v in tensors.items()}
+    margins = []
 
-    def attention(h, p, positions, win):
+    def attention(h, p, rope, win):
         T = h.shape[0]
         x = pm.rms_norm(h, w[p + "n1"], eps)
         q = pm.rms_norm((x @ w[p + "att.q"].T).reshape(T, nq, d), w[p + "att.qn"], eps)
         k = pm.rms_norm((x @ w[p + "att.k"].T).reshape(T, nkv, d), w[p + "att.kn"], eps)
         v = (x @ w[p + "att.v"].T).reshape(T, nkv, d)
-        q, k = pm.rope_neox(q, positions, theta, d), pm.rope_neox(k, positions, theta, d)
-        return h + pm.causal_attention(q, k, v, d ** -0.5, win).reshape(T, nq * d) @ w[p + "att.o"].T
+        q, k = rope(q), rope(k)
+        return pm.causal_attention(q, k, v, d ** -0.5, win).reshape(T, nq * d) @ w[p + "att.o"].T
 
     def plain(tokens):
         T = len(tokens)
+        pos = np.arange(T)
         h = w["emb"][np.array(tokens)]
-        h = attention(h, "blocks.0.", np.arange(T) / factor, window)
+        a = attention(h, "blocks.0.", lambda t: rope_pairs(t, pos, theta, d, factor, magnitude), window)
+        h = h + pm.rms_norm(a, w["blocks.0.n3"], eps)
         x = pm.rms_norm(h, w["blocks.0.n2"], eps)
-        pick = (x @ w["blocks.0.moe.r"].T).argmax(axis=1)
+        r = x @ w["blocks.0.moe.r"].T
+        top = np.sort(r, axis=1)
+        margins.append(float((top[:, -1] - top[:, -2]).min()))
+        pick = r.argmax(axis=1)
         w_in, w_out = w["blocks.0.moe.i"].reshape(E, I, H), w["blocks.0.moe.o"].reshape(E, H, I)
-        h = h + np.stack([np.maximum(x[t] @ w_in[pick[t]].T, 0) @ w_out[pick[t]].T for t in range(T)])
-        h = attention(h, "blocks.1.", np.arange(T), None)
+        f = np.stack([np.maximum(x[t] @ w_in[pick[t]].T, 0) @ w_out[pick[t]].T for t in range(T)])
+        h = h + pm.rms_norm(f, w["blocks.0.n4"], eps)
+        h = h + attention(h, "blocks.1.", lambda t: pm.rope_neox(t, pos, theta, d), None)
         x = pm.rms_norm(h, w["blocks.1.n2"], eps)
         h = h + pm.swiglu(x, w["blocks.1.ff.g"], w["blocks.1.ff.u"], w["blocks.1.ff.d"])
         return pm.rms_norm(h, w["fn"], eps) @ w["head"].T
 
+    tol = 2e-5 if dtype == torch.float32 else 1.5e-2
     reqs = [helpers.random_tokens(n, V, n) for n in (23, 5, 40, 12)]
+    refs = [plain(r) for r in reqs]
+    assert min(margins) > 0.05, "a router choice is too close to a tie for bfloat16 to keep"
     got = helpers.run_batches(eng, reqs, 2, [6, 3, 1])
-    for r, g in zip(reqs, got):
-        assert helpers.rel_err(g, plain(r)) < 2e-5
+    for ref, g in zip(refs, got):
+        assert helpers.rel_err(g, ref) < tol
     whole = helpers.run_whole(eng, reqs[2])
-    assert helpers.rel_err(whole, plain(reqs[2])) < 2e-5
+    assert helpers.rel_err(whole, refs[2]) < tol
     assert eng.cache.slots.held_count == 0
+    # through the entry point with its defaults
+    api = reflex_b200.Model(model, max_tokens=1024)
+    outs = api.generate([reqs[1], reqs[3]], 6)
+    for p, o in zip((reqs[1], reqs[3]), outs):
+        seq = list(p)
+        for tok in o:
+            logits = plain(seq)[-1]
+            best = pm.argmax_last(logits)
+            assert tok == best or logits[best] - logits[tok] <= 2 * tol * np.abs(logits).max()
+            seq.append(tok)

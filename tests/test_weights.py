@@ -155,3 +155,24 @@ def test_sharded_folder(tmp_path):
     check_names_and_shapes(spec, ck)
     assert len(read_tensors(spec, ck)) == len(names)
     ck.close()
+
+
+def test_generation_config_adds_end_of_sequence_ids(tmp_path):
+    """`generation_config.json`, when the folder has one, adds its
+    end-of-sequence ids to config.json's; a malformed one is refused by name."""
+    import json
+
+    from reflex_b200 import InvalidInput
+    from reflex_b200.weights.loader import load_spec
+    from tiny_configs import TINY_A
+
+    with open(tmp_path / "config.json", "w") as f:
+        json.dump(dict(TINY_A, eos_token_id=7), f)
+    assert load_spec(str(tmp_path))[1].eos_token_ids == (7,)
+    with open(tmp_path / "generation_config.json", "w") as f:
+        json.dump({"eos_token_id": [7, 9, 11], "temperature": 0.6}, f)
+    assert load_spec(str(tmp_path))[1].eos_token_ids == (7, 9, 11)
+    with open(tmp_path / "generation_config.json", "w") as f:
+        json.dump({"eos_token_id": "seven"}, f)
+    with pytest.raises(InvalidInput, match="generation_config.json"):
+        load_spec(str(tmp_path))

@@ -167,3 +167,78 @@ def test_mirror_agrees_with_the_plain_model_and_sees_a_changed_order():
     ref = pm.rope_neox(pm.rms_norm(q.astype(np.float64), wn.astype(np.float64), 1e-6), pos, 1e4, 32)
     np.testing.assert_allclose(got, ref, rtol=0, atol=5e-3)  # the 32-bit angle is off by up to pos * 2^-24
     np.testing.assert_allclose(got[:3], ref[:3], rtol=0, atol=2e-6)  # positions 0, 1, 5
+
+
+# ------------------------------------ the reference's own kernels, run once on a GPU
+KERNEL_GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "kernel_golden.npz")
+
+
+@pytest.mark.skipif(not os.path.exists(KERNEL_GOLDEN), reason="golden file absent")
+def test_plain_parts_match_the_reference_kernels_outputs():
+    """Outputs of the reference's attention_kernel, attention_prefill_kernel,
+    attention_online_kernel (+ combine), gemv_kernel, rmsnorm_kernel,
+    add_rmsnorm_kernel, rmsnorm_pair_kernel and rope_batch_kernel, compiled
+    unchanged from its checkout and run once on a GPU by
+    tests/golden/make_kernel_golden.py, against this folder's plain functions on
+    the same inputs (rebuilt from the seeds): the scale, the causal and window
+    bounds, the head map h // group, the softmax, x W^T, the norm with and
+    without the add before it, the rotation.  The bound for attention is the
+    reference's own between its kernels (1e-5,
+    src/model/attention_online_tests.rs:14); the 32-bit mirror is held to the
+    same numbers."""
+    sys_path_golden = os.path.join(os.path.dirname(__file__), "golden")
+    import sys
+
+    sys.path.insert(0, sys_path_golden)
+    try:
+        import make_kernel_golden as mk
+    finally:
+        sys.path.remove(sys_path_golden)
+    import fp32_mirror as mir
+
+    g = np.load(KERNEL_GOLDEN)
+    D = np.float64
+    for case, (heads, rows, start, window) in mk.PREFILL_CASES.items():
+        nq, nkv, d = mk.HEADS[heads]
+        x = mk.golden_inputs(case)
+        scale = float(np.float32(1.0) / np.sqrt(np.float32(d)))
+        keep_r, keep_h = mk.kept_rows(rows, heads), mk.kept_heads(heads)
+        T = start + rows
+        qfull = np.zeros((T, nq, d), dtype=D)
+        qfull[start:] = x["q"]
+        ref = pm.causal_attention(qfull, x["k"].astype(D), x["v"].astype(D), scale, window or None,
+                                  first_row=start)[start:]
+        want = ref[keep_r][:, keep_h]
+        for kind in ("prefill", "online1", f"online{mk.ONLINE_SPLITS.get(case, 1)}"):
+            np.testing.assert_allclose(g[f"{kind}/{case}"], want, rtol=0, atol=1e-5, err_msg=f"{kind}/{case}")
+        if f"decode/{case}" in g.files:
+            np.testing.assert_allclose(g[f"decode/{case}"], ref[rows - 1][keep_h], rtol=0, atol=1e-5)
+        # the mirror of the 32-bit kernel, on the same case
+        qm = np.zeros((T, nq, d), dtype=np.float32)
+        qm[start:] = x["q"]
+        got = mir.attention(qm, x["k"], x["v"], scale, window or None)[start:][keep_r][:, keep_h]
+        np.testing.assert_allclose(got, g[f"prefill/{case}"], rtol=0, atol=1e-5)
+
+    x = mk.golden_inputs("gemv")
+    np.testing.assert_allclose(x["x"].astype(D) @ x["w"].astype(D).T, g["gemv"], rtol=0, atol=2e-6)
+    np.testing.assert_allclose(mir.linear(x["x"], x["w"]), g["gemv"], rtol=0, atol=2e-6)
+
+    x = mk.golden_inputs("rmsnorm")
+    np.testing.assert_allclose(pm.rms_norm(x["x"].astype(D), x["w"].astype(D), 1e-6), g["rmsnorm"], rtol=3e-6, atol=1e-7)
+    s = x["x"][1].astype(D) + x["b"][1].astype(D)  # add, then norm (src/kernels_cuda/decode_ops.cu:10-35)
+    np.testing.assert_allclose(s, g["add_rmsnorm/sum"], rtol=2e-7, atol=1e-7)
+    np.testing.assert_allclose(pm.rms_norm(s, x["w"].astype(D), 1e-6), g["add_rmsnorm/out"], rtol=3e-6, atol=1e-7)
+    out, t = mir.rms_norm(x["x"][1:2], x["w"], 1e-6, delta=x["b"][1:2])
+    assert np.array_equal(t[0], g["add_rmsnorm/sum"])
+    np.testing.assert_allclose(out[0], g["add_rmsnorm/out"], rtol=3e-6, atol=1e-7)
+
+    x = mk.golden_inputs("pair")  # the per-head q and k norms: one weight vector for all heads
+    np.testing.assert_allclose(pm.rms_norm(x["x1"].astype(D), x["w1"].astype(D), 1e-5), g["pair/o1"], rtol=3e-6, atol=1e-7)
+    np.testing.assert_allclose(pm.rms_norm(x["x2"].astype(D), x["w2"].astype(D), 1e-5), g["pair/o2"], rtol=3e-6, atol=1e-7)
+
+    t = mk.golden_inputs("rope")["t"]
+    pos = np.arange(100, 117)
+    # the reference's angle is 32-bit (position / powf(base, e)): off from double by up to position * 2^-24
+    np.testing.assert_allclose(pm.rope_neox(t.astype(D), pos, 1e6, 32), g["rope"], rtol=0, atol=5e-5)
+    got = mir.head_norm_rope(t, None, 0.0, mir.rope_denominators(1e6, 32), 32, pos)
+    np.testing.assert_allclose(got, g["rope"], rtol=0, atol=5e-5)

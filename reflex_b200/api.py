@@ -198,10 +198,9 @@ class Model:
             entries = []
             for s, c in zip(seqs, candidates):
                 toks = list(prompt) + list(c[:-1])
-                entries.append((s, toks, list(range(P - 1, P - 1 + len(c)))))
-            logits = eng.step(entries)
-            idx = torch.tensor([t for c in candidates for t in c], dtype=torch.int64, device=logits.device)
-            picked = logits.gather(1, idx[:, None])[:, 0].tolist()
+                entries.append((s, toks, list(range(P - 1, P - 1 + len(c))), list(c)))
+            # the head's rows of the candidates' tokens only, not the whole vocabulary
+            picked = eng.step_scores(entries).tolist()
             eng.check_errors()
         finally:
             for s in seqs:

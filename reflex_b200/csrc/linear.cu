@@ -114,7 +114,111 @@ gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
     }
 }
 
+// y[j] = x[j, :] . W[ids[j], :]: the head's rows of a handful of token ids only,
+// for scoring given continuations (the reference's gathered product,
+// src/kernels_cuda/gemv_gather.cu:10-51): kilobytes of the head are read, not
+// the whole vocabulary.  One warp per pair.  32-bit: the lanes stage the two
+// rows in shared memory, a chunk at a time, and lane 0 runs one fused
+// multiply-add chain over k in index order, which gives the bits of
+// `gemm_f32_kernel` for the same row and column.  An id outside [0, V) gives
+// NaN and sets the error word (the host checks ids before it launches).
+constexpr int GATHER_WARPS = 4, GATHER_CHUNK = 512;
+
+__global__ void __launch_bounds__(GATHER_WARPS * 32)
+gather_dot_f32_kernel(const float* __restrict__ x, const float* __restrict__ W, const int* __restrict__ ids,
+                      float* __restrict__ y, int P, int K, int V, int* __restrict__ err) {
+    __shared__ float xs[GATHER_WARPS][GATHER_CHUNK];
+    __shared__ float ws[GATHER_WARPS][GATHER_CHUNK];
+    pdl_prologue();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int j = blockIdx.x * GATHER_WARPS + warp;
+    if (j >= P) return;
+    const int id = ids[j];
+    if (id < 0 || id >= V) {
+        if (lane == 0) {
+            y[j] = __int_as_float(0x7fc00000);
+            atomicExch(err, 1 + j);
+        }
+        return;
+    }
+    const float* xr = x + (size_t)j * K;
+    const float* wr = W + (size_t)id * K;
+    float acc = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += GATHER_CHUNK) {
+        const int n = min(GATHER_CHUNK, K - k0);
+        for (int i = lane; i < n; i += 32) {
+            xs[warp][i] = xr[k0 + i];
+            ws[warp][i] = wr[k0 + i];
+        }
+        __syncwarp();
+        if (lane == 0)
+            for (int i = 0; i < n; ++i) acc = fmaf(xs[warp][i], ws[warp][i], acc);
+        __syncwarp();
+    }
+    if (lane == 0) y[j] = acc;
+}
+
+// bfloat16 rows, 32-bit accumulation: 16-byte loads when K is a multiple of 8.
+__global__ void __launch_bounds__(GATHER_WARPS * 32)
+gather_dot_bf16_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W,
+                       const int* __restrict__ ids, float* __restrict__ y, int P, int K, int V,
+                       int* __restrict__ err) {
+    pdl_prologue();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int j = blockIdx.x * GATHER_WARPS + warp;
+    if (j >= P) return;
+    const int id = ids[j];
+    if (id < 0 || id >= V) {
+        if (lane == 0) {
+            y[j] = __int_as_float(0x7fc00000);
+            atomicExch(err, 1 + j);
+        }
+        return;
+    }
+    const __nv_bfloat16* xr = x + (size_t)j * K;
+    const __nv_bfloat16* wr = W + (size_t)id * K;
+    float acc = 0.0f;
+    if ((K & 7) == 0) {
+        const uint4* x4 = reinterpret_cast<const uint4*>(xr);
+        const uint4* w4 = reinterpret_cast<const uint4*>(wr);
+        for (int c = lane; c < K / 8; c += 32) {
+            const uint4 xv = x4[c], wv = w4[c];
+            const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+            const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 a = __bfloat1622float2(x2[i]), b = __bfloat1622float2(w2[i]);
+                acc = fmaf(a.x, b.x, acc);
+                acc = fmaf(a.y, b.y, acc);
+            }
+        }
+    } else {
+        for (int i = lane; i < K; i += 32) acc = fmaf(__bfloat162float(xr[i]), __bfloat162float(wr[i]), acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) y[j] = acc;
+}
+
 }  // namespace
+
+extern "C" int rfx_gather_dot(const void* x, const void* W, int dt, const int* ids, float* y, int P, int K,
+                              int V, int* err, void* stream) {
+    if (P <= 0) return 0;
+    if (K <= 0 || V <= 0) return RFX_ERR_BAD_ARG;
+    const int blocks = (P + GATHER_WARPS - 1) / GATHER_WARPS;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dt == RFX_DT_F32)
+        RFX_LAUNCH(gather_dot_f32_kernel, blocks, GATHER_WARPS * 32, 0, s, (const float*)x, (const float*)W, ids,
+                   y, P, K, V, err);
+    else if (dt == RFX_DT_BF16) {
+        if ((K & 7) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(W)) & 15))
+            return RFX_ERR_BAD_ARG;
+        RFX_LAUNCH(gather_dot_bf16_kernel, blocks, GATHER_WARPS * 32, 0, s, (const __nv_bfloat16*)x,
+                   (const __nv_bfloat16*)W, ids, y, P, K, V, err);
+    } else
+        return RFX_ERR_BAD_ARG;
+    return 0;
+}
 
 extern "C" int rfx_gemm_f32(const float* x, const float* W, float* y, int R, int N, int K,
                             void* stream) {

@@ -139,6 +139,23 @@ class CausalLM:
         ops.prof_mark("head")
         return out
 
+    def normed_rows(self, hidden: torch.Tensor, pending, rows: torch.Tensor) -> torch.Tensor:
+        """The final norm on the wanted rows, in the model's dtype."""
+        if isinstance(pending, ops.NormedInput):
+            return self.final_norm(hidden, rows=rows)  # hidden already holds the last delta
+        return self.final_norm(hidden, delta=pending, rows=rows)
+
+    def scores(self, batch, cache, ids: torch.Tensor) -> torch.Tensor:
+        """For each wanted row the head's logit of one given token id
+        (`ids`, int32 on the device, one per wanted row), float32 [wanted]: only
+        those rows of the head are read (src/model/dense.rs:2073-2133)."""
+        h, pending = self.hidden_states(batch, cache)
+        out = ops.gather_dot(self.normed_rows(h, pending, batch.want_rows), self.head, ids)
+        if self.spec.logit_scale != 1.0:
+            out = out * self.spec.logit_scale
+        ops.prof_mark("head")
+        return out
+
     def forward(self, batch, cache) -> torch.Tensor:
         h, pending = self.hidden_states(batch, cache)
         return self.logits(h, pending, batch.want_rows, batch.want_rows_host)

@@ -102,6 +102,11 @@ class Engine:
                         f"sequence {seq}: wanted place {w} is outside this step's {len(tokens)} tokens")
 
     def step(self, entries: Sequence[StepEntry], borrow: bool = False) -> torch.Tensor:
+        return self._run(entries, None, borrow)
+
+    def _run(self, entries: Sequence[StepEntry], head=None, borrow: bool = False) -> torch.Tensor:
+        """Checks, reserves cache, runs, commits.  `head(batch)`, when given, takes
+        the place of the full-vocabulary logits."""
         self._check(entries)
         cache = self.cache
         slots = [int(e[0]) for e in entries]
@@ -115,11 +120,14 @@ class Engine:
         try:
             n_want = sum(len(w) for w in want)
             # the captured step has one token and one wanted row, that token's, per sequence
-            if self.use_graphs and all(len(t) == 1 for t in tokens) and all(w == [0] for w in want):
+            if (head is None and self.use_graphs and all(len(t) == 1 for t in tokens)
+                    and all(w == [0] for w in want)):
                 logits = self._decode_graphed(tokens, slots, starts, want, borrow=borrow)
             else:
                 batch = make_batch(tokens, slots, starts, want, self.device, staging=self.staging)
-                if n_want:
+                if head is not None:
+                    logits = head(batch)
+                elif n_want:
                     logits = self.model.forward(batch, cache)
                 else:
                     self.model.hidden_states(batch, cache)
@@ -138,6 +146,30 @@ class Engine:
 
             ops.prof_report(f"{self.steps_run - 1}:rows={sum(len(t) for t in tokens)}")
         return logits
+
+    def step_scores(self, entries: Sequence[Tuple[int, Sequence[int], Sequence[int], Sequence[int]]]) -> torch.Tensor:
+        """A step that returns, instead of whole rows of logits, the logit of one
+        given token id at each wanted place: entries are (sequence, tokens,
+        wanted places, ids), one id per place; float32 [wanted] comes back.
+        The head's rows of those ids alone are read.  The ids need not be among
+        the step's tokens (a continuation's last token is only ever scored), so
+        they are checked here."""
+        V = self.vocab_size
+        for seq, _t, want, ids in entries:
+            if len(ids) != len(want):
+                raise InvalidInput(f"sequence {seq}: one token id per wanted place is needed")
+            for t in ids:
+                if not (0 <= int(t) < V):
+                    raise InvalidInput(f"sequence {seq}: token id {t} is outside the vocabulary [0, {V})")
+        flat = [int(t) for e in entries for t in e[3]]
+        if not flat:
+            raise InvalidInput("step_scores needs at least one wanted place")
+
+        def head(batch):
+            ids = torch.tensor(flat, dtype=torch.int32).to(self.device, non_blocking=True)
+            return self.model.scores(batch, self.cache, ids)
+
+        return self._run([(e[0], e[1], e[2]) for e in entries], head)
 
     def step_decode(self, seqs: Sequence[int], tokens_dev: torch.Tensor, borrow: bool = False) -> torch.Tensor:
         """One decode step whose tokens are already on the device: sequence

@@ -275,6 +275,26 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     return torch.mm(x, weight.t())
 
 
+def gather_dot(x: torch.Tensor, weight: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """y[j] = x[j] . weight[ids[j]], float32 [P]: row j of `x` against one row of
+    the matrix, chosen by id.  Scoring given continuations needs the head's rows
+    of a handful of ids, not the whole vocabulary
+    (src/kernels_cuda/gemv_gather.cu:10-51).  In 32-bit the bits are those of
+    `linear(x, weight)[j, ids[j]]`."""
+    P, K = x.shape
+    V, K2 = weight.shape
+    if K != K2 or ids.numel() != P:
+        raise InvalidInput("gather_dot: x [P, K], weight [V, K] and P ids are needed")
+    if x.dtype != weight.dtype:
+        raise InvalidInput(f"gather_dot: x is {x.dtype}, weight is {weight.dtype}")
+    y = torch.empty((P,), dtype=torch.float32, device=x.device)
+    st = native.lib().rfx_gather_dot(_chk(x, "x"), _chk(weight, "weight"), dt_code(x.dtype),
+                                     _chk(ids, "ids", torch.int32), y.data_ptr(), P, K, V,
+                                     device_error_word(x.device).data_ptr(), _stream())
+    native.check(st, f"gather_dot (P={P}, K={K})")
+    return y
+
+
 def gemm_tc_residual(x: torch.Tensor, weight: torch.Tensor, hidden: torch.Tensor,
                      norm_weight: torch.Tensor, norm_offset: float, eps: float, ksplit: int = 0) -> NormedInput:
     """hidden += x @ weight.T in place (float32), and the rows of the new hidden

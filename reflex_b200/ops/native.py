@@ -26,6 +26,7 @@ _SIGNATURES = {
                     c_void_p, c_int, c_int, c_void_p],
     "rfx_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "rfx_add": [c_void_p, c_void_p, c_int, c_longlong, c_void_p],
+    "rfx_gather_dot": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "rfx_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "rfx_gemm_bf16_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                          c_int, c_int, c_float, c_void_p, c_void_p],

@@ -40,6 +40,7 @@ F32_TOL = 3e-6
 F32_SHARP_TOL = 1e-3
 BF16_TOL = 1.5e-2
 BF16_SHARP_TOL = 4e-2
+FULL_DEPTH_BF16_TOL = 3e-2  # 36 layers at the benchmark model's widths
 
 
 def tol(dtype, sharp=False):
@@ -446,3 +447,90 @@ def test_a_token_id_fed_from_the_device_outside_the_vocabulary_is_reported():
     out = eng.step([(s, [4], [0])])
     assert bool(torch.isfinite(out).all())
     eng.close(s)
+
+
+def test_the_benchmark_model_at_full_depth_and_vocabulary():
+    """All 36 layers at the benchmark model's sizes with the 151,936-row head, in
+    bfloat16, random weights drawn on the device: two short prompts in one
+    prefill step, then three decode steps (captured), logits at every fed
+    position against the plain implementation, which rebuilds the same weights
+    tensor by tensor from (seed, name) and streams one layer at a time.  What
+    `bench.py` times is this model; here its output is checked."""
+    import gc
+
+    import plain_model
+    from reflex_b200.engine import Engine
+    from reflex_b200.weights import random_model_on_device
+    from reflex_b200.weights.random_init import draw
+
+    cfg = {
+        "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 36,
+        "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+        "intermediate_size": 12288, "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+        "tie_word_embeddings": False, "max_position_embeddings": 40960,
+    }
+    seed = 0
+    lm = random_model_on_device(cfg, seed, torch.bfloat16, "cuda:0")
+    eng = Engine(lm, max_tokens=1024)
+    V = cfg["vocab_size"]
+    seqs_tok = [helpers.random_tokens(5, V, 1), helpers.random_tokens(9, V, 2)]
+    n_prompt = [len(t) for t in seqs_tok]
+    ids = [eng.open(), eng.open()]
+    out = eng.step([(s, t, [len(t) - 1]) for s, t in zip(ids, seqs_tok)])
+    got = [[out[i].float().cpu().numpy()] for i in range(2)]
+    for _ in range(3):
+        nxt = [int(g[-1].argmax()) for g in got]
+        for t, n in zip(seqs_tok, nxt):
+            t.append(n)
+        out = eng.step([(s, [n], [0]) for s, n in zip(ids, nxt)])
+        for i in range(2):
+            got[i].append(out[i].float().cpu().numpy())
+    eng.check_errors()
+    assert eng._graphs, "the decode steps were to run as captured graphs"
+    for s in ids:
+        eng.close(s)
+    del eng, lm, out
+    gc.collect()
+    torch.cuda.empty_cache()
+
+    def tensor(name, shape, role="matrix"):
+        # the same (seed, name) draw, made on the device for speed and copied: the host
+        # draw gives the same bits (tests/test_upload_gpu.py holds them together)
+        dt = torch.float32 if role == "norm" else torch.bfloat16
+        return draw(name, shape, role, seed, "cuda:0", dt).float().cpu().numpy()
+
+    H, I, nq, nkv, d = 4096, 12288, 32, 8, 128
+    emb = tensor("model.embed_tokens.weight", (V, H), "table")
+    hs = [emb[np.array(t)] for t in seqs_tok]  # float32 throughout: the weights stay as they are drawn
+    del emb
+    for li in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{li}."
+        w = {p + "input_layernorm.weight": tensor(p + "input_layernorm.weight", (H,), "norm"),
+             p + "post_attention_layernorm.weight": tensor(p + "post_attention_layernorm.weight", (H,), "norm"),
+             p + "self_attn.q_norm.weight": tensor(p + "self_attn.q_norm.weight", (d,), "norm"),
+             p + "self_attn.k_norm.weight": tensor(p + "self_attn.k_norm.weight", (d,), "norm"),
+             p + "self_attn.q_proj.weight": tensor(p + "self_attn.q_proj.weight", (nq * d, H)),
+             p + "self_attn.k_proj.weight": tensor(p + "self_attn.k_proj.weight", (nkv * d, H)),
+             p + "self_attn.v_proj.weight": tensor(p + "self_attn.v_proj.weight", (nkv * d, H)),
+             p + "self_attn.o_proj.weight": tensor(p + "self_attn.o_proj.weight", (H, nq * d)),
+             p + "mlp.gate_proj.weight": tensor(p + "mlp.gate_proj.weight", (I, H)),
+             p + "mlp.up_proj.weight": tensor(p + "mlp.up_proj.weight", (I, H)),
+             p + "mlp.down_proj.weight": tensor(p + "mlp.down_proj.weight", (H, I))}
+        hs = [plain_model.decoder_layer(h, w, p, cfg, np.arange(h.shape[0]), None) for h in hs]
+    fn = tensor("model.norm.weight", (H,), "norm")
+    head = tensor("lm_head.weight", (V, H))
+    worst = 0.0
+    for i in range(2):
+        x = plain_model.rms_norm(hs[i][n_prompt[i] - 1:], fn, cfg["rms_norm_eps"])
+        ref = (x.astype(np.float32) @ head.T).astype(np.float64)
+        g = np.stack(got[i])
+        assert g.shape == ref.shape and np.isfinite(g).all()
+        err = helpers.rel_err(g, ref)
+        worst = max(worst, err)
+        # the greedy choice agrees wherever the plain model's margin is clear of the error
+        for r in range(ref.shape[0]):
+            top = np.sort(ref[r])[-2:]
+            if top[1] - top[0] > 4 * err * np.abs(ref).max():
+                assert int(g[r].argmax()) == int(ref[r].argmax())
+    print(f"full-depth bfloat16 error {worst:.3e}")
+    assert worst < FULL_DEPTH_BF16_TOL, worst

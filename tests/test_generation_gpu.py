@@ -134,6 +134,26 @@ def test_system1_scores_candidates_in_one_step():
     assert abs(resp.entropy + float((e / e.sum() * np.log2(e / e.sum())).sum())) < 1e-3
 
 
+@pytest.mark.parametrize("weights,tol", [("f32", 0.0), ("bf16", 1e-4)])
+def test_system1_reads_only_the_candidates_rows_of_the_head(weights, tol):
+    """The scores come from a product over the candidates' rows of the head
+    alone; they equal what the full-vocabulary logits hold at the same places
+    (bit for bit in 32-bit, within 1e-4 in bfloat16,
+    src/model/system1_tests.rs:14-65)."""
+    import reflex_b200
+
+    folder = helpers.model_folder("B", 7, "float32" if weights == "f32" else "bfloat16")
+    model = reflex_b200.Model.load(folder, weights=weights, max_tokens=2048)
+    prompt = helpers.random_tokens(70, 1000, 4)
+    cands = [[5], [77, 3, 910], [400, 401], [999, 0]]
+    resp = model.system1_evaluate(prompt, cands)
+    P = len(prompt)
+    for c, r in zip(cands, resp.results):
+        logits = model.forward_prompt(prompt + c[:-1]).cpu().numpy()
+        full = sum(float(logits[P - 1 + i, t]) for i, t in enumerate(c))  # summed as the entry point sums
+        assert abs(r.score - full) <= tol * max(1.0, abs(full)), (c, r.score, full)
+
+
 def test_command_line_generate_and_system1():
     folder = helpers.model_folder("A", 7, "float32")
     exe = [sys.executable, os.path.join(ROOT, "bin", "reflex")]

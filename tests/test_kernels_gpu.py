@@ -633,3 +633,31 @@ def test_f32_attention_equals_the_host_mirror(nq, nkv, d, T, window):
                                 i32(list(range(T))), i32([slots[0]] * T), nq, nkv, d, window, scale)
     ref = mir.attention(q.numpy(), ks[0].numpy(), vs[0].numpy(), scale, window)
     assert _bits_equal(out.reshape(T, nq, d), ref)
+
+
+@pytest.mark.parametrize("P,K,V", [(1, 64, 50), (7, 100, 333), (5, 4096, 151936), (40, 1030, 1000)])
+def test_gather_dot_reads_the_chosen_rows(P, K, V):
+    """The gathered product against the full product at the chosen columns:
+    the same bits in 32-bit, 32-bit accumulation of the same products in
+    bfloat16; a row id outside the matrix is reported, not read."""
+    g = torch.Generator().manual_seed(P + K)
+    W = (torch.randn(V, K, generator=g) * 0.05)
+    x = torch.randn(P, K, generator=g)
+    ids = torch.randint(0, V, (P,), generator=g).int()
+    ids[0] = V - 1
+    got = ops().gather_dot(x.to(DEV), W.to(DEV), ids.to(DEV)).cpu()
+    full = ops().linear(x.to(DEV), W[ids.long()].to(DEV)).cpu()  # [P, P]: the chosen rows only
+    assert torch.equal(got, full.diagonal())
+    xb, Wb = x.bfloat16(), W.bfloat16()
+    got = ops().gather_dot(xb.to(DEV), Wb.to(DEV), ids.to(DEV)).cpu()
+    ref = (xb.double() * Wb[ids.long()].double()).sum(dim=1)
+    assert relerr(got, ref.numpy()) < 2e-6
+    ops().check_device_errors(DEV)
+    bad = ids.clone()
+    bad[P - 1] = V
+    out = ops().gather_dot(x.to(DEV), W.to(DEV), bad.to(DEV)).cpu()
+    assert bool(torch.isnan(out[P - 1]))
+    from reflex_b200 import CudaError
+
+    with pytest.raises(CudaError):
+        ops().check_device_errors(DEV)

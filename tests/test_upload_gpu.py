@@ -1,6 +1,7 @@
 """The pinned-staging upload: every byte arrives, whatever the sizes of the
 tensors against the staging buffers."""
 
+import numpy as np
 import pytest
 import torch
 
@@ -45,3 +46,20 @@ def test_upload_refuses_bad_settings():
         Uploader("cpu")
     with pytest.raises(ValueError):
         Uploader(DEV, buffers=1)
+
+
+@pytest.mark.parametrize("shape,role", [((1000, 96), "matrix"), ((4097,), "norm"), ((3, 5, 7), "matrix"),
+                                        ((151936, 128), "table")])
+def test_random_weights_are_the_same_on_the_host_and_on_the_device(shape, role):
+    """The counter-based draw gives the same bits from the CUDA kernel and from
+    the NumPy restatement, in both element types, so a model drawn on the GPU
+    (the benchmark's) can be rebuilt tensor by tensor on the CPU."""
+    from reflex_b200.weights.random_init import draw, draw_host, tensor_key
+
+    name = f"model.layers.3.x.{role}"
+    for dtype in (torch.float32, torch.bfloat16):
+        dev = draw(name, shape, role, 11, "cuda:0", dtype)
+        kind, a, b = ("uniform", 0.9, 1.1) if role == "norm" else ("normal", 0.0, 0.02)
+        n = int(np.prod(shape))
+        host = torch.from_numpy(draw_host(tensor_key(11, name), n, kind, a, b)).reshape(shape).to(dtype)
+        assert torch.equal(dev.cpu(), host)

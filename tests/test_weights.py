@@ -176,3 +176,26 @@ def test_generation_config_adds_end_of_sequence_ids(tmp_path):
         json.dump({"eos_token_id": "seven"}, f)
     with pytest.raises(InvalidInput, match="generation_config.json"):
         load_spec(str(tmp_path))
+
+
+def test_random_draw_is_a_function_of_seed_name_and_index():
+    """N(0, 0.02) for matrices, 1 + U(-0.1, 0.1) for norms; the same values in one
+    piece or in parts; other seeds and names give other values; bfloat16 is the
+    32-bit draw rounded to nearest even."""
+    from reflex_b200.weights.random_init import draw, draw_host, tensor_key
+
+    x = draw("model.layers.0.mlp.up_proj.weight", (300, 1000), "matrix", 7).numpy()
+    assert abs(float(x.mean())) < 2e-4 and abs(float(x.std()) - 0.02) < 2e-4
+    assert 0.05 < float(np.abs(x).max()) < 0.12  # twelve uniforms: tails to six deviations at most
+    frac = float((np.abs(x) < 0.02).mean())
+    assert abs(frac - 0.6827) < 0.01
+    w = draw("model.norm.weight", (5000,), "norm", 7).numpy()
+    assert 0.9 < float(w.min()) < 0.905 and 1.095 < float(w.max()) < 1.1 and abs(float(w.mean()) - 1.0) < 3e-3
+    key = tensor_key(7, "t")
+    whole = draw_host(key, 1001, "normal", 0.0, 0.02)
+    parts = np.concatenate([draw_host(key, 333, "normal", 0.0, 0.02), draw_host(key, 668, "normal", 0.0, 0.02, 333)])
+    assert np.array_equal(whole, parts)
+    assert not np.array_equal(whole, draw_host(tensor_key(8, "t"), 1001, "normal", 0.0, 0.02))
+    assert not np.array_equal(whole, draw_host(tensor_key(7, "u"), 1001, "normal", 0.0, 0.02))
+    b = draw("model.layers.0.mlp.up_proj.weight", (300, 1000), "matrix", 7, dtype=torch.bfloat16)
+    assert torch.equal(b, torch.from_numpy(x).to(torch.bfloat16))

@@ -40,7 +40,7 @@ F32_TOL = 3e-6
 F32_SHARP_TOL = 1e-3
 BF16_TOL = 1.5e-2
 BF16_SHARP_TOL = 4e-2
-FULL_DEPTH_BF16_TOL = 3e-2  # 36 layers at the benchmark model's widths
+FULL_DEPTH_BF16_TOL = 4e-2  # 36 layers at the benchmark model's widths (measured: 2.5e-2)
 
 
 def tol(dtype, sharp=False):

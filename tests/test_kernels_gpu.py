@@ -185,6 +185,32 @@ def test_gemm_tc_residual_add_with_the_norm_folded_into_the_next_product(R, N, K
     ops().check_device_errors(DEV)
 
 
+@pytest.mark.parametrize("R", [1, 8, 64])
+def test_the_head_product_with_the_final_norm_folded_in_at_the_benchmark_models_sizes(R):
+    """The decode step's last product as the benchmark model runs it: rows that
+    await their norm factor (partial sums of squares from the product before)
+    against a 151,936 x 4,096 head, with the factor applied in the product's
+    prologue; against norm, then product, in double precision."""
+    N, K, V = 4096, 1024, 151936
+    g = torch.Generator().manual_seed(R)
+    x = torch.randn(R, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    h = torch.randn(R, N, generator=g) * 2
+    nw = 1 + 0.1 * torch.randn(N, generator=g)
+    gd = torch.Generator(device=DEV).manual_seed(R)
+    head = (torch.randn(V, N, generator=gd, device=DEV) * 0.02).bfloat16()  # drawn on the device: 622 M numbers
+    eps = 1e-6
+    hd = h.to(DEV).clone()
+    ni = ops().gemm_tc_residual(x.to(DEV), w.to(DEV), hd, nw.to(DEV), 0.0, eps)
+    assert ni.n_part > 1  # the sums of squares arrive in parts
+    y = ops().linear(ni, head, out_dtype=torch.float32)
+    ops().check_device_errors(DEV)
+    h_ref = h.double().numpy() + x.double().numpy() @ w.double().numpy().T
+    normed = pm.rms_norm(h_ref, nw.double().numpy(), eps)
+    ref = (normed.astype(np.float32) @ head.float().cpu().numpy().T).astype(np.float64)  # on the CPU, 32-bit sums
+    assert y.shape == (R, V) and relerr(y, ref) < 8e-3
+
+
 def test_gemm_tc_refuses_what_it_cannot_do():
     from reflex_b200 import CudaError
 

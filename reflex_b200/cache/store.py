@@ -64,7 +64,10 @@ class KVGroup:
             self.table_dev = torch.zeros((max_slots, pages_per_seq), dtype=torch.int32, device=device)
         else:  # bookkeeping only (host tests)
             self.k = self.v = self.table_dev = None
-        self.table_host = torch.zeros((max_slots, pages_per_seq), dtype=torch.int32)
+        # the host's copy of the page table; pinned beside a GPU so that `flush` can
+        # copy from it without making the host wait for the device
+        pin = device is not None and torch.device(device).type == "cuda"
+        self.table_host = torch.zeros((max_slots, pages_per_seq), dtype=torch.int32, pin_memory=pin)
         # per slot: first page index still held, one past the last page index held
         self.first: Dict[int, int] = {}
         self.end: Dict[int, int] = {}
@@ -123,10 +126,16 @@ class KVGroup:
         self._dirty.pop(slot, None)
 
     def flush(self) -> None:
-        """Bring the device's page table up to date (rows that changed)."""
-        if self.table_dev is not None:
-            for slot, (lo, hi) in self._dirty.items():
-                self.table_dev[slot, lo:hi].copy_(self.table_host[slot, lo:hi], non_blocking=False)
+        """Bring the device's page table up to date: one copy of the block of rows
+        that holds every changed row, enqueued on the stream without waiting for
+        the device.  The copy reads the pinned host table when the stream reaches
+        it; an entry the host has changed again by then belongs to a position no
+        kernel enqueued before the copy reads (a sequence's later pages, or a slot's
+        next sequence, which starts only after its last step has come back), so
+        the newer value does no harm."""
+        if self.table_dev is not None and self._dirty:
+            lo, hi = min(self._dirty), max(self._dirty) + 1
+            self.table_dev[lo:hi].copy_(self.table_host[lo:hi], non_blocking=True)
         self._dirty.clear()
 
     def view(self, entry: int) -> KVView:

@@ -12,6 +12,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
+import numpy as np
 import torch
 
 
@@ -82,29 +83,41 @@ def layout(n_rows: int, n_seqs: int, n_want: int):
 
 def pack_host(tokens: Sequence[Sequence[int]], slots: Sequence[int], starts: Sequence[int],
               want: Sequence[Sequence[int]]):
-    """Flatten a step into the int32 words of `layout`, plus the host lists."""
-    new_counts = [len(t) for t in tokens]
-    row0 = [0]
-    for n in new_counts:
-        row0.append(row0[-1] + n)
-    R, S = row0[-1], len(tokens)
-    want_rows = [row0[i] + w for i, ws in enumerate(want) for w in ws]
+    """Flatten a step into the int32 words of `layout` (a NumPy array), plus the
+    host lists.  Array operations throughout: a step's cost on the host does
+    not grow with a Python loop over its rows."""
+    S = len(tokens)
+    counts = np.fromiter((len(t) for t in tokens), dtype=np.int64, count=S)
+    row0 = np.zeros(S + 1, dtype=np.int64)
+    np.cumsum(counts, out=row0[1:])
+    R = int(row0[-1])
+    starts_a = np.asarray(starts, dtype=np.int64)
+    slots_a = np.asarray(slots, dtype=np.int64)
+    if R == S:  # one token a sequence: the decode step
+        flat = np.fromiter((t[0] for t in tokens), dtype=np.int64, count=S)
+        row_pos, row_slot = starts_a, slots_a
+    else:
+        flat = np.concatenate([np.asarray(t, dtype=np.int64) for t in tokens])
+        first = np.repeat(row0[:-1], counts)
+        row_pos = np.repeat(starts_a, counts) + (np.arange(R, dtype=np.int64) - first)
+        row_slot = np.repeat(slots_a, counts)
+    want_rows = [int(row0[i]) + w for i, ws in enumerate(want) for w in ws]
     offs, total = layout(R, S, len(want_rows))
-    words = [0] * total
+    words = np.zeros(total, dtype=np.int32)
 
     def put(name, values):
         p, n = offs[name]
         words[p:p + n] = values
 
-    put("tokens", [t for seq in tokens for t in seq])
-    put("row_pos", [starts[i] + j for i in range(S) for j in range(new_counts[i])])
-    put("row_slot", [slots[i] for i in range(S) for _ in range(new_counts[i])])
-    put("seq_slot", list(slots))
-    put("seq_start", list(starts))
-    put("seq_new", new_counts)
+    put("tokens", flat)
+    put("row_pos", row_pos)
+    put("row_slot", row_slot)
+    put("seq_slot", slots_a)
+    put("seq_start", starts_a)
+    put("seq_new", counts)
     put("seq_row0", row0)
     put("want_rows", want_rows)
-    return words, offs, new_counts, row0, want_rows
+    return words, offs, counts.tolist(), row0.tolist(), want_rows
 
 
 class Staging:
@@ -119,7 +132,7 @@ class Staging:
         self.events: List[Optional[torch.cuda.Event]] = [None] * depth
         self.next = 0
 
-    def copy(self, words: List[int], dev: torch.Tensor) -> None:
+    def copy(self, words, dev: torch.Tensor) -> None:
         """words -> pinned buffer -> `dev` (device int32, at least as long), on
         the current stream, without blocking the host."""
         i = self.next
@@ -130,7 +143,7 @@ class Staging:
         if self.buffers[i] is None or self.buffers[i].numel() < n:
             self.buffers[i] = torch.empty((max(n, 256),), dtype=torch.int32, pin_memory=True)
         host = self.buffers[i][:n]
-        host.copy_(torch.tensor(words, dtype=torch.int32))
+        host.copy_(torch.from_numpy(words))
         dev[:n].copy_(host, non_blocking=True)
         if self.events[i] is None:
             self.events[i] = torch.cuda.Event()
@@ -145,13 +158,15 @@ def make_batch(tokens, slots, starts, want, device, buffer: Optional[torch.Tenso
     reads the buffer sees the new step."""
     words, offs, new_counts, row0, want_rows = pack_host(tokens, slots, starts, want)
     if buffer is None:
-        dev = torch.empty((len(words),), dtype=torch.int32, device=device)
+        from ..ops.workspace import new
+
+        dev = new((len(words),), torch.int32, device, keep=True)  # lives for the step
     else:
         dev = buffer[: len(words)]
     if staging is not None:
         staging.copy(words, dev)
     else:
-        dev.copy_(torch.tensor(words, dtype=torch.int32))
+        dev.copy_(torch.from_numpy(words))
 
     def f(name):
         p, n = offs[name]

@@ -67,5 +67,8 @@ class DecodeGraph:
                 self.logits = eng.model.forward(batch, eng.cache)
             self.kernels = ops.launch_count() - before  # this library's kernels in the graph
             self.graph = g
+            # the captured launches point into the workspace as it is now: keep that
+            # memory alive, whatever the workspace grows to later
+            self.workspace_memory = eng.workspace.buffers() if eng.workspace is not None else None
         self.graph.replay()
         return self.logits if borrow else self.logits.clone()

@@ -110,6 +110,7 @@ class CausalLM:
             # the norm that will consume this run's result: the next run's first norm, or the final one
             next_norm = (getattr(self.layers[order[i + 1].layer], "fusable_first_norm", None)
                          if i + 1 < len(order) else self.final_norm)
+            ops.workspace.next_phase()  # this run's working memory; the last run's results stay readable
             ctx = RunContext(batch=batch, writes_cache=run.writes_cache, entry=run.cache)
             kind = cache.has(run.cache)
             if kind == "kv":
@@ -133,7 +134,7 @@ class CausalLM:
                 normed = self.final_norm(hidden, rows=rows)
         else:
             normed = self.final_norm(hidden, delta=pending, rows=rows)
-        out = ops.linear(normed, self.head, out_dtype=torch.float32)
+        out = ops.linear(normed, self.head, out_dtype=torch.float32, own=True)  # the caller's to keep
         if self.spec.logit_scale != 1.0:
             out = out * self.spec.logit_scale
         ops.prof_mark("head")

@@ -23,6 +23,7 @@ from ..cache.store import PAGE_TOKENS, Cache
 from ..errors import CacheError, InvalidInput
 from .batch import Staging, StepBatch, decode_context_bucket, make_batch
 from .model import CausalLM
+from ..ops.workspace import Workspace, use as use_workspace
 
 StepEntry = Tuple[int, Sequence[int], Sequence[int]]  # (sequence, tokens, wanted places)
 
@@ -53,7 +54,11 @@ class Engine:
         self._graph_pool = None
         self._eager_decodes = 0  # eager decode steps run so far
         self.steps_run = 0
-        self.staging = Staging(self.device) if torch.device(self.device).type == "cuda" else None
+        on_gpu = torch.device(self.device).type == "cuda"
+        self.staging = Staging(self.device) if on_gpu else None
+        # the steps' working memory: every op's result is a view into it, so a step
+        # allocates nothing; it grows to what the largest step so far needed
+        self.workspace = Workspace(self.device) if on_gpu else None
 
     # --- sequences ----------------------------------------------------------
     def open(self) -> int:
@@ -120,18 +125,21 @@ class Engine:
         try:
             n_want = sum(len(w) for w in want)
             # the captured step has one token and one wanted row, that token's, per sequence
-            if (head is None and self.use_graphs and all(len(t) == 1 for t in tokens)
-                    and all(w == [0] for w in want)):
-                logits = self._decode_graphed(tokens, slots, starts, want, borrow=borrow)
-            else:
-                batch = make_batch(tokens, slots, starts, want, self.device, staging=self.staging)
-                if head is not None:
-                    logits = head(batch)
-                elif n_want:
-                    logits = self.model.forward(batch, cache)
+            with use_workspace(self.workspace):
+                if (head is None and self.use_graphs and all(len(t) == 1 for t in tokens)
+                        and all(w == [0] for w in want)):
+                    logits = self._decode_graphed(tokens, slots, starts, want, borrow=borrow)
                 else:
-                    self.model.hidden_states(batch, cache)
-                    logits = torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+                    batch = make_batch(tokens, slots, starts, want, self.device, staging=self.staging)
+                    if head is not None:
+                        logits = head(batch)
+                    elif n_want:
+                        logits = self.model.forward(batch, cache)
+                    else:
+                        self.model.hidden_states(batch, cache)
+                        logits = torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+            if self.workspace is not None:
+                self.workspace.settle()
         except Exception:
             # the cache as it was: pages given back, fixed-size state put back
             for g, ends in zip(cache.kv_groups, before):
@@ -197,12 +205,15 @@ class Engine:
         cache.reserve(growth)
         saved_state = cache.snapshot_state(slots)
         try:
-            if self.use_graphs:
-                logits = self._decode_graphed(tokens, slots, starts, want, tokens_dev=tokens_dev, borrow=borrow)
-            else:
-                batch = make_batch(tokens, slots, starts, want, self.device, staging=self.staging)
-                batch.tokens.copy_(tokens_dev)
-                logits = self.model.forward(batch, cache)
+            with use_workspace(self.workspace):
+                if self.use_graphs:
+                    logits = self._decode_graphed(tokens, slots, starts, want, tokens_dev=tokens_dev, borrow=borrow)
+                else:
+                    batch = make_batch(tokens, slots, starts, want, self.device, staging=self.staging)
+                    batch.tokens.copy_(tokens_dev)
+                    logits = self.model.forward(batch, cache)
+            if self.workspace is not None:
+                self.workspace.settle()
         except Exception:
             # the cache as it was: pages given back, fixed-size state put back
             for g, ends in zip(cache.kv_groups, before):

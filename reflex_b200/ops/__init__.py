@@ -15,7 +15,8 @@ import torch
 from ..errors import CudaError, InvalidInput
 import os as _os
 
-from . import native
+from . import native, workspace
+from .workspace import new as _new
 
 F32, BF16 = 0, 1
 
@@ -55,7 +56,7 @@ def embed(table: torch.Tensor, ids: torch.Tensor, scale: float, err_flag: torch.
     """hidden[r] = table[ids[r]] * scale, as float32 [R, H]."""
     V, H = table.shape
     R = ids.numel()
-    out = torch.empty((R, H), dtype=torch.float32, device=table.device)
+    out = _new((R, H), torch.float32, table.device, keep=True)  # the residual stream: lives for the whole step
     st = native.lib().rfx_embed(
         _chk(table, "table"), dt_code(table.dtype), _chk(ids, "ids", torch.int32), R, H, V,
         float(scale), out.data_ptr(), _chk(err_flag, "err_flag", torch.int32), _stream())
@@ -75,7 +76,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     R, H = x.shape
     _chk(x, "x", torch.float32)
     r_out = R if rows is None else rows.numel()
-    out = torch.empty((r_out, H), dtype=out_dtype, device=x.device) if want_out else None
+    out = _new((r_out, H), out_dtype, x.device) if want_out else None
     x_out = x if (delta is not None and update_residual and rows is None) else None
     st = native.lib().rfx_rmsnorm(
         x.data_ptr(), _chk(delta, "delta"), dt_code(delta.dtype) if delta is not None else 0,
@@ -100,7 +101,7 @@ def swiglu(gate_up: torch.Tensor, alternating: bool = False) -> torch.Tensor:
     2i + 1."""
     R, two_i = gate_up.shape
     I = two_i // 2
-    out = torch.empty((R, I), dtype=gate_up.dtype, device=gate_up.device)
+    out = _new((R, I), gate_up.dtype, gate_up.device)
     st = native.lib().rfx_swiglu(_chk(gate_up, "gate_up"), out.data_ptr(), dt_code(gate_up.dtype),
                                  R, I, 1 if alternating else 0, _stream())
     native.check(st, "swiglu")
@@ -222,7 +223,7 @@ class NormedInput:
 
 
 def gemm_tc(x, weight: torch.Tensor, out_dtype: torch.dtype = torch.float32,
-            ksplit: int = 0, swiglu_pairs: bool = False) -> torch.Tensor:
+            ksplit: int = 0, swiglu_pairs: bool = False, own: bool = False) -> torch.Tensor:
     """The tcgen05/TMA product y = x @ weight.T (bfloat16 in, float32 accumulate).
     With `swiglu_pairs` the weight's rows alternate gate, up and the result is
     silu(gate) * up, [R, N / 2].  `x` may be a `NormedInput`."""
@@ -233,7 +234,7 @@ def gemm_tc(x, weight: torch.Tensor, out_dtype: torch.dtype = torch.float32,
     N = weight.shape[0]
     _chk(x, "x", torch.bfloat16)
     _chk(weight, "weight", torch.bfloat16)
-    y = torch.empty((R, N // 2 if swiglu_pairs else N), dtype=out_dtype, device=x.device)
+    y = _new((R, N // 2 if swiglu_pairs else N), out_dtype, x.device, own=own)
     st = native.lib().rfx_gemm_bf16_tc(
         x.data_ptr(), weight.data_ptr(), y.data_ptr(), dt_code(out_dtype), R, N, K, ksplit,
         1 if swiglu_pairs else 0, normed.ssq.data_ptr() if normed is not None else 0,
@@ -243,7 +244,8 @@ def gemm_tc(x, weight: torch.Tensor, out_dtype: torch.dtype = torch.float32,
     return y
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+           own: bool = False) -> torch.Tensor:
     """y = x @ weight.T for weight [N, K] row-major.
 
     float32: this library's own CUDA-core product (no reduced-precision matrix
@@ -251,7 +253,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     bfloat16: the weight-streaming tcgen05 kernel for up to GEMV_MAX_ROWS rows
     (decode), the library matrix product (cuBLAS, 32-bit accumulation) above
     that, where the reference uses a library product too
-    (src/model/kernels.rs:2518-2561)."""
+    (src/model/kernels.rs:2518-2561).  The result comes from the step's workspace;
+    with `own` it gets memory of its own (what a step hands to its caller)."""
     R, K = x.shape
     N, K2 = weight.shape
     if K != K2:
@@ -259,20 +262,21 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     if x.dtype != weight.dtype:
         raise InvalidInput(f"linear: x is {x.dtype}, weight is {weight.dtype}")
     if isinstance(x, NormedInput):
-        return gemm_tc(x, weight, out_dtype or torch.bfloat16)
+        return gemm_tc(x, weight, out_dtype or torch.bfloat16, own=own)
     _chk(x, "x")
     _chk(weight, "weight")
     if x.dtype == torch.float32:
-        y = torch.empty((R, N), dtype=torch.float32, device=x.device)
+        y = _new((R, N), torch.float32, x.device, own=own)
         st = native.lib().rfx_gemm_f32(x.data_ptr(), weight.data_ptr(), y.data_ptr(), R, N, K, _stream())
         native.check(st, f"gemm_f32 (R={R}, N={N}, K={K})")
         return y
     out_dtype = out_dtype or torch.bfloat16
     if R <= GEMV_MAX_ROWS and K % 8 == 0:
-        return gemm_tc(x, weight, out_dtype)
+        return gemm_tc(x, weight, out_dtype, own=own)
+    y = _new((R, N), out_dtype, x.device, own=own)
     if out_dtype == torch.float32:
-        return torch.mm(x, weight.t(), out_dtype=torch.float32)
-    return torch.mm(x, weight.t())
+        return torch.mm(x, weight.t(), out_dtype=torch.float32, out=y)
+    return torch.mm(x, weight.t(), out=y)
 
 
 def gather_dot(x: torch.Tensor, weight: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
@@ -310,8 +314,8 @@ def gemm_tc_residual(x: torch.Tensor, weight: torch.Tensor, hidden: torch.Tensor
     _chk(norm_weight, "norm_weight", torch.float32)
     if tuple(hidden.shape) != (R, N) or norm_weight.numel() != N:
         raise InvalidInput("gemm_tc_residual: hidden must be [rows, out] and the norm weight [out]")
-    hb = torch.empty((R, N), dtype=torch.bfloat16, device=x.device)
-    ssq = torch.empty((R * native.lib().rfx_gemm_bf16_tc_max_parts(N),), dtype=torch.float32, device=x.device)
+    hb = _new((R, N), torch.bfloat16, x.device)
+    ssq = _new((R * native.lib().rfx_gemm_bf16_tc_max_parts(N),), torch.float32, x.device)
     n_part = ctypes.c_int(0)
     st = native.lib().rfx_gemm_bf16_tc_residual(
         x.data_ptr(), weight.data_ptr(), hidden.data_ptr(), norm_weight.data_ptr(), float(norm_offset),
@@ -387,7 +391,7 @@ def qkv_post(qkv: torch.Tensor, q_weight, k_weight, eps: float, weight_offset: f
     nkv_in = nkv if writes_cache else 0
     if qkv.shape[1] != (nq + 2 * nkv_in) * head_dim:
         raise InvalidInput("qkv_post: qkv width does not match the head counts")
-    q = torch.empty((R, nq * head_dim), dtype=out_dtype, device=qkv.device)
+    q = _new((R, nq * head_dim), out_dtype, qkv.device)
     st = native.lib().rfx_qkv_post(
         _chk(qkv, "qkv"), dt_code(qkv.dtype), qkv.shape[1], _chk(q_weight, "q_norm", torch.float32),
         _chk(k_weight, "k_norm", torch.float32), float(eps), float(weight_offset),
@@ -405,7 +409,7 @@ def attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
                     row_slot: torch.Tensor, nq: int, nkv: int, head_dim: int,
                     window: Optional[int], scale: float) -> torch.Tensor:
     R = q.shape[0]
-    out = torch.empty_like(q)
+    out = _new(q.shape, q.dtype, q.device)
     st = native.lib().rfx_attention_plain(
         _chk(q, "q"), _chk(k_pages, "k_pages", q.dtype), _chk(v_pages, "v_pages", q.dtype),
         dt_code(q.dtype), _chk(page_table, "page_table", torch.int32), page_table.shape[1],
@@ -472,7 +476,7 @@ def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_sl
     if head_dim % 16 or not (16 <= head_dim <= 256):
         raise InvalidInput(f"attention_decode takes head_dim in steps of 16 up to 256, got {head_dim}")
     n_splits = n_splits or decode_splits(R, nq, nkv)
-    out = torch.empty_like(q)
+    out = _new(q.shape, q.dtype, q.device)
     if CLUSTER_MERGE and n_splits in (2, 4, 8):
         # the splits as one thread-block cluster that merges its partials itself
         st = native.lib().rfx_attention_decode_cluster(
@@ -483,8 +487,7 @@ def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_sl
         if st != native.ERR_UNSUPPORTED:
             native.check(st, f"attention_decode_cluster (head_dim={head_dim}, splits={n_splits})")
             return out
-    partial = (torch.empty((R * nq * n_splits * (head_dim + 2),), dtype=torch.float32, device=q.device)
-               if n_splits > 1 else None)
+    partial = _new((R * nq * n_splits * (head_dim + 2),), torch.float32, q.device) if n_splits > 1 else None
     st = native.lib().rfx_attention_decode(
         q.data_ptr(), _chk(k_pages, "k_pages", torch.bfloat16), _chk(v_pages, "v_pages", torch.bfloat16),
         _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
@@ -507,7 +510,7 @@ def attention_prefill(q, k_pages, v_pages, page_table, page_size, seq_slot, seq_
         raise InvalidInput(f"attention_prefill takes head_dim in steps of 16 up to 256, got {head_dim}")
     if nq // nkv > 128:
         raise InvalidInput(f"attention_prefill takes up to 128 query heads per kv head, got {nq // nkv}")
-    out = torch.empty_like(q)
+    out = _new(q.shape, q.dtype, q.device)
     S = seq_slot.numel()
     st = native.lib().rfx_attention_prefill(
         q.data_ptr(), _chk(k_pages, "k_pages", torch.bfloat16), _chk(v_pages, "v_pages", torch.bfloat16),
@@ -527,7 +530,7 @@ def attention_prefill_tc(q, k_pages, v_pages, page_table, page_size, seq_slot, s
         raise InvalidInput(f"attention_prefill_tc takes head_dim 64 or 128, got {head_dim}")
     if nq // nkv > 128:
         raise InvalidInput(f"attention_prefill_tc takes up to 128 query heads per kv head, got {nq // nkv}")
-    out = torch.empty_like(q)
+    out = _new(q.shape, q.dtype, q.device)
     st = native.lib().rfx_attention_prefill_tc(
         q.data_ptr(), _chk(k_pages, "k_pages", torch.bfloat16), _chk(v_pages, "v_pages", torch.bfloat16),
         k_pages.shape[0], _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,

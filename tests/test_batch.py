@@ -11,7 +11,7 @@ def test_pack_host_lays_out_rows_and_wanted_places():
 
     def field(name):
         p, n = offs[name]
-        return words[p:p + n]
+        return words[p:p + n].tolist()
 
     assert field("tokens") == [5, 6, 7, 9, 1, 2]
     assert field("row_pos") == [10, 11, 12, 0, 63, 64]

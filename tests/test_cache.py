@@ -170,3 +170,43 @@ def test_random_traffic_keeps_invariants():
     for s in list(live):
         c.give_slot(s)
     assert all(g.pool.held_count == 0 for g in c.kv_groups) and c.slots.held_count == 0
+
+
+def test_workspace_regions_take_turns_and_grow_after_the_step():
+    """The step's working memory: a request a region cannot hold is served by
+    the allocator and remembered; after `settle` the same requests are views
+    into the regions, a phase's memory is reused two runs later, what the last
+    run made stays untouched, and `keep` memory lives for the whole step."""
+    import torch
+
+    from reflex_b200.ops import workspace as wsm
+
+    ws = wsm.Workspace("cpu")
+
+    def one_step():
+        made = []
+        with wsm.use(ws):
+            made.append(wsm.new((10, 8), torch.float32, "cpu", keep=True))
+            for run in range(4):
+                wsm.next_phase()
+                made.append(wsm.new((100,), torch.float32, "cpu"))
+                made.append(wsm.new((7, 3), torch.bfloat16, "cpu"))
+        ws.settle()
+        return made
+
+    one_step()
+    assert ws.misses == 9 and ws.nbytes > 0
+    a = one_step()
+    assert ws.misses == 9  # everything came from the regions this time
+    hidden, r0, r1, r2, r3 = a[0], a[1], a[3], a[5], a[7]
+    assert r0.data_ptr() == r2.data_ptr() and r1.data_ptr() == r3.data_ptr() and r0.data_ptr() != r1.data_ptr()
+    assert all(t.data_ptr() % 256 == 0 for t in a)
+    assert hidden.shape == (10, 8) and a[2].dtype == torch.bfloat16
+    own = None
+    with wsm.use(ws):
+        own = wsm.new((5,), torch.float32, "cpu", own=True)
+        inside = wsm.new((5,), torch.float32, "cpu")
+    bufs = [b for b in ws.buffers() if b is not None]
+    lies_in = lambda t: any(b.data_ptr() <= t.data_ptr() < b.data_ptr() + b.numel() for b in bufs)
+    assert lies_in(inside) and not lies_in(own)
+    assert not lies_in(wsm.new((5,), torch.float32, "cpu"))  # no step: the allocator's

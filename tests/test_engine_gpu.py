@@ -534,3 +534,22 @@ def test_the_benchmark_model_at_full_depth_and_vocabulary():
                 assert int(g[r].argmax()) == int(ref[r].argmax())
     print(f"full-depth bfloat16 error {worst:.3e}")
     assert worst < FULL_DEPTH_BF16_TOL, worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_take_their_memory_from_the_engines_workspace(dtype):
+    """After the first step of a size has told the workspace how much it needs,
+    further steps of that size are served from it entirely (no request falls
+    through to the allocator), prefill and eager decode alike, and give the
+    same logits as before."""
+    V = ALL["B"]["vocab_size"]
+    folder = helpers.model_folder("B", 7, stored(dtype))
+    eng = helpers.make_engine(folder, dtype, max_tokens=1024, use_graphs=False)
+    toks = helpers.random_tokens(90, V, 12)
+    first = helpers.run_tail_one_by_one(eng, toks, 8)
+    misses = eng.workspace.misses
+    assert misses > 0 and eng.workspace.nbytes > 0
+    again = helpers.run_tail_one_by_one(eng, toks, 8)
+    assert eng.workspace.misses == misses
+    assert np.array_equal(first, again)
+    assert helpers.rel_err(again, helpers.plain_logits(folder, toks)) < tol(dtype)

@@ -23,6 +23,7 @@
 #include <tuple>
 
 #include "common.cuh"
+#include "paged.cuh"
 #include "sm100.cuh"
 
 namespace cg = cooperative_groups;
@@ -81,7 +82,29 @@ struct Fuse {
     float nw_offset;
     __nv_bfloat16* hb;     // [R, N]
     float* ssq_out;        // [R][tiles * ksplit]
+    // EPI 3 (below): the q/k/v product of a decode step, finished per head
+    const float* q_w;      // per-head norm weights [head_dim]; null: no per-head norm
+    const float* k_w;
+    float qk_eps, qk_offset;
+    const float* rope_denom;  // [head_dim / 2] angle denominators; null: no rotation
+    float magnitude;
+    const int* row_pos;    // [R]
+    const int* row_slot;   // [R]
+    __nv_bfloat16* q_out;  // [R, nq * head_dim]
+    __nv_bfloat16* k_pages;
+    __nv_bfloat16* v_pages;
+    rfx::PagedKV cache;
+    int nq, nkv_in, head_dim;
 };
+
+//  * EPI 3: W is the stacked q/k/v matrix of an attention layer whose head size
+//    is 64 or 128, so a 128-row tile holds whole heads.  The split-K partials are
+//    exchanged by activation row instead of by weight row: each rank of the
+//    cluster ends up with complete head vectors for its share of the rows and
+//    finishes them there: per-head RMSNorm of q and k, rotary encoding over the
+//    whole head (half-split pairs), q to the workspace, k and v into the paged
+//    cache at the row's position.  One launch instead of product + `qkv_post`,
+//    and the 32-bit q/k/v rows never go to memory.  Formulas as in qkv_post.cu.
 
 // EPI 0: y = x W^T.  EPI 1: W's rows alternate gate, up (row 2j gate_j, row 2j+1
 // up_j) and y[r, j] = silu(gate_j) * up_j, so the SwiGLU activation costs no
@@ -92,6 +115,163 @@ using rfx::silu_mul_for;
 
 using rfx::store2;
 using rfx::store4;
+
+// One head vector of a row, spread over a warp (lane l holds elements l, l + 32,
+// ...): per-head norm, rotation, store.  `rot`: this row's (cos, sin) pairs;
+// `w`: the lane's norm weights (offset added), null for no norm.
+template <int D>
+__device__ __forceinline__ void finish_head(float* hv, bool rotate_it, const float* w, const float* rot,
+                                            float eps, __nv_bfloat16* dst, int lane) {
+    constexpr int EPL = D / 32;  // elements per lane
+    if (w != nullptr) {
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) ss = fmaf(hv[i], hv[i], ss);
+        ss = rfx::warp_sum(ss);
+        const float rinv = 1.0f / sqrtf(ss * (1.0f / (float)D) + eps);
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) hv[i] = (hv[i] * rinv) * w[i];
+    }
+    if (rotate_it) {
+#pragma unroll
+        for (int i = 0; i < EPL / 2; ++i) {  // the pair (e, e + D / 2) lies in this lane
+            const float2 cs = *reinterpret_cast<const float2*>(rot + 2 * (lane + 32 * i));
+            const float lo = hv[i], hi = hv[i + EPL / 2];
+            hv[i] = fmaf(hi, -cs.y, lo * cs.x);
+            hv[i + EPL / 2] = fmaf(lo, cs.y, hi * cs.x);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) dst[lane + 32 * i] = __float2bfloat16_rn(hv[i]);
+}
+
+// The epilogue of EPI 3, run by the four epilogue warps (threads 64 .. 191).
+// recv: [BN][BM] floats that receive partial head vectors, by (source rank, row);
+// rot: [rows of this rank][head_dim / 2] (cos, sin) pairs, then per row its place
+// in the cache.  Everything that does not need the accumulator (the rows'
+// rotation, their places in the cache, the lane's norm weights) is made while
+// the main loop still runs: positions, slots and the page table are the step's
+// inputs, no other kernel's output.
+template <int BN, bool PRO>
+__device__ __forceinline__ void head_epilogue(float* recv, float* rot, uint32_t tmem_d, uint64_t* tmem_full_bar,
+                                              bool have, int ksplit, int z, int r0, int R, const Fuse& f,
+                                              const float* rstd_s, int* err) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q4 = warp & 3, m = q4 * 32 + lane, et = threadIdx.x - 64, ew = warp - 2;
+    const int D = f.head_dim, half = D / 2;
+    const int cw = BN / ksplit;  // activation rows each rank finishes (ksplit divides BN)
+    const bool rotate = f.rope_denom != nullptr;
+    unsigned long long* place = reinterpret_cast<unsigned long long*>(rot + (size_t)cw * D);  // [cw]
+    if (rotate) {
+        for (int e = et; e < cw * half; e += 128) {
+            const int cl = e / half, i = e - cl * half, r = r0 + z * cw + cl;
+            float sv = 0.0f, cv = 1.0f;
+            if (r < R) {
+                sincosf((float)f.row_pos[r] / f.rope_denom[i], &sv, &cv);  // as qkv_post's bfloat16 forms
+                sv *= f.magnitude;
+                cv *= f.magnitude;
+            }
+            rot[2 * e] = cv;
+            rot[2 * e + 1] = sv;
+        }
+    }
+    if (et < cw) {
+        const int r = r0 + z * cw + et;
+        unsigned long long off = 0;
+        if (r < R && f.nkv_in > 0) off = rfx::kv_offset(f.cache, f.row_slot[r], f.row_pos[r], 0);
+        place[et] = off;  // kv head 0's place; the others lie a (page, head) tile apart
+    }
+    // this tile's heads and the lane's norm weights for them
+    const int n_heads = f.nq + 2 * f.nkv_in;
+    const int hpt = BM / D;
+    int kind[2] = {3, 3};
+    float wv[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+    bool normed[2] = {false, false};
+#pragma unroll
+    for (int hi = 0; hi < 2; ++hi) {
+        const int head = blockIdx.x * hpt + hi;
+        if (hi < hpt && head < n_heads) {
+            kind[hi] = head < f.nq ? 0 : (head < f.nq + f.nkv_in ? 1 : 2);
+            const float* w = kind[hi] == 0 ? f.q_w : (kind[hi] == 1 ? f.k_w : nullptr);
+            if (w != nullptr) {
+                normed[hi] = true;
+                if (D == 128) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) wv[i] = f.qk_offset + w[lane + 32 * i];
+                } else {
+                    wv[2 * hi] = f.qk_offset + w[lane];
+                    wv[2 * hi + 1] = f.qk_offset + w[lane + 32];
+                }
+            }
+        }
+    }
+    if (have && !mbar_wait(tmem_full_bar, 0)) {
+        if (lane == 0) atomicExch(err, 3);
+        have = false;
+    }
+    tc_fence_after_sync();
+    // Row m of the tile, for every activation row (column of the accumulator): to
+    // the rank that finishes that activation row, slot [this rank][row][m].
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t lane_base = tmem_d + ((uint32_t)(q4 * 32) << 16);
+    uint32_t ahead[16];
+    if (have) tmem_ld_16_nowait(lane_base, ahead);
+#pragma unroll 1
+    for (int c = 0; c < BN / 16; ++c) {
+        float v[16];
+        if (have) {
+            tmem_ld_wait_16(ahead);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(ahead[j]);
+            if (c + 1 < BN / 16) tmem_ld_16_nowait(lane_base + (uint32_t)((c + 1) * 16), ahead);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int col = c * 16 + j, owner = col / cw, cl = col - owner * cw;
+            if (r0 + col < R) {  // rows past the batch are nobody's
+                float* base = ksplit > 1 ? cluster.map_shared_rank(recv, owner) : recv;
+                base[(size_t)(z * cw + cl) * BM + m] = v[j];
+            }
+        }
+    }
+    tc_fence_before_sync();
+    if (ksplit > 1) cluster.sync();
+    else asm volatile("bar.sync 1, 128;" ::: "memory");
+    // A warp finishes a row at a time: the ranks' partials summed in rank order.
+    const size_t kv_head_stride = (size_t)f.cache.page_size * D;
+    for (int cl = ew; cl < cw; cl += 4) {
+        const int col = z * cw + cl, r = r0 + col;
+        if (r >= R) continue;
+        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int p = 0; p < ksplit; ++p) {
+            const float* src = recv + (size_t)(p * cw + cl) * BM + lane;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] += src[32 * i];
+        }
+        if (PRO) {
+            const float fr = rstd_s[col];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] *= fr;
+        }
+        const float* rrow = rot + (size_t)2 * cl * half;
+        const size_t kv0 = (size_t)place[cl];
+#pragma unroll
+        for (int hi = 0; hi < 2; ++hi) {
+            if (kind[hi] > 2) continue;
+            const int head = blockIdx.x * hpt + hi;
+            __nv_bfloat16* dst;
+            if (kind[hi] == 0) dst = f.q_out + ((size_t)r * f.nq + head) * D;
+            else if (kind[hi] == 1) dst = f.k_pages + kv0 + (size_t)(head - f.nq) * kv_head_stride;
+            else dst = f.v_pages + kv0 + (size_t)(head - f.nq - f.nkv_in) * kv_head_stride;
+            const bool rot_it = rotate && kind[hi] < 2;
+            if (D == 128) finish_head<128>(v, rot_it, normed[hi] ? wv : nullptr, rrow, f.qk_eps, dst, lane);
+            else finish_head<64>(v + 2 * hi, rot_it, normed[hi] ? wv + 2 * hi : nullptr, rrow, f.qk_eps, dst, lane);
+        }
+    }
+}
 
 template <int BN, typename TO, int EPI, bool PRO>
 __global__ void __launch_bounds__(THREADS)
@@ -257,6 +437,10 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         float* stage0 = reinterpret_cast<float*>(tiles + (size_t)stages * S::STAGE_BYTES);
         const float* recv = stage0;
         float* sq = reinterpret_cast<float*>(tiles);  // [BN][mw] (split K); this CTA's stages are drained by then
+        if constexpr (EPI == 3) {
+            head_epilogue<BN, PRO>(stage0, stage0 + BN * BM, tmem_d, &tmem_full_bar, nkb > 0, ksplit, z, r0, R,
+                                   fuse, rstd_s, err);
+        } else {
         // Four neighbouring rows of the tile at a time where the sizes allow it
         // (the slices are whole multiples of four and so are the output's rows):
         // one 16-byte access per rank's partial, per residual, per result.
@@ -556,6 +740,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (!dry) tc_fence_before_sync();
             }
         }
+        }  // EPI != 3
     }
     // the producer and the MMA warp take part in the cluster's barrier too
     if (warp < 2 && ksplit > 1) {
@@ -656,8 +841,14 @@ struct Cut {
     int bm, tiles, ks;
 };
 
-Cut choose_cut(int N, int r_tiles, int num_kb, int ks_req) {
+Cut choose_cut(int N, int r_tiles, int num_kb, int ks_req, bool whole_tiles) {
     if (ks_req > 0) return Cut{BM, (N + BM - 1) / BM, ks_req};
+    if (whole_tiles) {  // tiles of exactly 128 rows; K split while CTAs are few
+        const int t = (N + BM - 1) / BM;
+        int k = 1;
+        while (k < 8 && t * r_tiles * k * 2 <= 2 * sm_count() && num_kb >= k * 4) k *= 2;
+        return Cut{BM, t, k};
+    }
     const int sms = sm_count();
     const int cps_first = knobs().cps;  // tuning aid: CTAs per SM to try first
     for (int pass = 0; pass < 2 && cps_first > 0; ++pass) {
@@ -698,7 +889,8 @@ int launch(const void* x, const void* W, void* y, int R, int N, int K, int kspli
     using S = Shape<BN>;
     const int r_tiles = (R + BN - 1) / BN;
     const int num_kb = (K + BK - 1) / BK;
-    Cut cut = choose_cut(N, r_tiles, num_kb, ksplit_req);
+    Cut cut = choose_cut(N, r_tiles, num_kb, ksplit_req, EPI == 3);
+    if (EPI == 3 && (r_tiles != 1 || BN % cut.ks)) return RFX_ERR_UNSUPPORTED;
     if (EPI == 1 && (cut.bm & 1)) {  // pairs must not straddle tiles
         cut.bm += 1;
         if (cut.bm > BM) return RFX_ERR_UNSUPPORTED;
@@ -721,11 +913,14 @@ int launch(const void* x, const void* W, void* y, int R, int N, int K, int kspli
     // after the stages, the tile that receives the cluster's partial rows
     constexpr int RECV_BYTES = BN * BM * 4;
     const int cap = knobs().smem_cap_kb * 1024;  // tuning aid
-    while (stages > 3 && stages * S::STAGE_BYTES + RECV_BYTES > cap) --stages;
+    // EPI 3 keeps its rows' rotation table behind the receive tile: (cos, sin) per row and pair
+    // EPI 3 keeps its rows' rotation table and places behind the receive tile
+    const int rot_bytes = EPI == 3 ? (BN / ks) * (fuse_in.head_dim * 4 + 8) : 0;
+    while (stages > 3 && stages * S::STAGE_BYTES + RECV_BYTES + rot_bytes > cap) --stages;
     if (stages * S::STAGE_BYTES < BN * BM * 4) return RFX_ERR_UNSUPPORTED;  // the squares of EPI 2
     if (n_part_out) *n_part_out = cut.tiles * ks;
     if (EPI == 2 && r_tiles != 1) return RFX_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)stages * S::STAGE_BYTES + RECV_BYTES + 1024;
+    const size_t smem = (size_t)stages * S::STAGE_BYTES + RECV_BYTES + rot_bytes + 1024;
     auto kernel = gemm_wt_kernel<BN, TO, EPI, PRO>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -746,7 +941,7 @@ int dispatch(const void* x, const void* W, void* y, int R, int N, int K, int ksp
     if (R <= 16) return launch<16, TO, EPI, PRO>(x, W, y, R, N, K, ksplit, fuse, n_part_out, err, s);
     if (R <= 32) return launch<32, TO, EPI, PRO>(x, W, y, R, N, K, ksplit, fuse, n_part_out, err, s);
     if (R <= 64) return launch<64, TO, EPI, PRO>(x, W, y, R, N, K, ksplit, fuse, n_part_out, err, s);
-    if (EPI == 2 || PRO) return RFX_ERR_UNSUPPORTED;  // the fused forms are for decode-sized batches
+    if (EPI >= 2 || PRO) return RFX_ERR_UNSUPPORTED;  // the fused forms are for decode-sized batches
     return launch<128, TO, EPI, PRO>(x, W, y, R, N, K, ksplit, fuse, n_part_out, err, s);
 }
 
@@ -814,6 +1009,54 @@ extern "C" int rfx_gemm_bf16_tc_residual(const void* x, const void* W, float* h,
     f.hb = (__nv_bfloat16*)hb;
     f.ssq_out = ssq_out;
     return dispatch<float, 2, false>(x, W, nullptr, R, N, K, ksplit, f, n_part_out, err, (cudaStream_t)stream);
+}
+
+// The q/k/v product of a decode step, finished per head (R <= 64, head_dim 64 or
+// 128, the rotation, if any, over the whole head in half-split pairs):
+//   q_out [R, nq * head_dim] = rotate(norm(x . Wq^T));  the key rotate(norm(x . Wk^T))
+//   and the value x . Wv^T of row r into the paged cache at (row_slot[r], row_pos[r]).
+// W is [(nq + 2 nkv_in) * head_dim, K]; nkv_in is nkv, or 0 for a product that
+// brings queries only.  ssq_in as in rfx_gemm_bf16_tc.
+extern "C" int rfx_gemm_bf16_tc_qkv(const void* x, const void* W, int R, int K, const float* ssq_in,
+                                    int n_part_in, int norm_h, float eps, const float* q_w,
+                                    const float* k_w, float qk_eps, float qk_offset,
+                                    const float* rope_denom, float magnitude, const int* row_pos,
+                                    const int* row_slot, void* q_out, void* k_pages, void* v_pages,
+                                    const int* page_table, int max_pages, int page_size, int nq,
+                                    int nkv_in, int nkv, int head_dim, int* err, void* stream) {
+    if (R <= 0) return 0;
+    if (R > 64 || (head_dim != 64 && head_dim != 128)) return RFX_ERR_UNSUPPORTED;
+    if (nq <= 0 || nkv <= 0 || (nkv_in != 0 && nkv_in != nkv)) return RFX_ERR_BAD_ARG;
+    const int N = (nq + 2 * nkv_in) * head_dim;
+    if (int c = check_common(x, W, R, N, K)) return c;
+    if (!row_pos || !row_slot || !q_out || (nkv_in && (!k_pages || !v_pages || !page_table))) return RFX_ERR_BAD_ARG;
+    Fuse f{};
+    const bool pro = ssq_in != nullptr;
+    if (pro) {
+        if (n_part_in <= 0 || norm_h <= 0) return RFX_ERR_BAD_ARG;
+        f.ssq_in = ssq_in;
+        f.n_part_in = n_part_in;
+        f.inv_h = 1.0f / (float)norm_h;
+        f.eps = eps;
+    }
+    f.q_w = q_w;
+    f.k_w = k_w;
+    f.qk_eps = qk_eps;
+    f.qk_offset = qk_offset;
+    f.rope_denom = rope_denom;
+    f.magnitude = magnitude;
+    f.row_pos = row_pos;
+    f.row_slot = row_slot;
+    f.q_out = (__nv_bfloat16*)q_out;
+    f.k_pages = (__nv_bfloat16*)k_pages;
+    f.v_pages = (__nv_bfloat16*)v_pages;
+    f.cache = rfx::PagedKV{page_table, max_pages, page_size, nkv, head_dim};
+    f.nq = nq;
+    f.nkv_in = nkv_in;
+    f.head_dim = head_dim;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (pro) return dispatch<__nv_bfloat16, 3, true>(x, W, q_out, R, N, K, 0, f, nullptr, err, s);
+    return dispatch<__nv_bfloat16, 3, false>(x, W, q_out, R, N, K, 0, f, nullptr, err, s);
 }
 
 // An upper bound of the partials a residual product of N weight rows writes per row.

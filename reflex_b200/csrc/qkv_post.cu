@@ -13,8 +13,9 @@
 // (src/model/config.rs:15-28).  cos and sin are multiplied by `magnitude` (1 for
 // the plain encoding; a frequency-scaled encoding's attention factor,
 // src/model/kernels.rs:3086-3129).  Elements >= rd stay.  v is stored as
-// projected.  All arithmetic is 32-bit; the angle is a 32-bit division, its sine
-// and cosine come from `exact_sincosf`, whose bits a host program can repeat.
+// projected.  All arithmetic is 32-bit; the angle is a 32-bit division; in the
+// 32-bit form its sine and cosine come from `exact_sincosf`, whose bits a host
+// program can repeat, in the bfloat16 forms from sincosf.
 //
 // Orders of the 32-bit form (32-bit in, 32-bit out: always the general kernel),
 // which a host mirror repeats: a head's sum of squares as a fused multiply-add
@@ -33,6 +34,17 @@ namespace {
 using namespace rfx;
 
 constexpr int MAX_PER_LANE = 16;  // head_dim <= 512
+
+// Sine and cosine of a row's angle.  The 32-bit form takes the routine whose bits
+// a host program can repeat (its range reduction runs in double precision, which
+// this GPU executes at a small fraction of its 32-bit rate); a result that is
+// rounded to bfloat16 takes the library's 32-bit routine, as every bfloat16
+// kernel that rotates does, so that prefill and decode rotate alike.
+template <typename TO>
+__device__ __forceinline__ void row_sincos(float theta, float* sv, float* cv) {
+    if constexpr (sizeof(TO) == 2) sincosf(theta, sv, cv);
+    else exact_sincosf(theta, sv, cv);
+}
 
 template <typename T, int N>
 struct alignas(sizeof(T) * N <= 16 ? sizeof(T) * N : 16) Pack {
@@ -122,7 +134,7 @@ qkv_post_wide_kernel(const TI* __restrict__ qkv, int row_stride, const float* __
             for (int i = threadIdx.x; i < half; i += blockDim.x) {
                 const float theta = (float)pos / rope_denom[i];
                 float sv, cv;
-                exact_sincosf(theta, &sv, &cv);
+                row_sincos<TO>(theta, &sv, &cv);
                 sn_tab[i] = sv * magnitude;
                 cs_tab[i] = cv * magnitude;
             }
@@ -275,7 +287,7 @@ qkv_post_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restr
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
             const float theta = (float)pos / rope_denom[i];
             float sv, cv;
-            exact_sincosf(theta, &sv, &cv);
+            row_sincos<TO>(theta, &sv, &cv);
             sn_tab[i] = sv * magnitude;
             cs_tab[i] = cv * magnitude;
         }

@@ -12,8 +12,10 @@ a time, so they share their intermediate buffers and a batch that shrinks
 through many sizes does not grow the device memory with every size.  Their
 results therefore live in shared storage too, and `run` hands out a copy unless
 the caller asks to borrow the graph's own buffer.  Only the engine's very first
-decode step runs eagerly (it sizes the lazily made buffers); every later
-(size, bucket) captures at its first use.  The engine keeps at most
+decode step runs eagerly (it sizes the lazily made buffers), and the first step
+of a batch size above what the library's own products take (it lets the
+vendor's product load its kernel for that shape); every other (size, bucket)
+captures at its first use.  The engine keeps at most
 `Engine.max_graphs` graphs and drops the least recently used.
 """
 
@@ -54,14 +56,20 @@ class DecodeGraph:
         if self.graph is None:
             # the first decode steps of a batch size run eagerly: they size every
             # lazily allocated buffer; later graphs of that size capture at once
-            if eng._eager_decodes < self.WARMUP:
+            from .. import ops
+
+            # Beyond the rows the library's own products take, the step calls the
+            # vendor's matrix product, which picks (and loads) a kernel per shape the
+            # first time it sees it, and loading inside a capture invalidates it: such
+            # a batch size runs eagerly once before it is captured.
+            first_of_size = self.n > ops.GEMV_MAX_ROWS and self.n not in eng._eager_sizes
+            if eng._eager_decodes < self.WARMUP or first_of_size:
                 eng._eager_decodes += 1
+                eng._eager_sizes.add(self.n)
                 return eng.model.forward(batch, eng.cache)
             # capture: the eager call above has already sized every lazy buffer
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            from .. import ops
-
             before = ops.launch_count()
             with torch.cuda.graph(g, pool=eng.graph_pool()):
                 self.logits = eng.model.forward(batch, eng.cache)

@@ -53,6 +53,7 @@ class Engine:
         self._graphs: Dict[Tuple[int, int], "object"] = {}  # insertion order = least recently used first
         self._graph_pool = None
         self._eager_decodes = 0  # eager decode steps run so far
+        self._eager_sizes: set = set()  # batch sizes that have run eagerly once
         self.steps_run = 0
         on_gpu = torch.device(self.device).type == "cuda"
         self.staging = Staging(self.device) if on_gpu else None

@@ -404,6 +404,66 @@ def qkv_post(qkv: torch.Tensor, q_weight, k_weight, eps: float, weight_offset: f
     return q
 
 
+def qkv_fused_takes(x, head_dim: int, rotation, qkv_weight: torch.Tensor) -> bool:
+    """Whether `qkv_fused` takes this call: a few bfloat16 rows (decode), a head
+    size of 64 or 128, and a rotation, if any, over the whole head in half-split
+    pairs."""
+    rows, K = x.shape
+    if not FUSE_QKV or x.dtype != torch.bfloat16 or qkv_weight.dtype != torch.bfloat16:
+        return False
+    if rows > min(GEMV_MAX_ROWS, FUSE_QKV_ROWS) or K % 8 or head_dim not in (64, 128):
+        return False
+    if rotation is not None and (rotation.pairing != "half" or rotation.rotary_dim != head_dim
+                                 or rotation.denominators is None):
+        return False
+    return True
+
+
+def qkv_fused(x, qkv_weight: torch.Tensor, q_weight, k_weight, eps: float, weight_offset: float,
+              rotation, row_pos: torch.Tensor, row_slot: torch.Tensor, k_pages, v_pages,
+              page_table: torch.Tensor, page_size: int, nq: int, nkv: int, head_dim: int,
+              writes_cache: bool) -> torch.Tensor:
+    """The q/k/v product of a decode step and what follows it, in one launch:
+    per-head q/k norm, rotary encoding, q out (bfloat16 [R, nq * head_dim]), k and
+    v into the cache.  `x`: bfloat16 rows or a `NormedInput`.  What `linear` +
+    `qkv_post` give, without the launch between them and without the 32-bit
+    q/k/v rows in memory."""
+    normed = x if isinstance(x, NormedInput) else None
+    if normed is not None:
+        x = normed.hb
+    R, K = x.shape
+    nkv_in = nkv if writes_cache else 0
+    if qkv_weight.shape[0] != (nq + 2 * nkv_in) * head_dim or qkv_weight.shape[1] != K:
+        raise InvalidInput("qkv_fused: the weight's shape does not match the head counts")
+    _chk(x, "x", torch.bfloat16)
+    _chk(qkv_weight, "qkv_weight", torch.bfloat16)
+    denom = None if rotation is None else rotation.denominators
+    q = _new((R, nq * head_dim), torch.bfloat16, x.device)
+    st = native.lib().rfx_gemm_bf16_tc_qkv(
+        x.data_ptr(), qkv_weight.data_ptr(), R, K,
+        normed.ssq.data_ptr() if normed is not None else 0, normed.n_part if normed is not None else 0,
+        normed.size if normed is not None else 0, float(normed.eps) if normed is not None else 0.0,
+        _chk(q_weight, "q_norm", torch.float32), _chk(k_weight, "k_norm", torch.float32), float(eps),
+        float(weight_offset), _chk(denom, "rope_denom", torch.float32),
+        float(rotation.magnitude) if rotation is not None else 1.0,
+        _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32), q.data_ptr(),
+        _chk(k_pages, "k_pages", torch.bfloat16), _chk(v_pages, "v_pages", torch.bfloat16),
+        _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size, nq, nkv_in, nkv,
+        head_dim, device_error_word(x.device).data_ptr(), _stream())
+    native.check(st, f"gemm_bf16_tc_qkv (R={R}, K={K}, head_dim={head_dim})")
+    return q
+
+
+FUSE_QKV = _env_flag("REFLEX_B200_FUSE_QKV", True)
+# Up to this many rows the fused form is the faster one (measured on a B200 at
+# Qwen3-8B sizes: 2.3 % of a step at batch 1, 0.7 % at batch 8, level at 16, behind
+# from 32 on).  With more rows the attention kernel that follows is the
+# step's largest after the feed-forward, and it gains more from starting early,
+# beside the light `qkv_post` launch, and fetching its cached pages meanwhile,
+# than the step gains from one launch less.
+FUSE_QKV_ROWS = _env_int("REFLEX_B200_FUSE_QKV_ROWS", 8, 0, 64)
+
+
 def attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                     page_table: torch.Tensor, page_size: int, row_pos: torch.Tensor,
                     row_slot: torch.Tensor, nq: int, nkv: int, head_dim: int,
@@ -444,24 +504,31 @@ def sm_count() -> int:
 
 def decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int = 64) -> int:
     """Key-range splits of the decode kernel for rows whose longest context has
-    `max_pages` pages.  A split costs a second kernel (the combine, whose work
-    grows with the splits) and buys parallelism; fitted to step times on a B200
-    at batches of 1 to 64 and contexts of 512 to 16,000: about 4 us fixed per
-    launch, 0.8 us per page a CTA walks plus 1.5 us per CTA, CTAs in whole waves
-    of two per SM; for the merge 2 us + 0.1 us a split inside a cluster (up to 8
-    splits), 3 us + 0.25 us a split through the combine kernel.  The
-    smallest estimate wins."""
+    `max_pages` pages.  A split buys parallelism and costs a CTA's fixed work
+    (query load, the warps' merge, the exchange of partials) once more.  Fitted
+    to kernel times on a B200 at batches of 1 to 64 and contexts of 640 to
+    16,384 (within 10 % of all of them): two CTAs fit an SM; while all CTAs are
+    resident together a CTA walks its pages at 1.0 us a page (latency); beyond
+    that the SMs are busy throughout and a page costs its share of the memory
+    bandwidth, 1.43 us per CTA slot; a CTA's fixed work is 4 to 5 us; 4 us for
+    the launch; the merge 1 us + 0.1 us a split inside a cluster (up to 8
+    splits), 3 us + 0.25 us a split through the combine kernel.  The smallest
+    estimate wins."""
     forced = _env_int("REFLEX_B200_DECODE_SPLITS", 0, 0, 64)  # tuning aid
     if forced > 0:
         return forced
     ctas = n_rows * nkv * ((nq // nkv + 7) // 8)
+    slots = 2 * sm_count()
     best, best_cost = 1, None
     for s in (1, 2, 4, 8, 16, 32, 64):
         if s > max(1, max_pages):
             break
-        waves = -(-ctas * s // (2 * sm_count()))
-        merge = 0.0 if s == 1 else (2.0 + 0.1 * s if s <= 8 else 3.0 + 0.25 * s)
-        cost = 4.0 + (-(-max_pages // s) * 0.8 + 1.5) * waves + merge
+        n = ctas * s
+        per_split = -(-max_pages // s)
+        resident = per_split * 1.0 + 5.0
+        streaming = n * (per_split * 1.43 + 4.0) / slots
+        merge = 0.0 if s == 1 else (1.0 + 0.1 * s if s <= 8 else 3.0 + 0.25 * s)
+        cost = 4.0 + (resident if n <= slots else max(resident, streaming)) + merge
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best

@@ -95,16 +95,25 @@ class GQAttention:
         kv = ctx.kv  # the cache entry's view
         batch = ctx.batch
         w = self.qkv if ctx.writes_cache else self.q_only
-        qkv = ops.linear(x, w, out_dtype=torch.float32 if x.shape[0] <= ops.GEMV_MAX_ROWS else None)
-        ops.prof_mark("qkv_gemm")
         rotation = None if self.position is None else self.position.rotation()
         norm = s.qk_norm
-        q = ops.qkv_post(
-            qkv, self.q_norm, self.k_norm, norm.eps if norm else 0.0,
-            norm.weight_offset if norm else 0.0, rotation, batch.row_pos, batch.row_slot,
-            kv.k_pages, kv.v_pages, kv.page_table, kv.page_size, s.num_heads, s.num_kv_heads,
-            s.head_dim, ctx.writes_cache, self.dtype)
-        ops.prof_mark("norm_rope")
+        if ops.qkv_fused_takes(x, s.head_dim, rotation, w):
+            # a few rows: norms, rotation and the cache write are the product's epilogue
+            q = ops.qkv_fused(
+                x, w, self.q_norm, self.k_norm, norm.eps if norm else 0.0,
+                norm.weight_offset if norm else 0.0, rotation, batch.row_pos, batch.row_slot,
+                kv.k_pages, kv.v_pages, kv.page_table, kv.page_size, s.num_heads, s.num_kv_heads,
+                s.head_dim, ctx.writes_cache)
+            ops.prof_mark("qkv_gemm")
+        else:
+            qkv = ops.linear(x, w, out_dtype=torch.float32 if x.shape[0] <= ops.GEMV_MAX_ROWS else None)
+            ops.prof_mark("qkv_gemm")
+            q = ops.qkv_post(
+                qkv, self.q_norm, self.k_norm, norm.eps if norm else 0.0,
+                norm.weight_offset if norm else 0.0, rotation, batch.row_pos, batch.row_slot,
+                kv.k_pages, kv.v_pages, kv.page_table, kv.page_size, s.num_heads, s.num_kv_heads,
+                s.head_dim, ctx.writes_cache, self.dtype)
+            ops.prof_mark("norm_rope")
         attn = ops.attention(q, kv.k_pages, kv.v_pages, kv.page_table, kv.page_size, batch,
                              s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale)
         ops.prof_mark("attn")

@@ -687,3 +687,88 @@ def test_gather_dot_reads_the_chosen_rows(P, K, V):
 
     with pytest.raises(CudaError):
         ops().check_device_errors(DEV)
+
+
+@pytest.mark.parametrize("nq,nkv,d,K,R,writes,norm,rope", [
+    (32, 8, 128, 4096, 8, True, True, True), (32, 8, 128, 4096, 1, True, True, True),
+    (32, 8, 128, 4096, 64, True, True, True), (40, 8, 128, 1024, 33, True, True, True),
+    (6, 2, 64, 96, 5, True, True, True), (3, 1, 64, 200, 17, True, True, True),
+    (4, 4, 128, 64, 3, False, True, True), (5, 1, 64, 320, 9, True, False, True),
+    (2, 2, 128, 128, 16, True, True, False)])
+def test_the_qkv_product_finished_per_head_equals_product_then_qkv_post(nq, nkv, d, K, R, writes, norm, rope):
+    """The decode step's q/k/v product with the per-head norms, the rotation and
+    the cache write as its epilogue, against the product followed by `qkv_post`
+    (the same formulas, sums in another order) and against the plain formulas;
+    with and without a norm folded into its prologue; untouched cache rows stay."""
+    from reflex_b200.parts import Rotation
+
+    g = torch.Generator().manual_seed(nq * 7 + d + R)
+    nkv_in = nkv if writes else 0
+    N = (nq + 2 * nkv_in) * d
+    x = torch.randn(R, K, generator=g).bfloat16()
+    W = (torch.randn(N, K, generator=g) * (2.0 / math.sqrt(K))).bfloat16()
+    qw = (1 + 0.1 * torch.randn(d, generator=g)) if norm else None
+    kw = (1 + 0.1 * torch.randn(d, generator=g)) if norm else None
+    theta, eps = 1e6, 1e-6
+    denom = torch.pow(torch.tensor(theta, dtype=torch.float64), torch.arange(d // 2, dtype=torch.float64) * 2 / d)
+    rot = Rotation(denom.float().to(DEV), d) if rope else None
+    positions = [(37 * i + 5) % 700 for i in range(R)]
+    n_pages = 700 // 64 + 1
+    slots = list(range(R))
+    table = (torch.arange(R * n_pages, dtype=torch.int32).reshape(R, n_pages))
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    dev = lambda t: None if t is None else t.to(DEV)
+
+    def run(fused, xin):
+        kp = torch.full((R * n_pages, nkv, 64, d), 7.0, dtype=torch.bfloat16, device=DEV)
+        vp = torch.full((R * n_pages, nkv, 64, d), 7.0, dtype=torch.bfloat16, device=DEV)
+        args = (dev(qw), dev(kw), eps, 0.0, rot, i32(positions), i32(slots), kp, vp, table.to(DEV), 64, nq, nkv, d, writes)
+        if fused:
+            assert ops().qkv_fused_takes(xin, d, rot, W) == (R <= ops().FUSE_QKV_ROWS)  # the engine's rule
+            q = ops().qkv_fused(xin, W.to(DEV), *args)  # the kernel itself takes up to 64 rows
+        else:
+            qkv = ops().linear(xin, W.to(DEV), out_dtype=torch.float32)
+            q = ops().qkv_post(qkv, *args, torch.bfloat16)
+        ops().check_device_errors(DEV)
+        return q.float().cpu(), kp.float().cpu(), vp.float().cpu()
+
+    q1, k1, v1 = run(True, x.to(DEV))
+    q0, k0, v0 = run(False, x.to(DEV))
+    scale = float(q0.abs().max())
+    assert float((q1 - q0).abs().max()) < 1e-2 * scale
+    assert float((k1 - k0).abs().max()) < 1e-2 * max(scale, 7.0) and float((v1 - v0).abs().max()) < 1e-2 * 7.0
+    # against the plain formulas
+    y = x.double().numpy() @ W.double().numpy().T
+    pos = np.array(positions)
+    qr = y[:, : nq * d].reshape(R, nq, d)
+    if norm:
+        qr = pm.rms_norm(qr, qw.double().numpy(), eps)
+    if rope:
+        qr = pm.rope_neox(qr, pos, theta, d)
+    assert relerr(q1.reshape(R, nq, d), qr) < 8e-3
+    if writes:
+        kr = y[:, nq * d:(nq + nkv) * d].reshape(R, nkv, d)
+        if norm:
+            kr = pm.rms_norm(kr, kw.double().numpy(), eps)
+        if rope:
+            kr = pm.rope_neox(kr, pos, theta, d)
+        vr = y[:, (nq + nkv) * d:].reshape(R, nkv, d)
+        touched = torch.zeros(R * n_pages, 64, dtype=torch.bool)
+        for i, p in enumerate(positions):
+            page = int(table[i, p // 64])
+            assert relerr(k1[page, :, p % 64], kr[i]) < 8e-3 and relerr(v1[page, :, p % 64], vr[i]) < 8e-3
+            touched[page, p % 64] = True
+        rest = ~touched[:, None, :, None].expand(R * n_pages, nkv, 64, d)
+        assert bool((k1[rest] == 7.0).all()) and bool((v1[rest] == 7.0).all())
+    # with the input norm folded in: rows that await their factor, from the product before
+    if K % 8 == 0 and K >= 64:
+        xr = torch.randn(R, 64, generator=g).bfloat16()
+        wr = (torch.randn(K, 64, generator=g) * 0.1).bfloat16()
+        h = torch.randn(R, K, generator=g) * 2
+        nw = 1 + 0.1 * torch.randn(K, generator=g)
+        outs = []
+        for fused in (True, False):
+            ni = ops().gemm_tc_residual(xr.to(DEV), wr.to(DEV), h.to(DEV).clone(), nw.to(DEV), 0.0, 1e-5)
+            outs.append(run(fused, ni))
+        assert float((outs[0][0] - outs[1][0]).abs().max()) < 1e-2 * float(outs[1][0].abs().max())
+        assert float((outs[0][1] - outs[1][1]).abs().max()) < 1e-2 * 7.0

@@ -841,7 +841,7 @@ struct Cut {
     int bm, tiles, ks;
 };
 
-Cut choose_cut(int N, int r_tiles, int num_kb, int ks_req, bool whole_tiles) {
+Cut choose_cut(int N, int r_tiles, int num_kb, int ks_req, bool whole_tiles, int bn) {
     if (ks_req > 0) return Cut{BM, (N + BM - 1) / BM, ks_req};
     if (whole_tiles) {  // tiles of exactly 128 rows; K split while CTAs are few
         const int t = (N + BM - 1) / BM;
@@ -873,7 +873,10 @@ Cut choose_cut(int N, int r_tiles, int num_kb, int ks_req, bool whole_tiles) {
     const int tiles = (N + BM - 1) / BM;
     // Between one and two 128-row tiles per SM the SMs that get two CTAs finish
     // late while the rest idle: cut lower tiles instead, two per SM, equal work.
-    if (r_tiles == 1 && tiles > sms && tiles < 2 * sms && knobs().even) {
+    // (Not with 64 activation rows: a lower tile brings the same activation tile
+    // for fewer weight rows, and what an SM can take in is the limit there; measured
+    // 2 % of a batch-64 step.)
+    if (r_tiles == 1 && tiles > sms && tiles < 2 * sms && knobs().even && bn < 64) {
         int bm = (N + 2 * sms - 1) / (2 * sms);
         bm = (bm + 1) & ~1;
         if (bm >= 32 && bm <= BM) return Cut{bm, (N + bm - 1) / bm, 1};
@@ -889,7 +892,7 @@ int launch(const void* x, const void* W, void* y, int R, int N, int K, int kspli
     using S = Shape<BN>;
     const int r_tiles = (R + BN - 1) / BN;
     const int num_kb = (K + BK - 1) / BK;
-    Cut cut = choose_cut(N, r_tiles, num_kb, ksplit_req, EPI == 3);
+    Cut cut = choose_cut(N, r_tiles, num_kb, ksplit_req, EPI == 3, BN);
     if (EPI == 3 && (r_tiles != 1 || BN % cut.ks)) return RFX_ERR_UNSUPPORTED;
     if (EPI == 1 && (cut.bm & 1)) {  // pairs must not straddle tiles
         cut.bm += 1;

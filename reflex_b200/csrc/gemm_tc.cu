@@ -155,7 +155,7 @@ __device__ __forceinline__ void finish_head(float* hv, bool rotate_it, const flo
 template <int BN, bool PRO>
 __device__ __forceinline__ void head_epilogue(float* recv, float* rot, uint32_t tmem_d, uint64_t* tmem_full_bar,
                                               bool have, int ksplit, int z, int r0, int R, const Fuse& f,
-                                              const float* rstd_s, int* err) {
+                                              const float* rstd_s, int* err, int trace_id) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q4 = warp & 3, m = q4 * 32 + lane, et = threadIdx.x - 64, ew = warp - 2;
     const int D = f.head_dim, half = D / 2;
@@ -210,6 +210,7 @@ __device__ __forceinline__ void head_epilogue(float* recv, float* rot, uint32_t 
         have = false;
     }
     tc_fence_after_sync();
+    if (warp == 2 && lane == 0) trace_mark(trace_id, 2);
     // Row m of the tile, for every activation row (column of the accumulator): to
     // the rank that finishes that activation row, slot [this rank][row][m].
     cg::cluster_group cluster = cg::this_cluster();
@@ -439,7 +440,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         float* sq = reinterpret_cast<float*>(tiles);  // [BN][mw] (split K); this CTA's stages are drained by then
         if constexpr (EPI == 3) {
             head_epilogue<BN, PRO>(stage0, stage0 + BN * BM, tmem_d, &tmem_full_bar, nkb > 0, ksplit, z, r0, R,
-                                   fuse, rstd_s, err);
+                                   fuse, rstd_s, err, trace_id);
         } else {
         // Four neighbouring rows of the tile at a time where the sizes allow it
         // (the slices are whole multiples of four and so are the output's rows):

@@ -194,12 +194,12 @@ def test_command_line_smoke_doctor_and_the_top2_probe():
     assert [int(l.split("top1_id=")[1].split()[0]) for l in probes] == ids  # greedy: the top id is the pick
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_trace_run_replays_steps_and_writes_logits(dtype, tmp_path):
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("B", "bfloat16"), ("A", "float32"), ("C", "bfloat16")])
+def test_trace_run_replays_steps_and_writes_logits(name, dtype, tmp_path):
     """bin/trace_run as a subprocess: two requests start together with unequal
     lengths, go on one token a step, the shorter one ends earlier, and a third
-    request then starts in the freed slot (the cache holds two requests)."""
-    name = "B"
+    request then starts in the freed slot (the cache holds two requests).  In
+    32-bit the files hold the host mirror's bits."""
     V = ALL[name]["vocab_size"]
     folder = helpers.model_folder(name, 7, "float32" if dtype == "float32" else "bfloat16")
     a, b, c = (helpers.random_tokens(n, V, 80 + n) for n in (70, 9, 40))
@@ -236,6 +236,13 @@ def test_trace_run_replays_steps_and_writes_logits(dtype, tmp_path):
         assert np.abs(x[1] - rb[5 + i]).max() < tol * scale
     assert not os.path.exists(os.path.join(out_dir, "5.f32"))  # nothing was wanted
     assert np.abs(load(6, 1)[0] - rc[39]).max() < tol * scale
+    if dtype == "float32":
+        import fp32_mirror
+
+        cfg, w = pm.read_model(folder)
+        ma, mc = fp32_mirror.forward(cfg, w, a), fp32_mirror.forward(cfg, w, c)
+        assert np.array_equal(load(0, 62)[:60], ma[:60]) and np.array_equal(load(3, 2)[0], ma[62])
+        assert np.array_equal(load(6, 1)[0], mc[39])
 
 
 def test_diagnostics_print_a_decode_steps_timeline():

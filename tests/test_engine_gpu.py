@@ -13,12 +13,14 @@ float32 runs sharpen every layer by 3 (scores spread by about 9), bfloat16
 runs sharpen only the last layer, since bfloat16's 8 significant bits start
 from 3e-3 per matrix product.
 
-Bounds, with what was measured on a B200 beside them:
-  float32, flat attention         3e-6    (3e-7 .. 7e-7)
-  float32, every layer sharp      1e-3    (1e-5 .. 1.4e-4, growing with the
-      position: the 32-bit rotation angle is off by up to position * 2^-24)
-  bfloat16, flat attention        1.5e-2  (2e-3 .. 7e-3)
-  bfloat16, last layer sharp      4e-2    (see the runs)
+Bounds, with what was measured on a B200 beside them (configurations A to D):
+  float32, flat attention         3e-6    (3.3e-7 .. 6.8e-7)
+  float32, every layer sharp      1e-3    (4.8e-6 .. 2.6e-5 in unequal batches,
+      1.9e-4 at 300 positions: the 32-bit rotation angle is off by up to
+      position * 2^-24)
+  bfloat16, flat attention        1.5e-2  (2.0e-3 .. 6.2e-3)
+  bfloat16, last layer sharp      4e-2    (1.8e-2 .. 2.2e-2 in unequal batches,
+      1.9e-2 at 300 positions)
 A key read from a wrong place moves a sharpened model's logits by tenths.  On
 the float32 path the logits must moreover be bit-equal however the tokens are
 cut into steps or batched: every kernel there reduces in an order that does not

@@ -4,6 +4,7 @@ mixer with state of its own that is defined here, registered, built and stepped
 without a change to the framework's files."""
 
 import math
+import os
 
 import numpy as np
 import pytest
@@ -144,15 +145,12 @@ def test_run_order_is_data_a_layer_twice_and_a_shared_cache(dtype):
     assert helpers.rel_err(got, ref) < (2e-5 if dtype == torch.float32 else 1.5e-2)
 
 
-def _toy_ema_model(dtype):
-    """Two layers of a toy mixer (an exponential moving average over a
-    sequence's tokens: state [hidden] per sequence, fixed size, zero at the
-    start, updated token by token) with the library's SwiGLU and norms."""
+def _toy_ema_class():
+    """Registers (once more, harmlessly) and returns a toy mixer: an exponential
+    moving average over a sequence's tokens: state [hidden] per sequence, fixed
+    size, zero at the start, updated token by token."""
     from reflex_b200.cache import StateSpec
-    from reflex_b200.config.spec import FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec
-    from reflex_b200.engine import CausalLM, expected_tensors
     from reflex_b200.parts import TensorInfo, register_mixer
-    from reflex_b200.weights import random_tensors
 
     @register_mixer("toy_ema")
     class ToyEma:
@@ -195,6 +193,16 @@ def _toy_ema_model(dtype):
                 raise RuntimeError("toy failure after the state was updated")
             return out @ self.mix.T
 
+    return ToyEma
+
+
+def _toy_ema_model(dtype):
+    """Two layers of the toy mixer with the library's SwiGLU and norms."""
+    from reflex_b200.config.spec import FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec
+    from reflex_b200.engine import CausalLM, expected_tensors
+    from reflex_b200.weights import random_tensors
+
+    ToyEma = _toy_ema_class()
     H, V = 40, 97
     mixer = MixerSpec("toy_ema", hidden_size=H, names=(("mix", "ema.mix.weight"),), params=(("decay", 0.75),))
     ffn = FeedForwardSpec("swiglu", H, 56, names=(("gate_proj", "ff.g"), ("up_proj", "ff.u"), ("down_proj", "ff.d")))
@@ -496,3 +504,148 @@ def test_toy_parts_chosen_layer_by_layer(dtype):
             best = pm.argmax_last(logits)
             assert tok == best or logits[best] - logits[tok] <= 2 * tol * np.abs(logits).max()
             seq.append(tok)
+
+
+@pytest.mark.parametrize("weights", ["f32", "bf16"])
+def test_a_toy_architecture_from_config_json_to_generation(weights, tmp_path):
+    """A whole architecture added from outside the framework: a typed config
+    read from its own config.json keys, a builder that turns it into a
+    `ModelSpec` (layers that alternate the toy state mixer and attention, a run
+    order that names a layer twice), and a registry entry.  The framework's
+    files stay as they are: the random-weights mode writes its model folder, the
+    loader checks and binds it by tensor name, the cache gives it a state group
+    beside a key/value group, and step, generation and candidate scoring run
+    it, in both precisions, against a plain forward written here."""
+    from dataclasses import dataclass
+
+    import reflex_b200
+    from reflex_b200 import CheckpointError
+    from reflex_b200 import CheckpointError as ConfigError  # a malformed config.json is a checkpoint error
+    from reflex_b200.config import RunEntry, register_architecture
+    from reflex_b200.config.spec import FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec
+    from reflex_b200.weights import SafetensorsFile, write_random_model, write_safetensors
+
+    _toy_ema_class()
+
+    @dataclass
+    class ToyConfig:
+        vocab: int
+        width: int
+        kinds: tuple  # "ema" | "attention" per layer
+        heads: int
+        kv_heads: int
+        head_size: int
+        ff: int
+        decay: float
+        eps: float
+        theta: float
+        repeat_last: bool
+
+        @classmethod
+        def from_dict(cls, d):
+            missing = [k for k in ("vocab", "width", "kinds", "ff") if k not in d]
+            if missing:
+                raise ConfigError(f"toy config.json lacks {missing}")
+            return cls(d["vocab"], d["width"], tuple(d["kinds"]), d.get("heads", 2), d.get("kv_heads", 1),
+                       d.get("head_size", 64), d["ff"], d.get("decay", 0.5), d.get("eps", 1e-5),
+                       d.get("theta", 1e4), bool(d.get("repeat_last", False)))
+
+        def to_dict(self):
+            return {"architectures": ["ToyHybridForCausalLM"], "vocab": self.vocab, "width": self.width,
+                    "kinds": list(self.kinds), "heads": self.heads, "kv_heads": self.kv_heads,
+                    "head_size": self.head_size, "ff": self.ff, "decay": self.decay, "eps": self.eps,
+                    "theta": self.theta, "repeat_last": self.repeat_last}
+
+    def build(c: ToyConfig) -> ModelSpec:
+        norm = NormSpec("rmsnorm", c.width, c.eps)
+        ffn = FeedForwardSpec("swiglu", c.width, c.ff, names=(("gate_proj", "ff.gate"), ("up_proj", "ff.up"), ("down_proj", "ff.down")))
+        layers = []
+        for i, kind in enumerate(c.kinds):
+            if kind == "ema":
+                mixer = MixerSpec("toy_ema", hidden_size=c.width, names=(("mix", "ema.mix"),), params=(("decay", c.decay),))
+            else:
+                mixer = MixerSpec("gqa_attention", hidden_size=c.width, num_heads=c.heads, num_kv_heads=c.kv_heads,
+                                  head_dim=c.head_size, scale=c.head_size ** -0.5,
+                                  qk_norm=NormSpec("rmsnorm", c.head_size, c.eps),
+                                  position=PositionSpec("rope_neox", c.head_size, c.head_size, c.theta),
+                                  names=(("q_proj", "att.q"), ("k_proj", "att.k"), ("v_proj", "att.v"), ("o_proj", "att.o"),
+                                         ("q_norm", "att.qn"), ("k_norm", "att.kn")))
+            layers.append(LayerSpec("prenorm", f"toy.{i}.", mixer, ffn, norm, norm,
+                                    names=(("mixer_norm", "n1"), ("feed_forward_norm", "n2"))))
+        order = [RunEntry(i, i) for i in range(len(layers))]
+        if c.repeat_last:  # the last layer once more, with its own cache entry: weights shared
+            order.append(RunEntry(len(layers) - 1, len(layers)))
+        return ModelSpec("toy_hybrid", c.vocab, c.width, layers, norm, tie_word_embeddings=False, max_positions=512,
+                         embedding_name="toy.emb", final_norm_name="toy.norm", head_name="toy.head", run_order=order,
+                         eos_token_ids=())
+
+    register_architecture(("ToyHybridForCausalLM", "toy_hybrid"), ToyConfig.from_dict, build)
+
+    cfg = {"architectures": ["ToyHybridForCausalLM"], "vocab": 211, "width": 72, "kinds": ["ema", "attention", "ema", "attention"],
+           "heads": 2, "kv_heads": 1, "head_size": 64, "ff": 104, "decay": 0.6, "repeat_last": True}
+    with pytest.raises(ConfigError):
+        reflex_b200.config.spec_from_config_dict({"architectures": ["ToyHybridForCausalLM"], "vocab": 5})
+    folder = str(tmp_path / "toy")
+    write_random_model(cfg, 5, folder, "float32" if weights == "f32" else "bfloat16")
+    model = reflex_b200.Model.load(folder, weights=weights, max_tokens=2048)
+    eng = model.engine
+    assert len(eng.cache.state_groups) == 1 and len(eng.cache.kv_groups) == 1
+    assert eng.use_graphs == (weights == "bf16")
+
+    f = SafetensorsFile(os.path.join(folder, "model.safetensors"))
+    w = {k: f.tensor(k).double().numpy() for k in f.keys()}
+    f.close()
+    H, d, nq, nkv = 72, 64, 2, 1
+
+    def plain(tokens):
+        T = len(tokens)
+        pos = np.arange(T)
+        h = w["toy.emb"][np.array(tokens)]
+        for li in (0, 1, 2, 3, 3):
+            p = f"toy.{li}."
+            x = pm.rms_norm(h, w[p + "n1"], 1e-5)
+            if cfg["kinds"][li] == "ema":
+                state, outs = np.zeros(H), []
+                for t in range(T):
+                    state = 0.6 * state + 0.4 * x[t]
+                    outs.append(state)
+                h = h + np.stack(outs) @ w[p + "ema.mix"].T
+            else:
+                q = pm.rms_norm((x @ w[p + "att.q"].T).reshape(T, nq, d), w[p + "att.qn"], 1e-5)
+                k = pm.rms_norm((x @ w[p + "att.k"].T).reshape(T, nkv, d), w[p + "att.kn"], 1e-5)
+                v = (x @ w[p + "att.v"].T).reshape(T, nkv, d)
+                q, k = pm.rope_neox(q, pos, 1e4, d), pm.rope_neox(k, pos, 1e4, d)
+                h = h + pm.causal_attention(q, k, v, d ** -0.5, None).reshape(T, nq * d) @ w[p + "att.o"].T
+            x = pm.rms_norm(h, w[p + "n2"], 1e-5)
+            h = h + pm.swiglu(x, w[p + "ff.gate"], w[p + "ff.up"], w[p + "ff.down"])
+        return pm.rms_norm(h, w["toy.norm"], 1e-5) @ w["toy.head"].T
+
+    tol = 1e-5 if weights == "f32" else 1.5e-2
+    reqs = [helpers.random_tokens(n, 211, 40 + n) for n in (70, 3, 33, 9)]
+    got = helpers.run_batches(eng, reqs, 2, [20, 3, 1])
+    for r, g in zip(reqs, got):
+        assert helpers.rel_err(g, plain(r)) < tol
+    assert eng.cache.slots.held_count == 0
+    if weights == "bf16":
+        assert any(g.graph is not None for g in eng._graphs.values())
+    outs = model.generate([reqs[1], reqs[3]], 8)
+    for p, o in zip((reqs[1], reqs[3]), outs):
+        seq = list(p)
+        for tok in o:
+            logits = plain(seq)[-1]
+            best = pm.argmax_last(logits)
+            assert tok == best or logits[best] - logits[tok] <= 2 * tol * np.abs(logits).max()
+            seq.append(tok)
+    # candidate scoring teacher-forces a continuation: the state mixer sees its tokens in order
+    res = model.system1_evaluate(reqs[3], [[5, 6, 7], [100]])
+    full = plain(reqs[3] + [5, 6])
+    want = float(full[len(reqs[3]) - 1, 5] + full[len(reqs[3]), 6] + full[len(reqs[3]) + 1, 7])
+    assert abs(res.results[0].score - want) < 3 * tol * np.abs(full).max()
+    # the loader's one error still names what is wrong with this architecture's checkpoint
+    f = SafetensorsFile(os.path.join(folder, "model.safetensors"))
+    tensors = [(k, f.tensor(k).clone()) for k in f.keys() if k != "toy.1.att.qn"] + [("toy.extra", torch.zeros(2))]
+    f.close()
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
+    with pytest.raises(CheckpointError) as e:
+        reflex_b200.Model.load(folder, weights=weights)
+    assert "toy.1.att.qn" in str(e.value) and "toy.extra" in str(e.value)

@@ -823,12 +823,13 @@ int env_int(const char* name, int dflt) {
 
 // Tuning aids, read from the environment once, at the first product.
 struct Knobs {
-    int cps, even, smem_kb, stages, smem_cap_kb, l2pf_mb;
+    int cps, even, smem_kb, stages, smem_cap_kb, l2pf_mb, max_cta_pct;
 };
 const Knobs& knobs() {
     static const Knobs k = {env_int("REFLEX_B200_GEMM_CPS", 0),      env_int("REFLEX_B200_GEMM_EVEN", 1),
                             env_int("REFLEX_B200_GEMM_SMEM_KB", 110), env_int("REFLEX_B200_GEMM_STAGES", 0),
-                            env_int("REFLEX_B200_GEMM_SMEM_CAP_KB", 112), env_int("REFLEX_B200_GEMM_L2PF_MB", 0)};
+                            env_int("REFLEX_B200_GEMM_SMEM_CAP_KB", 112), env_int("REFLEX_B200_GEMM_L2PF_MB", 0),
+                            env_int("REFLEX_B200_GEMM_MAX_CTA_PCT", 200)};
     return k;
 }
 
@@ -883,7 +884,8 @@ Cut choose_cut(int N, int r_tiles, int num_kb, int ks_req, bool whole_tiles, int
         if (bm >= 32 && bm <= BM) return Cut{bm, (N + bm - 1) / bm, 1};
     }
     int ks = 1;
-    while (ks < 8 && tiles * r_tiles * ks * 2 <= 2 * sms && num_kb >= ks * 4) ks *= 2;
+    const int max_ctas = sms * knobs().max_cta_pct / 100;  // tuning aid: CTAs the K split may make
+    while (ks < 8 && tiles * r_tiles * ks * 2 <= max_ctas && num_kb >= ks * 4) ks *= 2;
     return Cut{BM, tiles, ks};
 }
 

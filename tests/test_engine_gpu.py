@@ -555,3 +555,44 @@ def test_steps_take_their_memory_from_the_engines_workspace(dtype):
     assert eng.workspace.misses == misses
     assert np.array_equal(first, again)
     assert helpers.rel_err(again, helpers.plain_logits(folder, toks)) < tol(dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_context_across_graph_buckets_and_many_key_splits(dtype):
+    """2,000 tokens in one step, then 150 decoded one by one, on the model with
+    sliding layers and a head size of 48: the context passes 32 pages, where the
+    decode graphs' buckets change from steps of four pages to powers of two and
+    a single sequence's keys are split over more CTAs than a cluster holds (the
+    combine kernel merges them).  Every decoded position against the plain
+    implementation; in 32-bit also bit for bit against the host mirror."""
+    cfg = dict(ALL["C"], max_position_embeddings=4096)
+    import shutil
+    import tempfile
+
+    import plain_model
+    from reflex_b200.weights import write_random_model
+
+    folder = tempfile.mkdtemp(prefix="rfx_long_")
+    try:
+        write_random_model(cfg, 21, folder, stored(dtype))
+        eng = helpers.make_engine(folder, dtype, max_tokens=2304)
+        toks = helpers.random_tokens(2150, cfg["vocab_size"], 17)
+        pcfg, w = plain_model.read_model(folder)
+        s = eng.open()
+        out = [eng.step([(s, toks[:2000], [1999])]).float().cpu().numpy()]
+        for i in range(2000, 2150):
+            out.append(eng.step([(s, [toks[i]], [0])]).float().cpu().numpy())
+        eng.close(s)
+        got = np.concatenate(out, axis=0)
+        ref = plain_model.forward(pcfg, w, toks)[1999:]
+        err = np.abs(got - ref).max(axis=1) / np.abs(ref).max()
+        # the 32-bit rotation angle is off by up to position * 2^-24: 1.3e-4 at 2,150 positions
+        assert err.max() < (5e-4 if dtype == "float32" else BF16_TOL), int(err.argmax())
+        if dtype == "float32":
+            import fp32_mirror
+
+            assert np.array_equal(got, fp32_mirror.forward(pcfg, w, toks)[1999:])
+        else:
+            assert len({k[1] for k in eng._graphs}) >= 2  # more than one context bucket was captured
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)

@@ -649,3 +649,98 @@ def test_a_toy_architecture_from_config_json_to_generation(weights, tmp_path):
     with pytest.raises(CheckpointError) as e:
         reflex_b200.Model.load(folder, weights=weights)
     assert "toy.1.att.qn" in str(e.value) and "toy.extra" in str(e.value)
+
+
+def test_a_cache_group_whose_values_are_smaller_than_its_keys():
+    """A toy mixer that keeps a compressed value per position: its `KVSpec` asks
+    for 32-element keys and 8-element values.  The cache gives it pages of both
+    shapes under one page table; it reads and writes them with the step's
+    device-side positions and slots, and the model steps like any other."""
+    from reflex_b200.cache import KVSpec
+    from reflex_b200.config.spec import FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec
+    from reflex_b200.engine import CausalLM, Engine
+    from reflex_b200.parts import TensorInfo, register_mixer
+    from reflex_b200.weights import random_tensors
+
+    DK, DV = 32, 8
+
+    @register_mixer("toy_latent_attention")
+    class ToyLatent:
+        """One head; keys [DK], values compressed to [DV] and expanded after the
+        weighted sum; plain causal softmax attention."""
+
+        def __init__(self, spec, dtype, device):
+            self.spec, self.dtype, self.device = spec, dtype, device
+
+        @classmethod
+        def tensor_specs(cls, spec):
+            H = spec.hidden_size
+            return {"wq": TensorInfo((DK, H), "matrix"), "wk": TensorInfo((DK, H), "matrix"),
+                    "wv": TensorInfo((DV, H), "matrix"), "wo": TensorInfo((H, DV), "matrix")}
+
+        def cache_spec(self):
+            return KVSpec(1, DK, None, v_head_dim=DV)
+
+        def bind(self, tensors):
+            self.w = {k: v.to(self.device, torch.float32) for k, v in tensors.items()}
+
+        def forward(self, x, ctx):
+            kv, b = ctx.kv, ctx.batch
+            assert kv.k_pages.shape[-1] == DK and kv.v_pages.shape[-1] == DV
+            xf = x.float()
+            q, k, v = xf @ self.w["wq"].T, xf @ self.w["wk"].T, xf @ self.w["wv"].T
+            pos, slot = b.row_pos.long(), b.row_slot.long()
+            page = kv.page_table[slot, pos // kv.page_size].long()
+            kv.k_pages[page, 0, pos % kv.page_size] = k.to(kv.k_pages.dtype)
+            kv.v_pages[page, 0, pos % kv.page_size] = v.to(kv.v_pages.dtype)
+            out = torch.empty((x.shape[0], DV), dtype=torch.float32, device=x.device)
+            for i, sl in enumerate(b.slots):  # a row at a time: a toy
+                for r in range(b.row0[i], b.row0[i + 1]):
+                    p = b.starts[i] + (r - b.row0[i])
+                    idx = torch.arange(p + 1, device=x.device)
+                    pg = kv.page_table[sl, idx // kv.page_size].long()
+                    keys = kv.k_pages[pg, 0, idx % kv.page_size].float()
+                    vals = kv.v_pages[pg, 0, idx % kv.page_size].float()
+                    a = torch.softmax((keys @ q[r]) * DK ** -0.5, dim=0)
+                    out[r] = a @ vals
+            return out @ self.w["wo"].T
+
+    H, V = 24, 53
+    mixer = MixerSpec("toy_latent_attention", hidden_size=H,
+                      names=(("wq", "a.q"), ("wk", "a.k"), ("wv", "a.v"), ("wo", "a.o")))
+    ffn = FeedForwardSpec("swiglu", H, 40, names=(("gate_proj", "f.g"), ("up_proj", "f.u"), ("down_proj", "f.d")))
+    norm = NormSpec("rmsnorm", H, 1e-5)
+    layers = [LayerSpec("prenorm", f"l{i}.", mixer, ffn, norm, norm, names=(("mixer_norm", "n1"), ("feed_forward_norm", "n2")))
+              for i in range(2)]
+    spec = ModelSpec("toy_latent", V, H, layers, norm, tie_word_embeddings=True, max_positions=256,
+                     embedding_name="emb", final_norm_name="fn")
+    model = CausalLM(spec, torch.float32, DEV)
+    tensors = dict(random_tensors(spec, 2, torch.float32))
+    for k in tensors:
+        if ".a." in k:
+            tensors[k] = tensors[k] * 20  # attention that matters
+    model.bind(tensors)
+    eng = Engine(model, max_tokens=512)
+    g = eng.cache.kv_groups[0]
+    assert g.k.shape[-1] == DK and g.v.shape[-1] == DV
+    w = {k: v.double().numpy() for k, v in tensors.items()}
+
+    def plain(tokens):
+        T = len(tokens)
+        h = w["emb"][np.array(tokens)]
+        for i in range(2):
+            p = f"l{i}."
+            x = pm.rms_norm(h, w[p + "n1"], 1e-5)
+            q, k, v = x @ w[p + "a.q"].T, x @ w[p + "a.k"].T, x @ w[p + "a.v"].T
+            a = pm.causal_attention(q[:, None, :], k[:, None, :], np.pad(v, ((0, 0), (0, DK - DV)))[:, None, :],
+                                    DK ** -0.5, None)[:, 0, :DV]
+            h = h + a @ w[p + "a.o"].T
+            x = pm.rms_norm(h, w[p + "n2"], 1e-5)
+            h = h + pm.swiglu(x, w[p + "f.g"], w[p + "f.u"], w[p + "f.d"])
+        return pm.rms_norm(h, w["fn"], 1e-5) @ w["emb"].T
+
+    reqs = [helpers.random_tokens(n, V, 70 + n) for n in (70, 4, 9)]
+    got = helpers.run_batches(eng, reqs, 2, [66, 2, 1])
+    for r, gl in zip(reqs, got):
+        assert helpers.rel_err(gl, plain(r)) < 2e-5
+    assert eng.cache.slots.held_count == 0

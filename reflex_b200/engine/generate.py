@@ -103,9 +103,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int,
             first = True
             while live:
                 logits = engine.step(entries, **kw)
-                ids = pick(logits, live, [len(outputs[i]) for i in live])
-                if first or stats.decode_steps % 64 == 0:
-                    check_errors()  # the picked ids are on the host: the device has been waited for
+                ids = pick(logits, live, [len(outputs[i]) for i in live])  # (the device's error word comes with them)
                 if not first:
                     stats.decode_steps += 1
                     stats.decode_tokens += len(live)
@@ -157,9 +155,9 @@ def _decode_ahead(engine, entries, live, seqs, outputs, max_new_tokens, stops, p
                 tokens_dev = pending.dev[[at[i] for i in goes_on]]
             logits = engine.step_decode([seqs[i] for i in goes_on], tokens_dev, **kw)
             next_pending = pick_async(logits, goes_on, [len(outputs[i]) + 1 for i in goes_on])
-        ids = pending.wait()  # the step that picked them is over: the rows it carried are free
-        if first or stats.decode_steps % 64 == 0:
-            check_errors()
+        # the step that picked them is over: the rows it carried are free (the device's
+        # error word comes with the ids: no wait of its own inside the loop)
+        ids = pending.wait()
         if not first and any(i not in ended for i in live):
             stats.decode_steps += 1  # a step that carried only ended requests is not counted
         first = False

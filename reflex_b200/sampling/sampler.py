@@ -33,13 +33,24 @@ def trace_top2(logits: torch.Tensor, requests: Sequence[int]) -> None:
 
 class PendingIds:
     """Ids picked on the device and on their way to the host: `dev` (int32 [n])
-    can feed the next step at once; `wait()` gives the host list."""
+    can feed the next step at once; `wait()` gives the host list.  The device's
+    error word travels with them, so reading a step's ids also tells whether a
+    kernel up to that step reported an error, without a wait of its own."""
 
-    def __init__(self, dev: torch.Tensor, host: torch.Tensor, event):
+    def __init__(self, dev: torch.Tensor, host: torch.Tensor, event, err_host=None, err_dev=None):
         self.dev, self.host, self.event = dev, host, event
+        self.err_host, self.err_dev = err_host, err_dev
 
     def wait(self) -> List[int]:
         self.event.synchronize()
+        if self.err_host is not None:
+            code = int(self.err_host[0])
+            if code:
+                from ..errors import CudaError
+
+                self.err_dev.zero_()
+                raise CudaError(f"a kernel reported an error (code {code}: a bounded wait that ran out, or a "
+                                f"token id outside the vocabulary); the step's results are not valid")
         return self.host.tolist()
 
 
@@ -70,7 +81,7 @@ class Sampler:
     RING = 3  # picks in flight at most: the one being read and the one feeding the next step
 
     def _slot(self, n: int):
-        """(ids on the device, argmax scratch, pinned host ids, event) for the
+        """(ids on the device, argmax scratch, pinned host ids, event, pinned error word) for the
         next pick of n rows, from a small ring per batch size."""
         ring = _RINGS.setdefault((str(self.device), n), {"next": 0, "slots": [None] * self.RING})
         i = ring["next"]
@@ -79,7 +90,8 @@ class Sampler:
             ring["slots"][i] = (torch.empty((n,), dtype=torch.int32, device=self.device),
                                 torch.empty((n * 128,), dtype=torch.float32, device=self.device),
                                 torch.empty((n,), dtype=torch.int32, pin_memory=True),
-                                torch.cuda.Event())
+                                torch.cuda.Event(),
+                                torch.zeros((1,), dtype=torch.int32, pin_memory=True))
         return ring["slots"][i]
 
     def _upload_uniforms(self, values: List[float]) -> torch.Tensor:
@@ -105,7 +117,7 @@ class Sampler:
         """As `pick`, without waiting: the ids stay on the device for the next
         step and travel to the host behind an event."""
         n, V = logits.shape
-        dev, scratch, host, event = self._slot(n)
+        dev, scratch, host, event, err_host = self._slot(n)
         if TOP2_TRACE:
             trace_top2(logits, requests)
         if self.params.is_greedy():
@@ -118,8 +130,10 @@ class Sampler:
                 self._work = torch.empty((ops.sample_work_bytes(n, V),), dtype=torch.uint8, device=self.device)
             ops.sample(logits, t, u, top_k=k, top_p=tp, scratch=self._scratch[:n], out=dev, work=self._work)
         host.copy_(dev, non_blocking=True)
+        err_dev = ops.device_error_word(self.device)
+        err_host.copy_(err_dev, non_blocking=True)
         event.record()
-        return PendingIds(dev, host, event)
+        return PendingIds(dev, host, event, err_host, err_dev)
 
     def pick(self, logits: torch.Tensor, requests: Sequence[int], steps: Sequence[int]) -> List[int]:
         """logits [n, V] for the given requests, each at its own step count;

@@ -281,3 +281,21 @@ def test_system1_refuses_bad_candidates_and_gives_its_slots_back():
     assert small.engine.cache.slots.held_count == 0
     res = model.system1_evaluate([1, 2, 3], [[4, 5], [6]])
     assert len(res.probabilities) == 2
+
+
+def test_a_device_error_reaches_the_generation_loop_with_the_ids():
+    """The device's error word travels to the host with each step's picked ids,
+    so the loop learns of a kernel's error without a wait of its own: here a
+    bounded wait is made to run out just before a generation call, which must
+    raise, give its slots back, and leave the next call working."""
+    import reflex_b200
+    from reflex_b200 import CudaError, ops
+
+    folder = helpers.model_folder("A", 7, "bfloat16")
+    model = reflex_b200.Model.load(folder, weights="bf16", max_tokens=1024)
+    good = model.generate([[1, 2, 3], [4, 5]], 5)
+    ops.wait_probe(100_000)  # 0.1 ms on a barrier nothing signals: the error word is set
+    with pytest.raises(CudaError):
+        model.generate([[1, 2, 3], [4, 5]], 5)
+    assert model.engine.cache.slots.held_count == 0
+    assert model.generate([[1, 2, 3], [4, 5]], 5) == good

@@ -9,6 +9,11 @@ taken again:
 
     python -m reflex_b200.diagnostics decode-step [--batch 8] [--layers 3]
     python -m reflex_b200.diagnostics prefill-attention [--tokens 2048]
+    python -m reflex_b200.diagnostics decode-attention [--cases 64x640,8x4096]
+
+The third times the decode attention kernel alone with CUDA events, for each
+(batch x context) case at every number of key splits, beside the number the
+split model (`ops.decode_splits`) picks: the figures that model is fitted to.
 
 The reference times phases of a step with CUDA events
 (src/model/prefill_profile.rs:26-59, `REFLEX_PREFILL_PROFILE`); stamps written
@@ -163,6 +168,48 @@ def prefill_attention(tokens: int, config: Dict, out=sys.stdout) -> None:
     print(f"kernel, CUDA events, mean of 10 back-to-back launches: {a.elapsed_time(b) * 100:.1f} us", file=out)
 
 
+def decode_attention(cases: List[str], config: Dict, out=sys.stdout) -> None:
+    """Microseconds and GB/s of `ops.attention_decode` over a scrambled paged
+    cache, per case and number of key splits (20 launches after 3 warm-up
+    launches; a case's cache is larger than L2 from 126 MB on)."""
+    from . import ops
+
+    nq, nkv = config["num_attention_heads"], config["num_key_value_heads"]
+    d = config.get("head_dim") or config["hidden_size"] // nq
+    dev = "cuda:0"
+    for case in cases:
+        B, ctx = (int(x) for x in case.lower().split("x"))
+        pages_per = (ctx + 63) // 64
+        n_pages = B * pages_per
+        kp = torch.randn(n_pages, nkv, 64, d, device=dev).bfloat16()
+        vp = torch.randn(n_pages, nkv, 64, d, device=dev).bfloat16()
+        table = torch.randperm(n_pages, device=dev).int().reshape(B, pages_per)
+        q = torch.randn(B, nq * d, device=dev).bfloat16()
+        pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
+        slot = torch.arange(B, dtype=torch.int32, device=dev)
+        cells = []
+        for s_ in (1, 2, 4, 8, 16, 32):
+            if s_ > pages_per:
+                break
+
+            def run():
+                ops.attention_decode(q, kp, vp, table, 64, pos, slot, nq, nkv, d, None, d ** -0.5, n_splits=s_)
+
+            for _ in range(3):
+                run()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            for _ in range(20):
+                run()
+            b.record()
+            torch.cuda.synchronize()
+            us = a.elapsed_time(b) / 20 * 1000
+            cells.append(f"{s_} splits {us:7.1f} us {B * ctx * nkv * d * 4 / us / 1e3:5.0f} GB/s")
+        pick = ops.decode_splits(B, nq, nkv, pages_per)
+        print(f"batch {B:3d} context {ctx:6d} (model picks {pick:2d}): " + " | ".join(cells), file=out)
+
+
 def main(argv: List[str] = None) -> int:
     ap = argparse.ArgumentParser(prog="python -m reflex_b200.diagnostics", description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="what", required=True)
@@ -174,12 +221,18 @@ def main(argv: List[str] = None) -> int:
     b = sub.add_parser("prefill-attention")
     b.add_argument("--tokens", type=int, default=2048)
     b.add_argument("--config", default="", help="a config.json (default: Qwen3-8B layer sizes)")
+    c = sub.add_parser("decode-attention")
+    c.add_argument("--cases", default="1x640,8x640,64x640,32x1152,64x2048,8x4096,64x4096,8x16384,1x16384",
+                   help="batch x context, comma separated")
+    c.add_argument("--config", default="", help="a config.json (default: Qwen3-8B layer sizes)")
     ns = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("error: diagnostics: no CUDA device (there is no CPU path)", file=sys.stderr)
         return 1
     if ns.what == "decode-step":
         decode_step(ns.batch, ns.layers, ns.prompt, _config(ns.config))
+    elif ns.what == "decode-attention":
+        decode_attention(ns.cases.split(","), _config(ns.config))
     else:
         prefill_attention(ns.tokens, _config(ns.config))
     return 0

@@ -62,3 +62,42 @@ def test_generate_step_and_score_match_the_python_entry_point(smoke_program, wei
         assert abs(a - b) <= 1e-5 * max(1.0, abs(b))
     best = int(re.search(r"RFX_CAPI_SCORE_OK best_idx=(\d+)", res.stdout).group(1))
     assert best == want.best_idx
+
+
+def test_the_ctypes_client_turns_failures_into_the_librarys_exceptions():
+    """The same interface from Python through ctypes: a failure comes back as the
+    exception its stable category number names, with the C side's message."""
+    import reflex_b200
+    from reflex_b200.capi.client import CModel
+
+    with pytest.raises(reflex_b200.ReflexError) as e:
+        CModel.load("/nonexistent/model/folder")
+    assert e.value.code in (1, 10) and "nonexistent" in str(e.value)
+
+
+@pytest.mark.gpu
+def test_the_ctypes_client_generates_scores_and_steps_like_the_python_entry_point():
+    import numpy as np
+
+    import reflex_b200
+    from reflex_b200.capi.client import CModel
+
+    folder = helpers.model_folder("B", 7, "bfloat16")
+    prompts = [[5, 17, 3, 9], [11, 2]]
+    model = reflex_b200.Model.load(folder, weights="bf16", max_tokens=4096, max_batch=4)
+    with CModel.load(folder, "bf16", 4096, 4) as c:
+        assert c.generate(prompts, 6) == model.generate(prompts, 6)
+        rows, best, entropy = c.score(prompts[0], [[7], [8, 9]], 1.0)
+        want = model.system1_evaluate(prompts[0], [[7], [8, 9]], 1.0)
+        assert best == want.best_idx and abs(entropy - want.entropy) < 1e-5
+        for (s, p), r, wp in zip(rows, want.results, want.probabilities):
+            assert abs(s - r.score) <= 1e-5 * max(1.0, abs(r.score)) and abs(p - wp) < 1e-5
+        seq = c.open_sequence()
+        logits = np.array(c.step([(seq, prompts[0], [3])]), dtype=np.float32)
+        c.close_sequence(seq)
+        s2 = model.engine.open()  # the same step through the Python engine: the same kernels, the same bits
+        ref = model.engine.step([(s2, prompts[0], [3])]).cpu().numpy()
+        model.engine.close(s2)
+        assert logits.shape == ref.shape and np.array_equal(logits, ref)
+        with pytest.raises(reflex_b200.InvalidInput):
+            c.generate(prompts, 0)

@@ -100,6 +100,25 @@ def decode_step(batch: int, layers: int, prompt: int, config: Dict, out=sys.stdo
         print(f"{name:8s} {int(used.sum()):5d} {span(0)} {span(1)} {span(2)} {span(3)} "
               f"{r[:, 3].max() - r[:, 1].min():14.2f} {gap}", file=out)
         prev_exit = r[:, 3].max()
+    # A CTA's own spans (medians over the CTAs of the layers' launches, us): the
+    # main loop, then the epilogue's parts.  With the K dimension split over a
+    # cluster: partial rows pushed to their owners, the cluster's barrier, the
+    # sum and store; with one CTA a tile: the first 16 columns, the rest.
+    print(f"\n{'product':8s} {'main loop':>10s} {'push / first':>13s} {'barrier / rest':>15s} {'sum+store':>10s} "
+          f"{'to exit':>8s}   (a CTA's medians)", file=out)
+    for k, name in enumerate(names):
+        rows = [t[launch][t[launch][:, 0] > 0] for launch in range(k, 4 * layers, 4)]
+        rec = np.concatenate([x for x in rows if len(x)], axis=0) if rows else np.zeros((0, 8))
+        if not len(rec):
+            continue
+
+        def med(a: int, b: int) -> float:
+            ok = (rec[:, a] > 0) & (rec[:, b] > 0)
+            return float(np.median((rec[:, b] - rec[:, a])[ok]) / 1e3) if ok.any() else float("nan")
+
+        split = bool((rec[:, 6] > 0).any())
+        print(f"{name:8s} {med(1, 2):10.2f} {med(2, 4):13.2f} {med(4, 5):15.2f} "
+              f"{(med(5, 6) if split else float('nan')):10.2f} {med(6 if split else 5, 3):8.2f}", file=out)
     for s in seqs:
         eng.close(s)
 

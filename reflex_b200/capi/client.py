@@ -176,8 +176,11 @@ class CModel:
         if _lib().rfx_close_sequence(self._h, sequence) != 0:
             _raise_last()
 
-    def step(self, entries: Sequence[Tuple[int, Sequence[int], Sequence[int]]]) -> List[List[float]]:
-        """entries: (sequence, tokens, wanted places); float32 logits [wanted][vocab] as lists."""
+    def step(self, entries: Sequence[Tuple[int, Sequence[int], Sequence[int]]]):
+        """entries: (sequence, tokens, wanted places); float32 logits [wanted, vocab]
+        as a NumPy array of its own (the library's buffer is freed before returning)."""
+        import numpy as np
+
         keep = []
         arr = (_StepEntry * len(entries))()
         for i, (seq, toks, want) in enumerate(entries):
@@ -189,7 +192,9 @@ class CModel:
         if _lib().rfx_step(self._h, arr, len(entries), ctypes.byref(res)) != 0:
             _raise_last()
         try:
-            V = res.vocab
-            return [[float(res.logits[r * V + c]) for c in range(V)] for r in range(res.rows)]
+            rows, V = int(res.rows), int(res.vocab)
+            if rows == 0:
+                return np.zeros((0, V), dtype=np.float32)
+            return np.ctypeslib.as_array(res.logits, shape=(rows, V)).copy()
         finally:
             _lib().rfx_free_step_result(ctypes.byref(res))

@@ -136,7 +136,17 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             for (int n = 0; n < D / 16; ++n)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
+            // After the wait on the kernel before: first the loads of the pages that
+            // had to wait for it (the one with this row's own position), then the query
+            // rows, whose latency those loads then cover.
             rfx::pdl_wait();
+#pragma unroll
+            for (int i = 0; i < DEC_STAGES - 1; ++i) {
+                if (i >= issued) {
+                    if (pg0 + i < pg1) issue(pg0 + i, pages_first[i], i);
+                    else cp_async_commit();
+                }
+            }
             // the query heads of this tile; rows beyond the group are zero
             __syncthreads();  // every warp has read the tile for its dry pass
             for (int i = tid; i < 8 * (D / 8); i += DEC_THREADS) {
@@ -147,13 +157,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             }
             __syncthreads();
             load_query_fragments<D>(qs, qf);
-#pragma unroll
-            for (int i = 0; i < DEC_STAGES - 1; ++i) {
-                if (i >= issued) {
-                    if (pg0 + i < pg1) issue(pg0 + i, pages_first[i], i);
-                    else cp_async_commit();
-                }
-            }
         }
         ++pg;
         if (pg >= pg1) break;

@@ -30,6 +30,26 @@ namespace cg = cooperative_groups;
 using namespace attn;
 using rfx::PagedKV;
 
+// Optional timeline for tuning: when a buffer is set (rfx_attention_decode_trace),
+// thread 0 of every CTA stores %globaltimer at chosen moments of its life in the
+// record of its launch: 0 entry, 1 the kernel before is done, 2 query rows loaded,
+// 3 last page done, 4 the warps merged, 5 past the cluster's barrier, 6 exit.
+struct DecTraceRec {
+    unsigned long long t[8];
+};
+static __device__ DecTraceRec* g_dtrace = nullptr;
+static __device__ int g_dtrace_ctas = 0;  // records per launch
+static __device__ int g_dtrace_launches = 0;
+int g_dtrace_next = 0;  // launch counter: the record a launch writes
+__device__ __forceinline__ void dtrace_mark(int launch, int which) {
+    if (g_dtrace == nullptr || launch >= g_dtrace_launches || threadIdx.x != 0) return;
+    const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    if (cta >= g_dtrace_ctas) return;
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    g_dtrace[(size_t)launch * g_dtrace_ctas + cta].t[which] = t;
+}
+
 constexpr int PAGE = 64;
 constexpr int DEC_THREADS = 128;
 constexpr int DEC_STAGES = 3;  // pages in flight per CTA
@@ -42,7 +62,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                         __nv_bfloat16* __restrict__ out, float* __restrict__ partial, int nq,
                         int n_htiles, int n_splits, int window, float scale_log2, int cluster_merge,
-                        int tile_heads) {
+                        int trace_id) {
     constexpr int LD = D + 8;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [16][LD], rows 0..7 used
@@ -54,6 +74,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     float* recv_a = recv_l + MAX_RANKS * 16;                                  // [ranks][slice]
 
     rfx::pdl_launch_dependents();
+    dtrace_mark(trace_id, 0);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r = blockIdx.x;
     const int kvh = blockIdx.y / n_htiles, ht = blockIdx.y % n_htiles;
@@ -140,6 +161,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             // had to wait for it (the one with this row's own position), then the query
             // rows, whose latency those loads then cover.
             rfx::pdl_wait();
+            dtrace_mark(trace_id, 1);
 #pragma unroll
             for (int i = 0; i < DEC_STAGES - 1; ++i) {
                 if (i >= issued) {
@@ -157,12 +179,14 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             }
             __syncthreads();
             load_query_fragments<D>(qs, qf);
+            dtrace_mark(trace_id, 2);
         }
         ++pg;
         if (pg >= pg1) break;
     }
     cp_async_wait<0>();
     __syncthreads();  // all warps are done with the tiles before they are reused below
+    dtrace_mark(trace_id, 3);
 
     // a head's sum lies in the eight lanes that share lane % 4
 #pragma unroll
@@ -235,11 +259,13 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             }
         }
     }
+    dtrace_mark(trace_id, 4);
     if (n_splits > 1 && cluster_merge) {
         // One cluster barrier, then every rank merges its slice in rank order with
         // the combine kernel's arithmetic (the same bits) and writes it.  Nobody
         // reads another rank's memory after the barrier.
         cg::this_cluster().sync();
+        dtrace_mark(trace_id, 5);
         for (int off = tid; off < slice; off += DEC_THREADS) {
             const int i = split * slice + off;
             if (i >= total) break;
@@ -257,7 +283,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             out[((size_t)r * nq + h0 + row) * D + e] = __float2bfloat16_rn(A * inv);
         }
     }
-    (void)tile_heads;
+    dtrace_mark(trace_id, 6);
 }
 
 // out[head] = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in order.
@@ -337,7 +363,7 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
     e = rfx::launch(kernel, grid, dim3(DEC_THREADS), smem, s, cluster_merge ? n_splits : 1,
                     (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
                     cache, row_pos, row_slot, (__nv_bfloat16*)out, partial, nq, n_htiles, n_splits, window,
-                    scale * 1.4426950408889634f, cluster_merge, tile_heads);
+                    scale * 1.4426950408889634f, cluster_merge, g_dtrace_next++);
     if (e != cudaSuccess) return (int)e;
     if (n_splits > 1 && !cluster_merge)
         RFX_LAUNCH(attention_combine_kernel, R * nq, D <= 128 ? 64 : 128, 0, s, (const float*)partial,
@@ -434,6 +460,18 @@ int noalloc_scratch(float** out) {
 }
 
 }  // namespace
+
+// Tuning aid: give the decode attention kernel a device buffer of launches * ctas
+// records of eight 64-bit time stamps; the next launch writes record 0.  Null turns
+// it off.
+extern "C" int rfx_attention_decode_trace(void* buffer, int launches, int ctas) {
+    g_dtrace_next = 0;
+    DecTraceRec* p = (DecTraceRec*)buffer;
+    cudaError_t e = cudaMemcpyToSymbol(g_dtrace, &p, sizeof(p));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_dtrace_ctas, &ctas, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_dtrace_launches, &launches, sizeof(int));
+    return (int)e;
+}
 
 extern "C" long long rfx_attention_decode_noalloc_capacity(void) {
     return (long long)RFX_NOALLOC_SCRATCH_FLOATS;

@@ -71,15 +71,20 @@ def decode_step(batch: int, layers: int, prompt: int, config: Dict, out=sys.stdo
     lib.rfx_gemm_trace.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
     n_launch, n_cta = 4 * layers + 1, 1200
     buf = torch.zeros((n_launch * n_cta * 8,), dtype=torch.int64, device="cuda:0")
+    abuf = torch.zeros((layers * n_cta * 8,), dtype=torch.int64, device="cuda:0")
+    lib.rfx_attention_decode_trace.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
     from .engine.graphs import DecodeGraph
 
     for i in range(6):
         if i == DecodeGraph.WARMUP:  # this call captures the step's graph: its launches get trace ids from 0
             lib.rfx_gemm_trace(buf.data_ptr(), n_launch, n_cta)
+            lib.rfx_attention_decode_trace(abuf.data_ptr(), layers, n_cta)
         logits = eng.step([(s, [t], [0]) for s, t in zip(seqs, ids)])
         ids = ops.argmax(logits).tolist()
     torch.cuda.synchronize()
     lib.rfx_gemm_trace(0, 0, 0)
+    lib.rfx_attention_decode_trace(0, 0, 0)
+    ta = abuf.cpu().numpy().reshape(layers, n_cta, 8).astype(np.float64)
     t = buf.cpu().numpy().reshape(n_launch, n_cta, 8).astype(np.float64)
     t0 = t[t > 0].min()
     names = ["qkv", "o", "gate_up", "down"]
@@ -100,6 +105,17 @@ def decode_step(batch: int, layers: int, prompt: int, config: Dict, out=sys.stdo
         print(f"{name:8s} {int(used.sum()):5d} {span(0)} {span(1)} {span(2)} {span(3)} "
               f"{r[:, 3].max() - r[:, 1].min():14.2f} {gap}", file=out)
         prev_exit = r[:, 3].max()
+    # the attention kernel between a layer's qkv and o products, in the same clock
+    print(f"\n{'attention':9s} {'CTAs':>5s} {'entered':>17s} {'released':>17s} {'query rows':>17s} {'pages done':>17s} "
+          f"{'warps merged':>17s} {'left':>17s}", file=out)
+    for launch in range(layers):
+        rec = ta[launch]
+        used = rec[:, 0] > 0
+        if not used.any():
+            continue
+        r = (rec[used] - t0) / 1e3
+        span = lambda c: f"{r[:, c].min():8.2f}..{r[:, c].max():7.2f}"
+        print(f"{'':9s} {int(used.sum()):5d} {span(0)} {span(1)} {span(2)} {span(3)} {span(4)} {span(6)}", file=out)
     # A CTA's own spans (medians over the CTAs of the layers' launches, us): the
     # main loop, then the epilogue's parts.  With the K dimension split over a
     # cluster: partial rows pushed to their owners, the cluster's barrier, the

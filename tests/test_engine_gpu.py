@@ -139,6 +139,57 @@ def test_float32_logits_equal_the_host_mirror_bit_for_bit(name):
     assert eng.cache.slots.held_count == 0
 
 
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_requests_cut_into_steps_at_random_places(name, dtype):
+    """Seven requests of random lengths through three slots.  Every step takes,
+    from each live request, either one token or a chunk of random length, so
+    chunks of prompts and single tokens of other requests meet in one step, a
+    request's cuts fall anywhere (inside pages, at their edges, at the window's
+    edge), requests end at different steps and the next one takes the slot that
+    came free.  Every position's logits are asked for.  float32: the bits of the
+    host mirror; bfloat16: within the bound of the plain implementation."""
+    V = ALL[name]["vocab_size"]
+    folder = sharp_folder(name, 7, dtype)
+    rng = np.random.default_rng(sum(map(ord, name + dtype)))
+    lengths = [int(x) for x in rng.integers(1, 150, size=7)]
+    reqs = [helpers.random_tokens(n, V, 300 + i) for i, n in enumerate(lengths)]
+    eng = helpers.make_engine(folder, dtype, max_tokens=3 * 192, max_slots=3)
+    waiting = list(range(len(reqs)))
+    live = {}  # request -> (slot, tokens done)
+    got = {i: [] for i in range(len(reqs))}
+    steps = 0
+    while waiting or live:
+        while waiting and len(live) < 3:
+            live[waiting.pop(0)] = (eng.open(), 0)
+        entries, order = [], []
+        for i, (slot, done) in live.items():
+            left = len(reqs[i]) - done
+            n = 1 if rng.random() < 0.4 else int(rng.integers(1, min(left, 70) + 1))
+            entries.append((slot, reqs[i][done:done + n], list(range(n))))
+            order.append((i, n))
+        out = eng.step(entries).float().cpu().numpy()
+        steps += 1
+        row = 0
+        for i, n in order:
+            got[i].append(out[row:row + n])
+            row += n
+            slot, done = live[i]
+            if done + n == len(reqs[i]):
+                eng.close(slot)
+                del live[i]
+            else:
+                live[i] = (slot, done + n)
+    assert eng.cache.slots.held_count == 0 and steps > 7
+    for i, r in enumerate(reqs):
+        g = np.concatenate(got[i], axis=0)
+        if dtype == "float32":
+            ref = mirror_logits(folder, r)
+            bad = np.nonzero((g != ref).any(axis=1))[0]
+            assert bad.size == 0, f"request {i} of {len(r)} tokens: first differing position {int(bad[0])}"
+        else:
+            assert helpers.rel_err(g, helpers.plain_logits(folder, r)) < tol(dtype, sharp=True), (i, len(r))
+
+
 def test_float32_long_decoding_equals_the_host_mirror():
     """300 tokens one by one on the model with sliding layers: page edges, the
     window's edge and pages given back under way, bit for bit."""

@@ -53,7 +53,7 @@ __device__ __forceinline__ void dtrace_mark(int launch, int which) {
 constexpr int PAGE = 64;
 constexpr int DEC_THREADS = 128;
 constexpr int DEC_STAGES = 3;  // pages in flight per CTA
-constexpr int MAX_RANKS = 8;   // portable cluster size
+constexpr int MAX_RANKS = 16;  // 8 is the portable cluster size; 16 where the device places one
 
 template <int D>
 __global__ void __launch_bounds__(DEC_THREADS)
@@ -360,6 +360,31 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, const
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(R, cache.n_kv_heads * n_htiles, n_splits);
+    if (cluster_merge && n_splits > 8) {
+        // a cluster of 16 is beyond the portable size: allowed per kernel, and used
+        // only if the device can place one with this much shared memory (asked once)
+        static int placeable = -1;
+        if (placeable < 0) {
+            placeable = 0;
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+                cudaLaunchConfig_t cfg = {};
+                cfg.gridDim = dim3(1, 1, 16);
+                cfg.blockDim = dim3(DEC_THREADS);
+                cfg.dynamicSmemBytes = smem;
+                cudaLaunchAttribute at[1];
+                at[0].id = cudaLaunchAttributeClusterDimension;
+                at[0].val.clusterDim.x = 1;
+                at[0].val.clusterDim.y = 1;
+                at[0].val.clusterDim.z = 16;
+                cfg.attrs = at;
+                cfg.numAttrs = 1;
+                int n = 0;
+                if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) == cudaSuccess && n > 0) placeable = 1;
+            }
+            cudaGetLastError();  // a refusal is an answer, not an error to carry on
+        }
+        if (!placeable) return RFX_ERR_UNSUPPORTED;
+    }
     e = rfx::launch(kernel, grid, dim3(DEC_THREADS), smem, s, cluster_merge ? n_splits : 1,
                     (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
                     cache, row_pos, row_slot, (__nv_bfloat16*)out, partial, nq, n_htiles, n_splits, window,
@@ -378,7 +403,7 @@ int decode_entry(const void* q, const void* k_pages, const void* v_pages, const 
     if (R <= 0) return 0;
     if (page_size != PAGE || nkv <= 0 || nq % nkv != 0 || n_splits < 1) return RFX_ERR_BAD_ARG;
     if (n_splits > 1 && !partial && !cluster_merge) return RFX_ERR_BAD_ARG;
-    if (cluster_merge && n_splits != 2 && n_splits != 4 && n_splits != 8) return RFX_ERR_UNSUPPORTED;
+    if (cluster_merge && n_splits != 2 && n_splits != 4 && n_splits != 8 && n_splits != 16) return RFX_ERR_UNSUPPORTED;
     if (n_splits > MAX_SPLITS) return RFX_ERR_UNSUPPORTED;
     if (n_splits > 65535 || (long long)nkv * ((nq / nkv + 7) / 8) > 65535) return RFX_ERR_UNSUPPORTED;
     PagedKV cache{page_table, max_pages, page_size, nkv, head_dim};
@@ -411,7 +436,8 @@ extern "C" int rfx_attention_decode(const void* q, const void* k_pages, const vo
                         partial, R, nq, nkv, head_dim, n_splits, window, scale, 0, stream);
 }
 
-// The same with 2, 4 or 8 splits that form a thread-block cluster: every rank
+// The same with 2, 4, 8 or (where the device places such a cluster) 16 splits that
+// form a thread-block cluster: every rank
 // sends its partial to the rank that owns that slice of the output over
 // distributed shared memory, one cluster barrier, and the owners merge in rank
 // order with the combine kernel's arithmetic.  No scratch, no second kernel.

@@ -511,7 +511,7 @@ def decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int = 64) -> int:
     resident together a CTA walks its pages at 1.0 us a page (latency); beyond
     that the SMs are busy throughout and a page costs its share of the memory
     bandwidth, 1.43 us per CTA slot; a CTA's fixed work is 4 to 5 us; 4 us for
-    the launch; the merge 1 us + 0.1 us a split inside a cluster (up to 8
+    the launch; the merge 1 us + 0.1 us a split inside a cluster (up to 16
     splits), 3 us + 0.25 us a split through the combine kernel.  The smallest
     estimate wins."""
     forced = _env_int("REFLEX_B200_DECODE_SPLITS", 0, 0, 64)  # tuning aid
@@ -527,7 +527,7 @@ def decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int = 64) -> int:
         per_split = -(-max_pages // s)
         resident = per_split * 1.0 + 5.0
         streaming = n * (per_split * 1.43 + 4.0) / slots
-        merge = 0.0 if s == 1 else (1.0 + 0.1 * s if s <= 8 else 3.0 + 0.25 * s)
+        merge = 0.0 if s == 1 else (1.0 + 0.1 * s if s <= 16 else 3.0 + 0.25 * s)
         cost = 4.0 + (resident if n <= slots else max(resident, streaming)) + merge
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
@@ -544,7 +544,7 @@ def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_sl
         raise InvalidInput(f"attention_decode takes head_dim in steps of 16 up to 256, got {head_dim}")
     n_splits = n_splits or decode_splits(R, nq, nkv)
     out = _new(q.shape, q.dtype, q.device)
-    if CLUSTER_MERGE and n_splits in (2, 4, 8):
+    if CLUSTER_MERGE and n_splits in (2, 4, 8, 16):
         # the splits as one thread-block cluster that merges its partials itself
         st = native.lib().rfx_attention_decode_cluster(
             q.data_ptr(), _chk(k_pages, "k_pages", torch.bfloat16), _chk(v_pages, "v_pages", torch.bfloat16),

@@ -366,7 +366,7 @@ def test_attention_over_the_paged_cache(kernel, nq, nkv, d, seqs, window):
     (4, 2, 16, [1, 17, 64, 65], None, None), (6, 1, 32, [100, 129], None, 3), (3, 1, 48, [300, 38, 37], 37, 5),
     (32, 8, 128, [640] * 4, None, None), (32, 8, 128, [1, 63, 64, 4000], None, 16), (40, 2, 256, [999], None, 4),
     (7, 7, 80, [255, 256], 100, 2), (32, 8, 128, [520] * 8, None, 4), (32, 8, 128, [100, 3000], None, 8),
-    (20, 1, 64, [130, 64], None, 2)])
+    (20, 1, 64, [130, 64], None, 2), (32, 8, 128, [3840], None, 16), (16, 4, 256, [2000, 5], None, 16)])
 def test_attention_decode_splits(nq, nkv, d, ctxs, window, splits):
     g = torch.Generator().manual_seed(nq + d)
     slots, table, kp, vp, ks, vs = _paged(ctxs, nkv, d, torch.bfloat16, g)
@@ -379,7 +379,7 @@ def test_attention_decode_splits(nq, nkv, d, ctxs, window, splits):
                                  n_splits=splits)
     assert not bool(torch.isnan(out.float()).any())
     assert relerr(out.reshape(R, nq, d), ref) < 8e-3
-    if splits in (2, 4, 8):
+    if splits in (2, 4, 8, 16):
         # merged inside a cluster (the default) or by the combine kernel: the same bits
         import reflex_b200.ops as o
 

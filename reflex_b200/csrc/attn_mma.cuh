@@ -202,18 +202,29 @@ __device__ __forceinline__ void load_query_fragments(const __nv_bfloat16* qs, ui
 // sums l[2] (added across those lanes by the caller at the end), and
 // acc[i][..]: rows 16 i + lane / 4 (+ 8) of O^T for the two heads.
 //   visible(j): whether tile key j (0-based in the tile) is visible
-template <int D, typename Visible>
+//   SWZ: the tiles' layout.  false: [keys][D + 8], rows padded.  true: as the TMA
+//   writes them with the 128-byte swizzle, blocks of 64 columns, [D / 64][keys][64],
+//   a row's 16-byte chunk c at chunk c ^ (row & 7) (tile base 1024-byte aligned).
+template <int D, bool SWZ>
+__device__ __forceinline__ const __nv_bfloat16* tile_at(const __nv_bfloat16* tile, int row, int col) {
+    if (SWZ) {
+        const int chunk = ((col & 63) >> 3) ^ (row & 7);
+        return tile + (col >> 6) * (64 * 64) + row * 64 + chunk * 8 + (col & 7);
+    }
+    return tile + row * (D + 8) + col;
+}
+
+template <int D, bool SWZ = false, typename Visible>
 __device__ __forceinline__ void attend_keys16(const uint32_t (&qf)[D / 16][2], const __nv_bfloat16* ks,
                                               const __nv_bfloat16* vs, int key0, float scale_log2,
                                               Visible visible, float (&m)[2], float (&l)[2],
                                               float (&acc)[D / 16][4]) {
     const int lane = threadIdx.x & 31;
-    constexpr int LD = D + 8;
     float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
     for (int k = 0; k < D / 16; ++k) {
         uint32_t a[4];
-        ldmatrix_x4(a, ks + (key0 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LD + k * 16 + 8 * (lane >> 4));
+        ldmatrix_x4(a, tile_at<D, SWZ>(ks, key0 + (lane & 7) + 8 * ((lane >> 3) & 1), k * 16 + 8 * (lane >> 4)));
         mma_bf16(s, a, qf[k][0], qf[k][1]);
     }
     // s[0], s[1]: key lane / 4, the two heads; s[2], s[3]: key lane / 4 + 8
@@ -254,7 +265,7 @@ __device__ __forceinline__ void attend_keys16(const uint32_t (&qf)[D / 16][2], c
 #pragma unroll
     for (int i = 0; i < D / 16; ++i) {
         uint32_t a[4];
-        ldmatrix_x4_trans(a, vs + (key0 + (lane & 7) + 8 * (lane >> 4)) * LD + i * 16 + 8 * ((lane >> 3) & 1));
+        ldmatrix_x4_trans(a, tile_at<D, SWZ>(vs, key0 + (lane & 7) + 8 * (lane >> 4), i * 16 + 8 * ((lane >> 3) & 1)));
         mma_bf16(acc[i], a, b0, b1);
     }
 }

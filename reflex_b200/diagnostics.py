@@ -71,7 +71,7 @@ def decode_step(batch: int, layers: int, prompt: int, config: Dict, out=sys.stdo
     lib.rfx_gemm_trace.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
     n_launch, n_cta = 4 * layers + 1, 1200
     buf = torch.zeros((n_launch * n_cta * 8,), dtype=torch.int64, device="cuda:0")
-    abuf = torch.zeros((layers * n_cta * 8,), dtype=torch.int64, device="cuda:0")
+    abuf = torch.zeros((layers * n_cta * 12,), dtype=torch.int64, device="cuda:0")
     lib.rfx_attention_decode_trace.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
     from .engine.graphs import DecodeGraph
 
@@ -84,7 +84,7 @@ def decode_step(batch: int, layers: int, prompt: int, config: Dict, out=sys.stdo
     torch.cuda.synchronize()
     lib.rfx_gemm_trace(0, 0, 0)
     lib.rfx_attention_decode_trace(0, 0, 0)
-    ta = abuf.cpu().numpy().reshape(layers, n_cta, 8).astype(np.float64)
+    ta = abuf.cpu().numpy().reshape(layers, n_cta, 12).astype(np.float64)
     t = buf.cpu().numpy().reshape(n_launch, n_cta, 8).astype(np.float64)
     t0 = t[t > 0].min()
     names = ["qkv", "o", "gate_up", "down"]
@@ -203,11 +203,12 @@ def prefill_attention(tokens: int, config: Dict, out=sys.stdout) -> None:
     print(f"kernel, CUDA events, mean of 10 back-to-back launches: {a.elapsed_time(b) * 100:.1f} us", file=out)
 
 
-def decode_attention(cases: List[str], config: Dict, out=sys.stdout) -> None:
+def decode_attention(cases: List[str], config: Dict, out=sys.stdout, stamps: bool = False) -> None:
     """Microseconds and GB/s of `ops.attention_decode` over a scrambled paged
     cache, per case and number of key splits (20 launches after 3 warm-up
     launches; a case's cache is larger than L2 from 126 MB on)."""
     from . import ops
+    from .ops import native
 
     nq, nkv = config["num_attention_heads"], config["num_key_value_heads"]
     d = config.get("head_dim") or config["hidden_size"] // nq
@@ -243,6 +244,25 @@ def decode_attention(cases: List[str], config: Dict, out=sys.stdout) -> None:
             cells.append(f"{s_} splits {us:7.1f} us {B * ctx * nkv * d * 4 / us / 1e3:5.0f} GB/s")
         pick = ops.decode_splits(B, nq, nkv, pages_per)
         print(f"batch {B:3d} context {ctx:6d} (model picks {pick:2d}): " + " | ".join(cells), file=out)
+        if stamps:
+            # one more launch with the model's pick, stamped: where a CTA's time goes
+            lib = native.lib()
+            lib.rfx_attention_decode_trace.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
+            n_cta = B * nkv * ((nq // nkv + 7) // 8) * pick
+            buf = torch.zeros((n_cta * 12,), dtype=torch.int64, device=dev)
+            lib.rfx_attention_decode_trace(buf.data_ptr(), 1, n_cta)
+            ops.attention_decode(q, kp, vp, table, 64, pos, slot, nq, nkv, d, None, d ** -0.5, n_splits=pick)
+            torch.cuda.synchronize()
+            lib.rfx_attention_decode_trace(0, 0, 0)
+            t = buf.cpu().numpy().reshape(n_cta, 12).astype(np.float64)
+            per = -(-pages_per // pick)
+            med = lambda a, b: float(np.median(t[:, b] - t[:, a]) / 1e3)
+            print(f"    {n_cta} CTAs of {per} pages: query rows {med(1, 2):.2f} us, pages {med(2, 3):.2f} us "
+                  f"({med(2, 3) / per:.2f} a page; thread 0's cycles a page: waiting for it "
+                  f"{float(np.median(t[:, 7])) / per:.0f}, issuing later loads {float(np.median(t[:, 8])) / per:.0f}, "
+                  f"tile code {float(np.median(t[:, 9])) / per:.0f}), warps' merge {med(3, 4):.2f}, "
+                  f"to exit {med(4, 6):.2f}; first entry to last exit {(t[:, 6].max() - t[:, 0].min()) / 1e3:.2f} us",
+                  file=out)
 
 
 def main(argv: List[str] = None) -> int:
@@ -260,6 +280,7 @@ def main(argv: List[str] = None) -> int:
     c.add_argument("--cases", default="1x640,8x640,64x640,32x1152,64x2048,8x4096,64x4096,8x16384,1x16384",
                    help="batch x context, comma separated")
     c.add_argument("--config", default="", help="a config.json (default: Qwen3-8B layer sizes)")
+    c.add_argument("--stamps", action="store_true", help="after each case, where a CTA's time goes (its own stamps)")
     ns = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("error: diagnostics: no CUDA device (there is no CPU path)", file=sys.stderr)
@@ -267,7 +288,7 @@ def main(argv: List[str] = None) -> int:
     if ns.what == "decode-step":
         decode_step(ns.batch, ns.layers, ns.prompt, _config(ns.config))
     elif ns.what == "decode-attention":
-        decode_attention(ns.cases.split(","), _config(ns.config))
+        decode_attention(ns.cases.split(","), _config(ns.config), stamps=ns.stamps)
     else:
         prefill_attention(ns.tokens, _config(ns.config))
     return 0

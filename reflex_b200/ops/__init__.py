@@ -544,13 +544,17 @@ def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_sl
         raise InvalidInput(f"attention_decode takes head_dim in steps of 16 up to 256, got {head_dim}")
     n_splits = n_splits or decode_splits(R, nq, nkv)
     out = _new(q.shape, q.dtype, q.device)
+    # pages of the store, for the kernel's TMA maps: [pages, kv heads, page, head_dim], one piece
+    pool_pages = int(k_pages.shape[0]) if (k_pages.dim() == 4 and k_pages.is_contiguous()
+                                           and v_pages.is_contiguous() and v_pages.shape == k_pages.shape) else 0
     if CLUSTER_MERGE and n_splits in (2, 4, 8, 16):
         # the splits as one thread-block cluster that merges its partials itself
         st = native.lib().rfx_attention_decode_cluster(
             q.data_ptr(), _chk(k_pages, "k_pages", torch.bfloat16), _chk(v_pages, "v_pages", torch.bfloat16),
             _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
             _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32), out.data_ptr(),
-            R, nq, nkv, head_dim, n_splits, int(window or 0), float(scale), _stream())
+            R, nq, nkv, head_dim, n_splits, int(window or 0), float(scale), pool_pages,
+            device_error_word(q.device).data_ptr(), _stream())
         if st != native.ERR_UNSUPPORTED:
             native.check(st, f"attention_decode_cluster (head_dim={head_dim}, splits={n_splits})")
             return out
@@ -560,7 +564,7 @@ def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_sl
         _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
         _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32), out.data_ptr(),
         partial.data_ptr() if partial is not None else 0, R, nq, nkv, head_dim, n_splits,
-        int(window or 0), float(scale), _stream())
+        int(window or 0), float(scale), pool_pages, device_error_word(q.device).data_ptr(), _stream())
     native.check(st, f"attention_decode (head_dim={head_dim}, splits={n_splits})")
     return out
 

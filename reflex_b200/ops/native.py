@@ -42,9 +42,11 @@ _SIGNATURES = {
     "rfx_attention_plain": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "rfx_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
-                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong,
+                             c_void_p, c_void_p],
     "rfx_attention_decode_cluster": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
-                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong,
+                                     c_void_p, c_void_p],
     "rfx_attention_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_float, c_void_p],

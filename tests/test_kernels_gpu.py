@@ -366,7 +366,10 @@ def test_attention_over_the_paged_cache(kernel, nq, nkv, d, seqs, window):
     (4, 2, 16, [1, 17, 64, 65], None, None), (6, 1, 32, [100, 129], None, 3), (3, 1, 48, [300, 38, 37], 37, 5),
     (32, 8, 128, [640] * 4, None, None), (32, 8, 128, [1, 63, 64, 4000], None, 16), (40, 2, 256, [999], None, 4),
     (7, 7, 80, [255, 256], 100, 2), (32, 8, 128, [520] * 8, None, 4), (32, 8, 128, [100, 3000], None, 8),
-    (20, 1, 64, [130, 64], None, 2), (32, 8, 128, [3840], None, 16), (16, 4, 256, [2000, 5], None, 16)])
+    (20, 1, 64, [130, 64], None, 2), (32, 8, 128, [3840], None, 16), (16, 4, 256, [2000, 5], None, 16),
+    # one sequence and long walks
+    (32, 8, 128, [3840], None, 8), (32, 8, 128, [8000], None, 16), (8, 2, 64, [2000, 700], None, 4),
+    (3, 1, 48, [3000, 38], 1000, 2), (32, 8, 128, [1500], None, 1)])
 def test_attention_decode_splits(nq, nkv, d, ctxs, window, splits):
     g = torch.Generator().manual_seed(nq + d)
     slots, table, kp, vp, ks, vs = _paged(ctxs, nkv, d, torch.bfloat16, g)

@@ -507,28 +507,36 @@ def decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int = 64) -> int:
     `max_pages` pages.  A split buys parallelism and costs a CTA's fixed work
     (query load, the warps' merge, the exchange of partials) once more.  Fitted
     to kernel times on a B200 at batches of 1 to 64 and contexts of 640 to
-    16,384 (within 10 % of all of them): two CTAs fit an SM; while all CTAs are
-    resident together a CTA walks its pages at 1.0 us a page (latency); beyond
-    that the SMs are busy throughout and a page costs its share of the memory
-    bandwidth, 1.43 us per CTA slot; a CTA's fixed work is 4 to 5 us; 4 us for
-    the launch; the merge 1 us + 0.1 us a split inside a cluster (up to 16
-    splits), 3 us + 0.25 us a split through the combine kernel.  The smallest
-    estimate wins."""
+    16,384: two CTAs fit an SM; a CTA walks its pages at 0.6 us a page with an
+    SM to itself and 0.85 us beside another (its tile code, not the memory);
+    the pages of all CTAs together cannot come faster than the memory gives
+    them, 1.35 us per page and CTA slot; a CTA's fixed work is 3 to 4 us; 4 us
+    for the launch; the merge 1 us + 0.15 us a split inside a cluster of up to
+    8, 5 us in one of 16, 3 us + 0.25 us a split through the combine kernel.
+    The smallest estimate wins."""
     forced = _env_int("REFLEX_B200_DECODE_SPLITS", 0, 0, 64)  # tuning aid
     if forced > 0:
         return forced
     ctas = n_rows * nkv * ((nq // nkv + 7) // 8)
-    slots = 2 * sm_count()
+    sms = sm_count()
+    slots = 2 * sms
     best, best_cost = 1, None
     for s in (1, 2, 4, 8, 16, 32, 64):
         if s > max(1, max_pages):
             break
         n = ctas * s
         per_split = -(-max_pages // s)
-        resident = per_split * 1.0 + 5.0
-        streaming = n * (per_split * 1.43 + 4.0) / slots
-        merge = 0.0 if s == 1 else (1.0 + 0.1 * s if s <= 16 else 3.0 + 0.25 * s)
-        cost = 4.0 + (resident if n <= slots else max(resident, streaming)) + merge
+        resident = per_split * (0.6 if n <= sms else 0.85) + 4.0
+        streaming = n * (per_split * 1.35 + 3.0) / slots
+        if s == 1:
+            merge = 0.0
+        elif s <= 8:
+            merge = 1.0 + 0.15 * s
+        elif s == 16:
+            merge = 5.0
+        else:
+            merge = 3.0 + 0.25 * s
+        cost = 4.0 + max(resident, streaming) + merge
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best

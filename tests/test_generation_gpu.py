@@ -247,7 +247,8 @@ def test_trace_run_replays_steps_and_writes_logits(name, dtype, tmp_path):
 
 def test_diagnostics_print_a_decode_steps_timeline():
     """The kernels' own time stamps, read back for a tiny model: one line per
-    product of the captured step, in launch order, each later than the last."""
+    product of the captured step, in launch order, each later than the last;
+    then the attention kernel of each layer, and a CTA's medians per product."""
     import io
 
     from reflex_b200 import diagnostics
@@ -255,10 +256,16 @@ def test_diagnostics_print_a_decode_steps_timeline():
 
     out = io.StringIO()
     diagnostics.decode_step(batch=2, layers=2, prompt=8, config=dict(TINY_B), out=out)
-    lines = [l.split() for l in out.getvalue().splitlines()[2:]]
+    tables = out.getvalue().split("\n\n")
+    assert len(tables) == 3
+    lines = [l.split() for l in tables[0].splitlines()[2:]]
     assert [l[0] for l in lines] == ["qkv", "o", "gate_up", "down"] * 2 + ["head"]
     left = [float(l[-2]) if len(l) > 11 else float(l[-1]) for l in lines]  # released -> left, us
     assert all(0.0 < v < 1000.0 for v in left)
+    attention = tables[1].splitlines()
+    assert attention[0].split()[0] == "attention" and len(attention) == 1 + 2  # a line per layer
+    medians = [l.split()[0] for l in tables[2].splitlines()[1:]]
+    assert medians == ["qkv", "o", "gate_up", "down"]
 
 
 def test_system1_refuses_bad_candidates_and_gives_its_slots_back():

@@ -511,7 +511,7 @@ def decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int = 64) -> int:
     SM to itself and 0.85 us beside another (its tile code, not the memory);
     the pages of all CTAs together cannot come faster than the memory gives
     them, 1.35 us per page and CTA slot; a CTA's fixed work is 3 to 4 us; 4 us
-    for the launch; the merge 1 us + 0.15 us a split inside a cluster of up to
+    for the launch; the merge 1 us + 0.12 us a split inside a cluster of up to
     8, 5 us in one of 16, 3 us + 0.25 us a split through the combine kernel.
     The smallest estimate wins."""
     forced = _env_int("REFLEX_B200_DECODE_SPLITS", 0, 0, 64)  # tuning aid
@@ -531,7 +531,7 @@ def decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int = 64) -> int:
         if s == 1:
             merge = 0.0
         elif s <= 8:
-            merge = 1.0 + 0.15 * s
+            merge = 1.0 + 0.12 * s
         elif s == 16:
             merge = 5.0
         else:

@@ -190,31 +190,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     // wait, the query rows, and the real passes.
     const bool tracing = g_dtrace != nullptr && tid == 0;
     long long waited = 0, issuing = 0, attending = 0;
-    // After the wait on the kernel before: first the loads of the pages that had to
-    // wait for it (the one with this row's own position), then the query rows, whose
-    // latency those loads then cover.
-#define RFX_AFTER_WAIT()                                                                                   \
-    do {                                                                                                   \
-        rfx::pdl_wait();                                                                                   \
-        dtrace_mark(trace_id, 1);                                                                          \
-        _Pragma("unroll") for (int i = 0; i < DEC_STAGES - 1; ++i) {                                       \
-            if (i >= issued) {                                                                             \
-                if (pg0 + i < pg1) issue(pg0 + i, pages_first[i], i);                                      \
-                else if (!TMA) cp_async_commit();                                                          \
-            }                                                                                              \
-        }                                                                                                  \
-        /* the query heads of this tile; rows beyond the group are zero */                                 \
-        __syncthreads(); /* every warp has read the tile for its dry pass */                               \
-        for (int i = tid; i < 8 * (D / 8); i += NT) {                                                      \
-            const int row = i / (D / 8), c = i % (D / 8);                                                  \
-            uint4 v = make_uint4(0, 0, 0, 0);                                                              \
-            if (row < nh) v = *reinterpret_cast<const uint4*>(q + ((size_t)r * nq + h0 + row) * D + c * 8); \
-            *reinterpret_cast<uint4*>(qs + row * LD + c * 8) = v;                                          \
-        }                                                                                                  \
-        __syncthreads();                                                                                   \
-        load_query_fragments<D>(qs, qf);                                                                   \
-        dtrace_mark(trace_id, 2);                                                                          \
-    } while (0)
     auto reset = [&]() {
         m[0] = m[1] = -INFINITY;
         l[0] = l[1] = 0.0f;
@@ -329,14 +304,35 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             if (tracing && !dry) attending += clock64() - c2;
             if (dry) {
                 reset();
-                RFX_AFTER_WAIT();
+                // After the wait on the kernel before: first the loads of the pages that had
+                // to wait for it (the one with this row's own position), then the query rows,
+                // whose latency those loads then cover.
+                rfx::pdl_wait();
+                dtrace_mark(trace_id, 1);
+#pragma unroll
+                for (int i = 0; i < DEC_STAGES - 1; ++i) {
+                    if (i >= issued) {
+                        if (pg0 + i < pg1) issue(pg0 + i, pages_first[i], i);
+                        else cp_async_commit();
+                    }
+                }
+                // the query heads of this tile; rows beyond the group are zero
+                __syncthreads();  // every warp has read the tile for its dry pass
+                for (int i = tid; i < 8 * (D / 8); i += DEC_THREADS) {
+                    const int row = i / (D / 8), c = i % (D / 8);
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    if (row < nh) v = *reinterpret_cast<const uint4*>(q + ((size_t)r * nq + h0 + row) * D + c * 8);
+                    *reinterpret_cast<uint4*>(qs + row * LD + c * 8) = v;
+                }
+                __syncthreads();
+                load_query_fragments<D>(qs, qf);
+                dtrace_mark(trace_id, 2);
             }
             ++pg;
             if (pg >= pg1) break;
         }
         cp_async_wait<0>();
     }
-#undef RFX_AFTER_WAIT
     __syncthreads();  // all warps are done with the tiles before they are reused below
     dtrace_mark(trace_id, 3);
     if (tracing) {

@@ -369,7 +369,9 @@ def test_attention_over_the_paged_cache(kernel, nq, nkv, d, seqs, window):
     (20, 1, 64, [130, 64], None, 2), (32, 8, 128, [3840], None, 16), (16, 4, 256, [2000, 5], None, 16),
     # one sequence and long walks
     (32, 8, 128, [3840], None, 8), (32, 8, 128, [8000], None, 16), (8, 2, 64, [2000, 700], None, 4),
-    (3, 1, 48, [3000, 38], 1000, 2), (32, 8, 128, [1500], None, 1)])
+    (3, 1, 48, [3000, 38], 1000, 2), (32, 8, 128, [1500], None, 1),
+    # head sizes of three 64-column boxes; a window with the pages coming by TMA
+    (6, 2, 192, [300, 70], None, 2), (8, 2, 128, [500, 100, 64], 100, 2), (4, 4, 64, [257], 65, None)])
 def test_attention_decode_splits(nq, nkv, d, ctxs, window, splits):
     g = torch.Generator().manual_seed(nq + d)
     slots, table, kp, vp, ks, vs = _paged(ctxs, nkv, d, torch.bfloat16, g)

@@ -166,9 +166,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     uint32_t qf[D / 16][2];
     load_query_fragments<D>(qs, qf);  // whatever the tile holds: the dry pass only needs operands
 
-    // a ring of DEC_STAGES pages: one commit group per page, empty groups past the end
-    // The page id of a load is read one iteration before the load is issued, so
-    // the page-table read never stalls the loop.
+    // a ring of DEC_STAGES pages (16-byte copies: one commit group per page, empty
+    // groups past the end; TMA: a barrier per stage).  The page id of a load is read
+    // one iteration before the load is issued, so the page-table read never stalls
+    // the loop.
     int pages_first[DEC_STAGES];
 #pragma unroll
     for (int i = 0; i < DEC_STAGES; ++i) pages_first[i] = pg0 + i < pg1 ? table[pg0 + i] : 0;

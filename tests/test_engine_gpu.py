@@ -647,3 +647,43 @@ def test_a_long_context_across_graph_buckets_and_many_key_splits(dtype):
             assert len({k[1] for k in eng._graphs}) >= 2  # more than one context bucket was captured
     finally:
         shutil.rmtree(folder, ignore_errors=True)
+
+
+def test_a_step_whose_intermediates_pass_two_to_the_31_elements():
+    """26 prompts of 4,096 tokens in one step at the benchmark model's widths (two
+    layers): 106,496 rows, so the feed-forward's intermediate has 2.6e9 elements
+    and every index that multiplies rows by a width must be 64 bits wide.  A
+    request's logits in that batch against the same request alone (the library's
+    matrix product may pick another algorithm for another number of rows, so a
+    last-bit difference is allowed, no more), and a decode step after it."""
+    from reflex_b200.engine import Engine
+    from reflex_b200.weights import random_model_on_device
+
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_size": 4096,
+           "intermediate_size": 12288, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+           "num_hidden_layers": 2, "vocab_size": 2048, "rms_norm_eps": 1e-6, "rope_theta": 1e6,
+           "tie_word_embeddings": False, "max_position_embeddings": 8192}
+    lm = random_model_on_device(cfg, 0, torch.bfloat16, "cuda:0")
+    n_seq, L = 26, 4096
+    assert n_seq * L * 2 * cfg["intermediate_size"] > 2 ** 31
+    eng = Engine(lm, max_tokens=(n_seq + 1) * (L + 64), max_slots=n_seq + 1)
+    g = torch.Generator().manual_seed(1)
+    prompts = torch.randint(0, cfg["vocab_size"], (n_seq, L), generator=g).tolist()
+    want = [0, L // 2, L - 1]
+    seqs = [eng.open() for _ in prompts]
+    big = eng.step([(s, p, want) for s, p in zip(seqs, prompts)]).float().cpu().numpy()
+    eng.check_errors()
+    assert np.isfinite(big).all()
+    for i in (0, 11, n_seq - 1):
+        s = eng.open()
+        one = eng.step([(s, prompts[i], want)]).float().cpu().numpy()
+        eng.close(s)
+        assert helpers.rel_err(big[3 * i:3 * i + 3], one) < 1e-4, i
+    ids = [int(x) for x in big[2::3].argmax(axis=1)]
+    out = eng.step([(s, [t], [0]) for s, t in zip(seqs, ids)]).float().cpu().numpy()
+    eng.check_errors()
+    assert np.isfinite(out).all()
+    for s in seqs:
+        eng.close(s)
+    del eng, lm
+    torch.cuda.empty_cache()

@@ -28,6 +28,7 @@
 #include "common.cuh"
 #include "paged.cuh"
 #include "sm100.cuh"
+#include "tma_host.cuh"
 
 namespace {
 
@@ -416,34 +417,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 }
 
 // ---- host ---------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    return fn;
-}
-
-bool make_map_2d(CUtensorMap* map, const void* base, long long rows, int cols, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
+using rfx::tma::encode_fn;
+using rfx::tma::EncodeTiledFn;
 
 // q [R, nq, D]: dims (D, nq, R), a box of 64 columns x g heads x bq positions
 bool make_map_q(CUtensorMap* map, const void* base, int R, int nq, int D, int g, int bq) {
@@ -468,8 +443,8 @@ int launch_tc(const void* q, const void* k_pages, const void* v_pages, long long
     const int bq = ROWS / g;
     CUtensorMap mq, mk, mv;
     const long long kv_rows = n_pages_total * cache.n_kv_heads * PAGE;
-    if (!make_map_q(&mq, q, R, nq, D, g, bq) || !make_map_2d(&mk, k_pages, kv_rows, D, PAGE) ||
-        !make_map_2d(&mv, v_pages, kv_rows, D, PAGE))
+    if (!make_map_q(&mq, q, R, nq, D, g, bq) || !rfx::tma::make_map_rows64(&mk, k_pages, kv_rows, D, PAGE) ||
+        !rfx::tma::make_map_rows64(&mv, v_pages, kv_rows, D, PAGE))
         return RFX_ERR_UNSUPPORTED;
     const size_t smem = Smem::total(D);
     auto kernel = attention_prefill_tc_kernel<D>;
